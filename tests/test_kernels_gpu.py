@@ -1,0 +1,207 @@
+"""Each CUDA kernel alone against its plain torch reference (tests/cpu_kernels.py),
+at sizes other than the tiny models': widths and vocabularies that are no power
+of two, head sizes in steps of 16, odd head counts and groups."""
+import math
+
+import pytest
+import torch
+
+from cpu_kernels import PAGE, PlainKernels
+
+pytestmark = pytest.mark.gpu
+
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+
+
+@pytest.fixture(scope="module")
+def K():
+    from zlm_b200.kernels import get_kernels
+    return get_kernels()
+
+
+def rnd(shape, dtype, seed, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g) * scale).to(dtype)
+
+
+def close(got, want, dtype, atol=None, rtol=None):
+    atol = atol if atol is not None else (1e-5 if dtype == torch.float32 else 2e-2)
+    rtol = rtol if rtol is not None else (1e-5 if dtype == torch.float32 else 2e-2)
+    torch.testing.assert_close(got.float().cpu(), want.float().cpu(), atol=atol, rtol=rtol)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_embed(K, dtype):
+    V, H, T = 301, 72, 9
+    table = rnd((V, H), DT[dtype], 1)
+    ids = torch.tensor([0, 300, 7, 7, 150, 1, 299, 33, 2], dtype=torch.int32)
+    want = torch.empty(T, H)
+    PlainKernels().embed(want, table, ids)
+    got = torch.empty(T, H, device="cuda")
+    K.embed(got, table.cuda(), ids.cuda())
+    assert torch.equal(got.cpu(), want)
+
+
+@pytest.mark.parametrize("out_dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("w_dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("H", [72, 1000, 4096])
+def test_rmsnorm(K, out_dtype, w_dtype, H):
+    T = 5
+    x = rnd((T, H), torch.float32, 2, 3.0)
+    w = (1 + rnd((H,), torch.float32, 3, 0.1)).to(DT[w_dtype])
+    rows = torch.tensor([4, 0, 2], dtype=torch.int32)
+    for r in (None, rows):
+        R = T if r is None else 3
+        want = torch.empty(R, H, dtype=DT[out_dtype])
+        PlainKernels().rmsnorm(want, x, w, 1e-5, r)
+        got = torch.empty(R, H, dtype=DT[out_dtype], device="cuda")
+        K.rmsnorm(got, x.cuda(), w.cuda(), 1e-5, None if r is None else r.cuda())
+        close(got, want, DT[out_dtype], atol=1e-5 if out_dtype == "float32" else 4e-2)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_swiglu(K, dtype):
+    T, I = 7, 200
+    gu = rnd((T, 2 * I), DT[dtype], 4, 4.0)
+    want = torch.empty(T, I, dtype=DT[dtype])
+    PlainKernels().swiglu(want, gu)
+    got = torch.empty(T, I, dtype=DT[dtype], device="cuda")
+    K.swiglu(got, gu.cuda())
+    close(got, want, DT[dtype], atol=1e-5 if dtype == "float32" else 5e-2)
+
+
+@pytest.mark.parametrize("T,N,K_", [(1, 70, 50), (3, 129, 77), (64, 64, 16), (65, 200, 1000), (130, 67, 33)])
+def test_linear_f32(K, T, N, K_):
+    x, w = rnd((T, K_), torch.float32, 5), rnd((N, K_), torch.float32, 6, 0.1)
+    want = x.double() @ w.double().t()
+    got = torch.empty(T, N, device="cuda")
+    K.linear(got, x.cuda(), w.cuda())
+    close(got, want, torch.float32, atol=1e-5, rtol=1e-5)
+    base = rnd((T, N), torch.float32, 7)
+    acc = base.clone().cuda()
+    K.linear(acc, x.cuda(), w.cuda(), accumulate=True)
+    close(acc, base.double() + want, torch.float32, atol=1e-5, rtol=1e-5)
+
+
+def test_linear_f32_is_batch_invariant(K):
+    x, w = rnd((70, 300), torch.float32, 8), rnd((90, 300), torch.float32, 9)
+    whole = torch.empty(70, 90, device="cuda")
+    K.linear(whole, x.cuda(), w.cuda())
+    for t in (0, 13, 69):
+        one = torch.empty(1, 90, device="cuda")
+        K.linear(one, x[t:t + 1].contiguous().cuda(), w.cuda())
+        assert torch.equal(one[0], whole[t])
+
+
+@pytest.mark.parametrize("T", [1, 2, 3, 4, 5, 8, 9, 16, 17, 33, 64, 65, 128, 300])
+@pytest.mark.parametrize("N,K_", [(72, 40), (200, 1000), (1024, 512), (151, 4096)])
+def test_linear_bf16(K, T, N, K_):
+    x, w = rnd((T, K_), torch.bfloat16, 10), rnd((N, K_), torch.bfloat16, 11, 0.05)
+    want = x.double() @ w.double().t()
+    for out_dtype in (torch.bfloat16, torch.float32):
+        got = torch.empty(T, N, dtype=out_dtype, device="cuda")
+        K.linear(got, x.cuda(), w.cuda())
+        close(got, want, out_dtype, atol=1e-3 if out_dtype == torch.float32 else 3e-2, rtol=1e-2)
+    base = rnd((T, N), torch.float32, 12)
+    acc = base.clone().cuda()
+    K.linear(acc, x.cuda(), w.cuda(), accumulate=True)
+    close(acc, base.double() + want, torch.float32, atol=1e-3, rtol=1e-3)
+
+
+def test_linear_bf16_refuses_odd_inner_size(K):
+    from zlm_b200.kernels import KernelError
+    x, w = rnd((4, 36), torch.bfloat16, 1).cuda(), rnd((8, 36), torch.bfloat16, 2).cuda()
+    with pytest.raises(KernelError, match="multiple of 8"):
+        K.linear(torch.empty(4, 8, dtype=torch.bfloat16, device="cuda"), x, w)
+
+
+def make_paged(nkv, hd, lens, dtype, seed, n_pages=64):
+    """A pool filled at random, a shuffled block table, and per-sequence slots that
+    are not 0, 1, 2 ... so that a wrong slot or page shows."""
+    g = torch.Generator().manual_seed(seed)
+    pool = (torch.randn((n_pages, 2, nkv, PAGE, hd), generator=g)).to(dtype)
+    slots = [3, 0, 5, 1, 4][:len(lens)]
+    table = torch.zeros((6, 16), dtype=torch.int32)
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    for s, n in zip(slots, lens):
+        for lp in range((n + PAGE - 1) // PAGE):
+            table[s, lp] = perm.pop()
+    return pool, table, slots
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("nq,nkv,hd,n_rot,norm", [(4, 2, 16, 16, True), (6, 2, 48, 48, True), (5, 5, 80, 32, False),
+                                                  (8, 1, 128, 128, True), (3, 1, 256, 0, True)])
+def test_qk_norm_rope_write(K, dtype, nq, nkv, hd, n_rot, norm):
+    dt = DT[dtype]
+    lens = [70, 5, 130]
+    pool, table, slots = make_paged(nkv, hd, lens, dt, 20)
+    # new tokens: the last 3 positions of each sequence
+    pos = torch.tensor([p for n in lens for p in range(n - 3, n)], dtype=torch.int32)
+    slot = torch.tensor([s for s in slots for _ in range(3)], dtype=torch.int32)
+    T = pos.numel()
+    qkv = rnd((T, (nq + 2 * nkv) * hd), dt, 21, 2.0)
+    qw = (1 + rnd((hd,), torch.float32, 22, 0.2)) if norm else None
+    kw = (1 + rnd((hd,), torch.float32, 23, 0.2)) if norm else None
+    i = torch.arange(n_rot // 2, dtype=torch.float64)
+    inv = (10000.0 ** (-2.0 * i / hd)).float() if n_rot else None
+    want_qkv, want_pool = qkv.clone(), pool.clone()
+    PlainKernels().qk_norm_rope_write(want_qkv, qw, kw, 1e-6, inv, n_rot, pos, slot, table, want_pool, nq, nkv, hd)
+    got_qkv, got_pool = qkv.cuda(), pool.cuda()
+    c = lambda t: None if t is None else t.cuda()
+    K.qk_norm_rope_write(got_qkv, c(qw), c(kw), 1e-6, c(inv), n_rot, pos.cuda(), slot.cuda(), table.cuda(),
+                         got_pool, nq, nkv, hd)
+    tol = dict(atol=2e-5, rtol=1e-5) if dtype == "float32" else dict(atol=5e-2, rtol=2e-2)
+    close(got_qkv[:, :nq * hd], want_qkv[:, :nq * hd], dt, **tol)
+    close(got_pool, want_pool, dt, **tol)
+    # nothing but the new tokens' places changed
+    changed = (got_pool.cpu() != pool).any(-1).sum().item()
+    assert changed <= T * 2 * nkv
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("nq,nkv,hd,window", [(4, 2, 16, 0), (6, 2, 48, 24), (5, 5, 80, 0), (8, 1, 128, 100),
+                                              (3, 1, 256, 0), (32, 8, 128, 0)])
+def test_attention_over_the_cache(K, dtype, nq, nkv, hd, window):
+    """Decode-like (one query per sequence) and prefill-like (several queries) rows
+    over sequences that span pages; one far key is made to stand out."""
+    dt = DT[dtype]
+    lens = [300, 5, 129, 64]
+    pool, table, slots = make_paged(nkv, hd, lens, dt, 30)
+    pos_list, slot_list = [], []
+    for n, s in zip(lens, slots):
+        for p in ([n - 1] if n != 129 else list(range(120, 129))):
+            pos_list.append(p)
+            slot_list.append(s)
+    pos = torch.tensor(pos_list, dtype=torch.int32)
+    slot = torch.tensor(slot_list, dtype=torch.int32)
+    T = pos.numel()
+    q = rnd((T, nq * hd), dt, 31)
+    # make key 17 of the first sequence (far from its query at 299) dominate head 0
+    page = int(table[slots[0], 17 // PAGE])
+    scale = 1.0 / math.sqrt(hd)
+    q0 = q[0, :hd].float()
+    pool[page, 0, 0, 17 % PAGE, :] = (q0 * (30.0 / (float(q0 @ q0) * scale))).to(dt)   # score 30
+    want = torch.empty(T, nq * hd, dtype=dt)
+    PlainKernels().attention(want, q, pool, table, pos, slot, nq, nkv, hd, scale, window)
+    got = torch.empty(T, nq * hd, dtype=dt, device="cuda")
+    K.attention(got, q.cuda(), pool.cuda(), table.cuda(), pos.cuda(), slot.cuda(), nq, nkv, hd, scale, window)
+    close(got, want, dt, atol=2e-5 if dtype == "float32" else 3e-2, rtol=1e-4 if dtype == "float32" else 3e-2)
+    if window == 0:
+        # the far key really carries the first row's head 0
+        v17 = pool[page, 1, 0, 17 % PAGE, :].float()
+        assert (got[0, :hd].float().cpu() - v17).abs().max() < 0.05 * v17.abs().max() + 0.05
+
+
+def test_argmax_ties_to_lowest_index(K):
+    V = 1543
+    logits = rnd((5, V), torch.float32, 40)
+    logits[1, 700] = logits[1, 1400] = 50.0
+    logits[2, :] = 0.0
+    logits[3, V - 1] = 99.0
+    logits[4, 0] = 99.0
+    out = torch.empty(5, dtype=torch.int32, device="cuda")
+    K.argmax(out, logits.cuda())
+    want = torch.empty(5, dtype=torch.int32)
+    PlainKernels().argmax(want, logits)
+    assert out.cpu().tolist() == want.tolist() == [int(logits[0].argmax()), 700, 0, V - 1, 0]

@@ -1,0 +1,85 @@
+// Shared helpers of the sm_100a kernel library: dtype codes, loads that widen to
+// fp32, warp and block reductions with a fixed order, and the error channel of
+// the extern "C" entry points.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+
+#define ZLM_DTYPE_F32 0
+#define ZLM_DTYPE_BF16 1
+
+// tokens per page of the paged cache; the Python side asserts the same value
+#define ZLM_PAGE 64
+
+#define ZLM_OK 0
+#define ZLM_ERR_ARG 1
+#define ZLM_ERR_CUDA 2
+#define ZLM_ERR_UNSUPPORTED 3
+
+void zlm_set_error(const char* fmt, ...);
+int zlm_check_launch(const char* what);
+
+#define ZLM_REQUIRE(cond, ...)                 \
+    do {                                       \
+        if (!(cond)) {                         \
+            zlm_set_error(__VA_ARGS__);        \
+            return ZLM_ERR_ARG;                \
+        }                                      \
+    } while (0)
+
+__device__ __forceinline__ float to_f32(float v) { return v; }
+__device__ __forceinline__ float to_f32(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) {
+    return __float2bfloat16_rn(v);
+}
+
+// a vector weight (norm weights) may be stored in bf16 or fp32, whatever the
+// compute dtype is; read it through this
+struct VecW {
+    const void* p;
+    int dtype;
+    __device__ __forceinline__ float operator[](int i) const {
+        return dtype == ZLM_DTYPE_F32 ? ((const float*)p)[i]
+                                      : __bfloat162float(((const __nv_bfloat16*)p)[i]);
+    }
+};
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Block-wide sum whose order depends only on blockDim (so a row's result does
+// not depend on what else is in the batch).  `red` holds 32 floats.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nw = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float t = (lane < nw) ? red[lane] : 0.f;
+    t = warp_sum(t);
+    return t;
+}
+__device__ __forceinline__ float block_max(float v, float* red) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nw = (blockDim.x + 31) >> 5;
+    v = warp_max(v);
+    __syncthreads();
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float t = (lane < nw) ? red[lane] : -INFINITY;
+    t = warp_max(t);
+    return t;
+}

@@ -1,0 +1,123 @@
+// Embedding gather, RMSNorm over rows of the fp32 residual stream, and SwiGLU.
+// Formulas: src/runtime/executor.zig:714-764 (row lookup, no scale),
+// src/kernels/transformer/norm.zig:4-37 (eps inside the root, x*inv then *w),
+// src/kernels/transformer/activation.zig:8-13 (g / (1 + e^-g) * u).
+#include "common.cuh"
+#include <stdarg.h>
+#include <stdio.h>
+
+// ---------------------------------------------------------------- error channel
+static thread_local char g_err[512] = "";
+
+void zlm_set_error(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(g_err, sizeof(g_err), fmt, ap);
+    va_end(ap);
+}
+
+int zlm_check_launch(const char* what) {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) {
+        zlm_set_error("%s: %s", what, cudaGetErrorString(e));
+        return ZLM_ERR_CUDA;
+    }
+    return ZLM_OK;
+}
+
+extern "C" const char* zlm_last_error() { return g_err; }
+extern "C" int zlm_page_tokens() { return ZLM_PAGE; }
+
+// ---------------------------------------------------------------- embedding
+template <typename TW>
+__global__ void embed_kernel(float* __restrict__ out, const TW* __restrict__ table,
+                             const int* __restrict__ ids, int H, int V) {
+    const int t = blockIdx.x;
+    int id = ids[t];
+    // ids are validated on the host; clamp so that a bad id can never read
+    // outside the table
+    id = id < 0 ? 0 : (id >= V ? V - 1 : id);
+    const TW* row = table + (size_t)id * H;
+    float* o = out + (size_t)t * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = to_f32(row[i]);
+}
+
+extern "C" int zlm_embed(float* out, const void* table, int table_dtype, const int* ids, int T,
+                         int H, int V, cudaStream_t st) {
+    if (T == 0) return ZLM_OK;
+    ZLM_REQUIRE(T > 0 && H > 0 && V > 0, "embed: bad sizes T=%d H=%d V=%d", T, H, V);
+    const int threads = H >= 1024 ? 256 : 128;
+    if (table_dtype == ZLM_DTYPE_F32)
+        embed_kernel<float><<<T, threads, 0, st>>>(out, (const float*)table, ids, H, V);
+    else if (table_dtype == ZLM_DTYPE_BF16)
+        embed_kernel<__nv_bfloat16><<<T, threads, 0, st>>>(out, (const __nv_bfloat16*)table, ids, H, V);
+    else
+        ZLM_REQUIRE(false, "embed: unsupported table dtype %d", table_dtype);
+    return zlm_check_launch("embed");
+}
+
+// ---------------------------------------------------------------- rmsnorm
+// one block per output row; rows[r] (optional) selects the input row
+template <typename TO>
+__global__ void rmsnorm_kernel(TO* __restrict__ out, const float* __restrict__ x, VecW w,
+                               const int* __restrict__ rows, int H, float eps) {
+    __shared__ float red[32];
+    const int r = blockIdx.x;
+    const int src = rows ? rows[r] : r;
+    const float* xr = x + (size_t)src * H;
+    float s = 0.f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        const float v = xr[i];
+        s = fmaf(v, v, s);
+    }
+    s = block_sum(s, red);
+    const float inv = 1.0f / sqrtf(s / (float)H + eps);
+    TO* o = out + (size_t)r * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = from_f32<TO>((xr[i] * inv) * w[i]);
+}
+
+extern "C" int zlm_rmsnorm(void* out, int out_dtype, const float* x, const void* w, int w_dtype,
+                           const int* rows, int R, int H, float eps, cudaStream_t st) {
+    if (R == 0) return ZLM_OK;
+    ZLM_REQUIRE(R > 0 && H > 0, "rmsnorm: bad sizes R=%d H=%d", R, H);
+    ZLM_REQUIRE(w_dtype == ZLM_DTYPE_F32 || w_dtype == ZLM_DTYPE_BF16, "rmsnorm: weight dtype %d", w_dtype);
+    VecW vw{w, w_dtype};
+    const int threads = 256;   // fixed: the order of the sum must not depend on the batch
+    if (out_dtype == ZLM_DTYPE_F32)
+        rmsnorm_kernel<float><<<R, threads, 0, st>>>((float*)out, x, vw, rows, H, eps);
+    else if (out_dtype == ZLM_DTYPE_BF16)
+        rmsnorm_kernel<__nv_bfloat16><<<R, threads, 0, st>>>((__nv_bfloat16*)out, x, vw, rows, H, eps);
+    else
+        ZLM_REQUIRE(false, "rmsnorm: unsupported output dtype %d", out_dtype);
+    return zlm_check_launch("rmsnorm");
+}
+
+// ---------------------------------------------------------------- swiglu
+// gu is [T, 2I]: gate in columns [0, I), up in [I, 2I)
+template <typename TA>
+__global__ void swiglu_kernel(TA* __restrict__ out, const TA* __restrict__ gu, int T, int I) {
+    const size_t n = (size_t)T * I;
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < n;
+         e += (size_t)gridDim.x * blockDim.x) {
+        const size_t t = e / I;
+        const int i = (int)(e - t * I);
+        const float g = to_f32(gu[t * 2 * I + i]);
+        const float u = to_f32(gu[t * 2 * I + I + i]);
+        out[e] = from_f32<TA>((g / (1.0f + expf(-g))) * u);
+    }
+}
+
+extern "C" int zlm_swiglu(void* out, const void* gu, int dtype, int T, int I, cudaStream_t st) {
+    if (T == 0) return ZLM_OK;
+    ZLM_REQUIRE(T > 0 && I > 0, "swiglu: bad sizes T=%d I=%d", T, I);
+    const size_t n = (size_t)T * I;
+    int blocks = (int)((n + 255) / 256);
+    if (blocks > 148 * 16) blocks = 148 * 16;
+    if (dtype == ZLM_DTYPE_F32)
+        swiglu_kernel<float><<<blocks, 256, 0, st>>>((float*)out, (const float*)gu, T, I);
+    else if (dtype == ZLM_DTYPE_BF16)
+        swiglu_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)gu, T, I);
+    else
+        ZLM_REQUIRE(false, "swiglu: unsupported dtype %d", dtype);
+    return zlm_check_launch("swiglu");
+}

@@ -1,0 +1,187 @@
+"""Python face of the CUDA kernel library (``csrc/*.cu`` -> ``libzlm_b200.so``).
+
+Every method takes torch tensors that already live on the GPU, checks what the
+kernel cannot check itself (dtype, contiguity, shapes), and launches on torch's
+current stream.  There is no CPU path: constructing ``CudaKernels`` without the
+library or without a GPU raises.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_void_p
+from typing import Optional
+
+import torch
+
+F32, BF16 = 0, 1
+PAGE_TOKENS = 64
+
+_DT = {torch.float32: F32, torch.bfloat16: BF16}
+
+STORE, ACCUM, STORE_F32 = 0, 1, 2
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _dt(t: torch.Tensor) -> int:
+    try:
+        return _DT[t.dtype]
+    except KeyError:
+        raise KernelError(f"unsupported dtype {t.dtype}") from None
+
+
+def _ptr(t: Optional[torch.Tensor]) -> int:
+    return 0 if t is None else t.data_ptr()
+
+
+class CudaKernels:
+    """Loads (building first if needed) the kernel library and exposes its entry
+    points.  One instance per process is enough; see ``get_kernels``."""
+
+    name = "cuda"
+
+    def __init__(self, verbose_build: bool = True):
+        from .csrc.build import library_path
+        self.lib_path = library_path(verbose=verbose_build)
+        self.lib = ctypes.CDLL(self.lib_path)
+        self.lib.zlm_last_error.restype = ctypes.c_char_p
+        if self.lib.zlm_page_tokens() != PAGE_TOKENS:
+            raise KernelError("kernel library and Python disagree on the cache page size")
+        if not torch.cuda.is_available():
+            raise KernelError("zlm_b200 needs a CUDA GPU (sm_100a); none is visible and there is no CPU path")
+        self._fn = {}
+
+    # -- plumbing ---------------------------------------------------------
+    def _call(self, name: str, *args):
+        fn = self._fn.get(name)
+        if fn is None:
+            fn = getattr(self.lib, name)
+            fn.restype = c_int
+            self._fn[name] = fn
+        rc = fn(*args)
+        if rc != 0:
+            raise KernelError(self.lib.zlm_last_error().decode())
+
+    @staticmethod
+    def _stream() -> c_void_p:
+        return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    # -- kernels ----------------------------------------------------------
+    def embed(self, out: torch.Tensor, table: torch.Tensor, ids: torch.Tensor) -> None:
+        """out[t, :] = table[ids[t], :] widened to fp32."""
+        T, H = out.shape
+        assert out.dtype == torch.float32 and ids.dtype == torch.int32 and table.shape[1] == H
+        assert out.is_contiguous() and table.is_contiguous()
+        self._call("zlm_embed", c_void_p(out.data_ptr()), c_void_p(table.data_ptr()), c_int(_dt(table)),
+                   c_void_p(ids.data_ptr()), c_int(T), c_int(H), c_int(table.shape[0]), self._stream())
+
+    def rmsnorm(self, out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, eps: float,
+                rows: Optional[torch.Tensor] = None) -> None:
+        """out[r] = x[rows[r] or r] * rsqrt(mean(x^2) + eps) * w; x is the fp32 stream."""
+        R, H = out.shape
+        assert x.dtype == torch.float32 and x.shape[1] == H and w.shape == (H,)
+        assert out.is_contiguous() and x.is_contiguous() and w.is_contiguous()
+        assert rows is None or (rows.dtype == torch.int32 and rows.numel() >= R)
+        self._call("zlm_rmsnorm", c_void_p(out.data_ptr()), c_int(_dt(out)), c_void_p(x.data_ptr()),
+                   c_void_p(w.data_ptr()), c_int(_dt(w)), c_void_p(_ptr(rows)), c_int(R), c_int(H),
+                   c_float(eps), self._stream())
+
+    def swiglu(self, out: torch.Tensor, gu: torch.Tensor) -> None:
+        """out[t, i] = silu(gu[t, i]) * gu[t, I + i]."""
+        T, I = out.shape
+        assert gu.shape == (T, 2 * I) and gu.dtype == out.dtype
+        assert out.is_contiguous() and gu.is_contiguous()
+        self._call("zlm_swiglu", c_void_p(out.data_ptr()), c_void_p(gu.data_ptr()), c_int(_dt(out)),
+                   c_int(T), c_int(I), self._stream())
+
+    def linear(self, out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, accumulate: bool = False) -> None:
+        """out = x @ w.T (out in x's dtype, or fp32), or out += x @ w.T into the fp32
+        residual stream when ``accumulate``.  w is [N, K] row-major."""
+        T, K = x.shape
+        N = w.shape[0]
+        assert w.shape[1] == K and out.shape == (T, N) and w.dtype == x.dtype
+        assert x.stride(1) == 1 and out.stride(1) == 1 and w.is_contiguous()
+        ldx, ldy = x.stride(0), out.stride(0)
+        if accumulate:
+            assert out.dtype == torch.float32
+        if x.dtype == torch.float32:
+            assert out.dtype == torch.float32 and ldx == K
+            self._call("zlm_gemm_f32", c_void_p(out.data_ptr()), c_void_p(x.data_ptr()),
+                       c_void_p(w.data_ptr()), c_int(T), c_int(N), c_int(K), c_int(ldy),
+                       c_int(1 if accumulate else 0), self._stream())
+            return
+        if x.dtype != torch.bfloat16:
+            raise KernelError(f"linear: unsupported dtype {x.dtype}")
+        mode = ACCUM if accumulate else (STORE_F32 if out.dtype == torch.float32 else STORE)
+        if mode == STORE:
+            assert out.dtype == torch.bfloat16
+        name = "zlm_gemv_bf16" if T <= 8 else "zlm_gemm_bf16_mma"
+        self._call(name, c_void_p(out.data_ptr()), c_void_p(x.data_ptr()), c_void_p(w.data_ptr()),
+                   c_int(T), c_int(N), c_int(K), c_int(ldx), c_int(ldy), c_int(mode), self._stream())
+
+    def qk_norm_rope_write(self, qkv: torch.Tensor, q_w: Optional[torch.Tensor],
+                           k_w: Optional[torch.Tensor], eps: float,
+                           inv_freq: Optional[torch.Tensor], n_rot: int, token_pos: torch.Tensor,
+                           token_slot: torch.Tensor, block_table: Optional[torch.Tensor],
+                           pool: Optional[torch.Tensor], nq: int, nkv: int, hd: int,
+                           write: bool = True) -> None:
+        """On qkv [T, (nq + 2 nkv) hd]: per-head RMSNorm of q and k (if weights are
+        given), rotation of q and k by the token's position (if inv_freq is given); q is
+        updated in place; with ``write`` k and v go to the token's place in the paged
+        pool, without it k is updated in place and v is left alone.  With nkv == 0 only
+        q is touched (a layer that reads another layer's cache)."""
+        T = qkv.shape[0]
+        assert qkv.shape[1] == (nq + 2 * nkv) * hd and qkv.stride(1) == 1
+        has_norm = q_w is not None
+        if has_norm:
+            assert q_w.shape == (hd,) and (nkv == 0 or (k_w is not None and k_w.shape == (hd,) and k_w.dtype == q_w.dtype))
+        if inv_freq is not None:
+            assert inv_freq.dtype == torch.float32 and inv_freq.numel() * 2 == n_rot
+        else:
+            n_rot = 0
+        write = bool(write and nkv)
+        if write:
+            assert pool is not None and pool.dtype == qkv.dtype and pool.is_contiguous()
+            assert tuple(pool.shape[1:]) == (2, nkv, PAGE_TOKENS, hd)
+            assert block_table is not None and block_table.dtype == torch.int32
+        self._call("zlm_qk_norm_rope_write", c_void_p(qkv.data_ptr()), c_int(_dt(qkv)), c_int(qkv.stride(0)),
+                   c_void_p(_ptr(q_w)), c_void_p(_ptr(k_w)), c_int(_dt(q_w) if has_norm else F32),
+                   c_int(1 if has_norm else 0), c_float(eps), c_void_p(_ptr(inv_freq)), c_int(n_rot),
+                   c_void_p(token_pos.data_ptr()), c_void_p(token_slot.data_ptr()),
+                   c_void_p(_ptr(block_table)), c_int(block_table.stride(0) if block_table is not None else 0),
+                   c_void_p(_ptr(pool)), c_int(nq), c_int(nkv), c_int(hd), c_int(1 if write else 0), c_int(T),
+                   self._stream())
+
+    def attention(self, out: torch.Tensor, q: torch.Tensor, pool: torch.Tensor, block_table: torch.Tensor,
+                  token_pos: torch.Tensor, token_slot: torch.Tensor, nq: int, nkv: int, hd: int,
+                  scale: float, window: int, plan=None) -> None:
+        """out[t, h] = softmax(q[t, h] . K * scale) V over the keys [start, pos[t]] of the
+        token's slot; q may be a column view of the fused qkv buffer."""
+        T = q.shape[0]
+        assert out.shape == (T, nq * hd) and q.shape[1] == nq * hd and q.dtype == out.dtype == pool.dtype
+        assert q.stride(1) == 1 and out.stride(1) == 1 and pool.is_contiguous()
+        assert tuple(pool.shape[1:]) == (2, nkv, PAGE_TOKENS, hd)
+        self._call("zlm_attention_generic", c_void_p(out.data_ptr()), c_int(out.stride(0)),
+                   c_void_p(q.data_ptr()), c_int(q.stride(0)), c_int(_dt(q)), c_void_p(pool.data_ptr()),
+                   c_void_p(block_table.data_ptr()), c_int(block_table.stride(0)),
+                   c_void_p(token_pos.data_ptr()), c_void_p(token_slot.data_ptr()), c_int(T), c_int(nq),
+                   c_int(nkv), c_int(hd), c_float(scale), c_int(window), self._stream())
+
+    def argmax(self, out: torch.Tensor, logits: torch.Tensor) -> None:
+        """out[r] = index of the highest logit of row r, ties to the lowest index."""
+        R, V = logits.shape
+        assert logits.dtype == torch.float32 and logits.stride(1) == 1 and out.dtype == torch.int32
+        self._call("zlm_argmax", c_void_p(out.data_ptr()), c_void_p(logits.data_ptr()), c_int(R), c_int(V),
+                   c_int(logits.stride(0)), self._stream())
+
+
+_KERNELS: Optional[CudaKernels] = None
+
+
+def get_kernels() -> CudaKernels:
+    global _KERNELS
+    if _KERNELS is None:
+        _KERNELS = CudaKernels()
+    return _KERNELS

@@ -1,0 +1,177 @@
+"""Interfaces of the parts a model is put together from, and the two objects they
+are handed: ``Runtime`` (device, compute dtype, kernels, scratch buffers; lives
+as long as the engine) and ``StepContext`` (which tokens this step runs, where
+they sit in their sequences and in the cache; lives for one step).
+
+No part knows which model it is in: it gets its sizes and constants as
+constructor parameters, names its tensors by local names, and sees the rest of
+the world only through these two objects.
+
+Interfaces
+----------
+Norm              forward(out[R, H], x_f32[T, H], rows=None)
+PositionEncoding  either fused into the mixer (``RotaryHalfSplit`` exposes
+                  ``inv_freq`` / ``n_rot``) or ``apply(q, k, ctx)`` in place
+Mixer             forward(x[T, H], residual_f32[T, H], ctx, io): residual += mix(x)
+FeedForward       forward(x[T, H], residual_f32[T, H], ctx): residual += ffn(x)
+Block             forward(hidden_f32[T, H], ctx, io)
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Dict, List, Optional, Sequence, Tuple
+
+import torch
+
+
+@dataclass(frozen=True)
+class ParamSpec:
+    """One tensor a part wants from the checkpoint.
+
+    kind:  "matrix"  cast to the compute dtype;
+           "vector"  kept in 32-bit if the file stores it so, else compute dtype;
+           "int"     integer table, kept as int32.
+    init:  how the random-weights mode fills it ("normal": N(0, 0.02);
+           "one_plus_normal": 1 + N(0, 0.02); "zeros").
+    ignorable: may be present in the file although the part does not use it.
+    """
+    shape: Tuple[int, ...]
+    kind: str = "matrix"
+    init: str = "normal"
+    ignorable: bool = False
+
+
+@dataclass(frozen=True)
+class CacheRequest:
+    """What a mixer wants to keep per token: keys and values for ``num_kv_heads``
+    heads of ``head_dim``, either all of them (window == 0) or the last
+    ``window``."""
+    num_kv_heads: int
+    head_dim: int
+    window: int = 0
+
+
+@dataclass(frozen=True)
+class StateRequest:
+    """Fixed-size state a mixer wants per sequence (zeroed when a slot is taken)."""
+    shape: Tuple[int, ...]
+    dtype: torch.dtype = torch.float32
+
+
+class Workspace:
+    """Scratch buffers by name.  A buffer grows when asked for more and keeps its
+    address otherwise, so steady-state steps allocate nothing and captured
+    graphs stay valid; ``generation`` counts the reallocations."""
+
+    def __init__(self, device):
+        self.device = device
+        self._bufs: Dict[str, torch.Tensor] = {}
+        self.generation = 0
+
+    def get(self, name: str, shape: Sequence[int], dtype: torch.dtype) -> torch.Tensor:
+        n = 1
+        for s in shape:
+            n *= int(s)
+        key = f"{name}:{dtype}"
+        buf = self._bufs.get(key)
+        if buf is None or buf.numel() < n:
+            buf = torch.empty(max(n, 1), dtype=dtype, device=self.device)
+            self._bufs[key] = buf
+            self.generation += 1
+        return buf[:n].view(*shape)
+
+
+class Runtime:
+    def __init__(self, device, dtype: torch.dtype, kernels):
+        self.device = device
+        self.dtype = dtype
+        self.k = kernels
+        self.ws = Workspace(device)
+
+
+@dataclass
+class CacheView:
+    """One schedule entry's share of a cache group: ``pool`` is
+    [pages, 2, kv_heads, PAGE_TOKENS, head_dim]; ``block_table`` [slots, max_pages]
+    maps a slot's logical page to a pool page; ``writes`` is False for an entry
+    that reads another entry's cache."""
+    pool: torch.Tensor
+    block_table: torch.Tensor
+    writes: bool
+    group: Any = None
+
+
+@dataclass
+class LayerIO:
+    """What one schedule entry owns beside its weights."""
+    cache: Optional[CacheView] = None
+    state: Optional[torch.Tensor] = None     # [slots, *StateRequest.shape]
+
+
+@dataclass
+class StepContext:
+    """The tokens of one step.  Device tensors are int32.  Sequence r contributes
+    tokens cu_seqlens[r] .. cu_seqlens[r+1]-1, which sit at positions
+    seq_start[r] .. seq_start[r] + seq_new[r] - 1 of slot seq_slot[r]."""
+    T: int
+    R: int
+    token_ids: torch.Tensor
+    token_pos: torch.Tensor
+    token_slot: torch.Tensor
+    token_seq: torch.Tensor
+    seq_slot: torch.Tensor
+    seq_start: torch.Tensor
+    seq_new: torch.Tensor
+    cu_seqlens: torch.Tensor
+    # host copies of the per-sequence arrays
+    h_seq_slot: List[int] = field(default_factory=list)
+    h_seq_start: List[int] = field(default_factory=list)
+    h_seq_new: List[int] = field(default_factory=list)
+    is_decode: bool = False
+    max_new: int = 0
+    max_len: int = 0          # longest sequence after this step
+    extras: Dict[str, Any] = field(default_factory=dict)
+
+
+class Part:
+    """Base of every part.  ``rt`` is set by ``attach`` before ``bind``."""
+    rt: Runtime
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        return {}
+
+    def attach(self, rt: Runtime) -> None:
+        self.rt = rt
+
+    def bind(self, params: Dict[str, torch.Tensor]) -> None:
+        """Takes the loaded tensors (by local name).  May fuse or re-lay them."""
+
+    # a part whose forward launches only kernels (no host-side branching on
+    # device data, no allocation) may be captured in a CUDA graph
+    graph_safe = True
+
+
+class Norm(Part):
+    def forward(self, out: torch.Tensor, x: torch.Tensor, rows: Optional[torch.Tensor] = None) -> None:
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    def apply(self, q: torch.Tensor, k: Optional[torch.Tensor], ctx: StepContext) -> None:
+        raise NotImplementedError
+
+
+class Mixer(Part):
+    def cache_request(self) -> Optional[CacheRequest]:
+        return None
+
+    def state_request(self) -> Optional[StateRequest]:
+        return None
+
+    def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx: StepContext, io: LayerIO) -> None:
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx: StepContext) -> None:
+        raise NotImplementedError

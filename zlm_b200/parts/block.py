@@ -1,0 +1,39 @@
+"""Block arrangements: how a mixer and a feed-forward sit on the residual stream.
+
+``pre_norm``: h = h + mixer(norm(h)); h = h + ffn(norm(h)), plain adds in fp32
+(src/architectures/impl/qwen3/block.zig:21-41).  The parts add their output
+into the stream themselves, so the last projection of each can carry the add.
+"""
+from __future__ import annotations
+
+from typing import Dict
+
+import torch
+
+from ..registry import register_arrangement
+from .base import FeedForward, LayerIO, Mixer, Norm, Part, StepContext
+
+
+@register_arrangement("pre_norm")
+class PreNormBlock(Part):
+    def __init__(self, hidden_size: int, mixer: Mixer, feed_forward: FeedForward,
+                 mixer_norm: Norm, feed_forward_norm: Norm):
+        self.hidden = int(hidden_size)
+        self.mixer, self.ffn = mixer, feed_forward
+        self.mixer_norm, self.ffn_norm = mixer_norm, feed_forward_norm
+
+    def children(self) -> Dict[str, Part]:
+        return {"mixer": self.mixer, "feed_forward": self.ffn,
+                "mixer_norm": self.mixer_norm, "feed_forward_norm": self.ffn_norm}
+
+    @property
+    def graph_safe(self) -> bool:      # type: ignore[override]
+        return all(c.graph_safe for c in self.children().values())
+
+    def forward(self, hidden: torch.Tensor, ctx: StepContext, io: LayerIO) -> None:
+        rt = self.rt
+        x = rt.ws.get("block.normed", hidden.shape, rt.dtype)
+        self.mixer_norm.forward(x, hidden)
+        self.mixer.forward(x, hidden, ctx, io)
+        self.ffn_norm.forward(x, hidden)
+        self.ffn.forward(x, hidden, ctx)

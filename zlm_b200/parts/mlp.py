@@ -1,0 +1,39 @@
+"""Dense SwiGLU feed-forward: down(silu(gate x) * up x), silu(g) = g / (1 + e^-g)
+(src/architectures/impl/qwen3/block.zig:36-39,
+src/kernels/transformer/activation.zig:8-13).  Gate and up are one fused
+projection [gate | up], as the reference fuses them for decode
+(src/kernels/linear/matvec/form/fused.zig:27-86).
+"""
+from __future__ import annotations
+
+from typing import Dict
+
+import torch
+
+from ..registry import register_feed_forward
+from .base import FeedForward, ParamSpec, StepContext
+
+
+@register_feed_forward("swiglu")
+class SwiGLU(FeedForward):
+    def __init__(self, hidden_size: int, intermediate_size: int):
+        self.hidden = int(hidden_size)
+        self.inter = int(intermediate_size)
+
+    def param_specs(self) -> Dict[str, ParamSpec]:
+        return {"gate_proj.weight": ParamSpec((self.inter, self.hidden)),
+                "up_proj.weight": ParamSpec((self.inter, self.hidden)),
+                "down_proj.weight": ParamSpec((self.hidden, self.inter))}
+
+    def bind(self, params: Dict[str, torch.Tensor]) -> None:
+        self.w_gu = torch.cat([params.pop("gate_proj.weight"), params.pop("up_proj.weight")], dim=0).contiguous()
+        self.w_down = params.pop("down_proj.weight")
+
+    def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx: StepContext) -> None:
+        rt, k = self.rt, self.rt.k
+        T = x.shape[0]
+        gu = rt.ws.get("ffn.gu", (T, 2 * self.inter), rt.dtype)
+        k.linear(gu, x, self.w_gu)
+        act = rt.ws.get("ffn.act", (T, self.inter), rt.dtype)
+        k.swiglu(act, gu)
+        k.linear(residual, act, self.w_down, accumulate=True)
