@@ -30,25 +30,26 @@ class StepError(ValueError):
 
 
 class MetaLayout:
-    """Offsets of the per-step arrays inside the int32 buffer."""
-    TOKEN_ARRAYS = ("token_ids", "token_pos", "token_slot", "token_seq")
-    SEQ_ARRAYS = ("seq_slot", "seq_start", "seq_new")
+    """Where the per-step arrays sit inside the int32 buffer.  The arrays of a step
+    with T tokens and R sequences are packed at the front, so one small copy carries
+    them; their addresses depend only on (T, R), which is what a captured decode
+    graph is keyed by."""
+    ORDER = ("token_ids", "token_pos", "token_slot", "token_seq", "seq_slot", "seq_start", "seq_new",
+             "cu_seqlens", "want_rows")
 
     def __init__(self, max_tokens: int, max_seqs: int):
         self.max_tokens, self.max_seqs = int(max_tokens), int(max_seqs)
-        off = 0
-        self.off = {}
-        for n in self.TOKEN_ARRAYS:
-            self.off[n] = off
-            off += self.max_tokens
-        for n in self.SEQ_ARRAYS:
-            self.off[n] = off
-            off += self.max_seqs
-        self.off["cu_seqlens"] = off
-        off += self.max_seqs + 1
-        self.off["want_rows"] = off
-        off += self.max_tokens
-        self.size = off
+        self.size = self.used(self.max_tokens, self.max_seqs)
+
+    @staticmethod
+    def offsets(T: int, R: int):
+        return {"token_ids": 0, "token_pos": T, "token_slot": 2 * T, "token_seq": 3 * T,
+                "seq_slot": 4 * T, "seq_start": 4 * T + R, "seq_new": 4 * T + 2 * R,
+                "cu_seqlens": 4 * T + 3 * R, "want_rows": 4 * T + 4 * R + 1}
+
+    @staticmethod
+    def used(T: int, R: int) -> int:
+        return 5 * T + 4 * R + 1
 
 
 class MetaStager:
@@ -67,27 +68,30 @@ class MetaStager:
         self.events: List[Optional[torch.cuda.Event]] = [None] * self.RING
         self.turn = 0
         self.h2d_bytes = 0
+        self.off = MetaLayout.offsets(0, 0)
 
     def view(self, name: str, n: int) -> torch.Tensor:
-        o = self.layout.off[name]
+        o = self.off[name]
         return self.dev[o:o + n]
 
-    def upload(self, arrays) -> None:
-        """arrays: name -> numpy int32 array.  One copy covers all of them."""
+    def upload(self, arrays, T: int, R: int) -> None:
+        """arrays: name -> numpy int32 array of a step with T tokens and R sequences.
+        One copy covers all of them; an array that is absent keeps the device's content
+        (token ids that a previous step left there)."""
         i = self.turn
         self.turn = (self.turn + 1) % self.RING
         if self.events[i] is not None:
             self.events[i].synchronize()
+        self.off = MetaLayout.offsets(T, R)
         h = self.host[i]
         hn = h.numpy()
         lo, hi = self.layout.size, 0
         for name, a in arrays.items():
-            o = self.layout.off[name]
+            o = self.off[name]
             hn[o:o + len(a)] = a
             lo, hi = min(lo, o), max(hi, o + len(a))
         if hi <= lo:
             return
-        # the arrays are spread over the buffer; one copy of the span is cheaper than many
         self.dev[lo:hi].copy_(h[lo:hi], non_blocking=True)
         self.h2d_bytes = (hi - lo) * 4
         if self.cuda:

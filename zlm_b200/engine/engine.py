@@ -62,6 +62,11 @@ class Engine:
         self.layout = MetaLayout(self.max_step_tokens, self.max_batch)
         self.stager = MetaStager(self.layout, self.device)
         self.steps_run = 0
+        from ..sampling import Sampler
+        self.sampler = Sampler(self.rt)
+        self._sample_meta = torch.zeros((2, self.max_batch), dtype=torch.int32, device=self.device)
+        from .decode import DecodeRunner
+        self.decoder = DecodeRunner(self)
 
     # ---- construction -------------------------------------------------------
     @classmethod
@@ -110,12 +115,47 @@ class Engine:
         arrays, T, R, W = plan_step(entries, self.cache.lengths, self.spec.vocab_size, self.layout)
         growth = [(e.slot, len(e.tokens)) for e in entries]
         self.cache.reserve(growth)            # raises before anything is launched
-        self.stager.upload(arrays)
+        self.stager.upload(arrays, T, R)
         ctx = make_context(self.stager, arrays, T, R)
-        hidden = self.model.forward(ctx, self.cache.ios)
-        logits = None
-        if W:
-            logits = self.model.logits(hidden, self.stager.view("want_rows", W), W)
+        logits = self.run_model(ctx, W)
         self.cache.commit(growth)
         self.steps_run += 1
         return logits
+
+    def run_model(self, ctx, wanted: int) -> Optional[torch.Tensor]:
+        """The device work of one step: every schedule entry over the step's tokens,
+        then logits at the ``wanted`` first rows of the uploaded ``want_rows``."""
+        hidden = self.model.forward(ctx, self.cache.ios)
+        if not wanted:
+            return None
+        return self.model.logits(hidden, self.stager.view("want_rows", wanted), wanted)
+
+    # ---- sampling and generation -------------------------------------------------
+    def prefill_sample(self, slots: Sequence[int], prompts: Sequence[Sequence[int]], params,
+                       requests: Sequence[int]) -> List[int]:
+        """One step with every prompt whole; one token chosen per row at its prompt's
+        end, back on the host."""
+        logits = self.step([StepEntry(s, p, [len(p) - 1]) for s, p in zip(slots, prompts)])
+        R = len(slots)
+        meta = self._sample_meta[:, :R]
+        if not params.greedy:
+            # the token being chosen sits at position len(prompt)
+            meta.copy_(torch.tensor([list(requests), [len(p) for p in prompts]], dtype=torch.int32))
+        return self.sampler.sample(logits, params, meta[0], meta[1]).tolist()
+
+    def decode_sample(self, slots: Sequence[int], tokens: Sequence[int], params,
+                      requests: Sequence[int]) -> List[int]:
+        """One decode step: feeds one token per row, returns the next ones on the host."""
+        return self.decoder.step(slots, tokens, params, requests).tolist()
+
+    def generate(self, prompts: Sequence[Sequence[int]], max_tokens: int = 256, temperature: float = 0.0,
+                 top_k: int = 0, top_p: float = 1.0, seed: int = 0,
+                 stop_token_ids: Optional[Sequence[int]] = None, include_stop: bool = False, on_token=None):
+        """Token-id prompts in, generated token ids out (see ``generate.generate``).
+        Option names and defaults are the reference's ``run`` command's
+        (src/cli/commands/run.zig:116-120): max_tokens 256, temperature 0 (greedy),
+        top_k 0 (off), top_p 1 (off)."""
+        from ..sampling import SamplingParams
+        from .generate import generate
+        return generate(self, prompts, max_tokens, SamplingParams(temperature, top_k, top_p, seed),
+                        stop_token_ids, include_stop, on_token)

@@ -52,6 +52,11 @@ class CudaKernels:
         if not torch.cuda.is_available():
             raise KernelError("zlm_b200 needs a CUDA GPU (sm_100a); none is visible and there is no CPU path")
         self._fn = {}
+        self._launches = 0
+
+    def launches(self) -> int:
+        """Kernel launches issued through this object so far."""
+        return self._launches
 
     # -- plumbing ---------------------------------------------------------
     def _call(self, name: str, *args):
@@ -61,6 +66,7 @@ class CudaKernels:
             fn.restype = c_int
             self._fn[name] = fn
         rc = fn(*args)
+        self._launches += 1
         if rc != 0:
             raise KernelError(self.lib.zlm_last_error().decode())
 
@@ -175,6 +181,19 @@ class CudaKernels:
         assert logits.dtype == torch.float32 and logits.stride(1) == 1 and out.dtype == torch.int32
         self._call("zlm_argmax", c_void_p(out.data_ptr()), c_void_p(logits.data_ptr()), c_int(R), c_int(V),
                    c_int(logits.stride(0)), self._stream())
+
+    def sample(self, out: torch.Tensor, logits: torch.Tensor, temperature: float, top_k: int, top_p: float,
+               seed: int, request: torch.Tensor, position: torch.Tensor) -> None:
+        """out[r] = a draw from softmax(logits[r] / temperature) restricted to the top_k
+        best and to the nucleus of mass top_p; the uniform of row r is a hash of
+        (seed, request[r], position[r])."""
+        R, V = logits.shape
+        assert logits.dtype == torch.float32 and logits.stride(1) == 1 and out.dtype == torch.int32
+        assert request.dtype == torch.int32 and position.dtype == torch.int32
+        self._call("zlm_sample", c_void_p(out.data_ptr()), c_void_p(logits.data_ptr()), c_int(R), c_int(V),
+                   c_int(logits.stride(0)), c_float(temperature), c_int(top_k), c_float(top_p),
+                   ctypes.c_ulonglong(seed & 0xFFFFFFFFFFFFFFFF), c_void_p(request.data_ptr()),
+                   c_void_p(position.data_ptr()), self._stream())
 
 
 _KERNELS: Optional[CudaKernels] = None
