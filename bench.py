@@ -243,6 +243,51 @@ def run(args) -> dict:
     }
 
 
+def profile(args) -> int:
+    """A small case for ncu: the engine at the bench's layer sizes with ``--layers``
+    layers; the wanted phase runs eagerly (no graph) between cudaProfilerStart and
+    cudaProfilerStop, so that ``ncu --profile-from-start off`` sees only it."""
+    import torch
+    from zlm_b200 import Engine, StepEntry
+    from zlm_b200.registry import config_from_dict
+    from zlm_b200.sampling import SamplingParams
+    d = dict(QWEN3_8B)
+    d["num_hidden_layers"] = args.layers
+    cfg = config_from_dict(d)
+    B, L = args.batch, args.prompt_len
+    eng = Engine.from_random(cfg, seed=0, dtype="bfloat16", device="cuda:0", max_tokens=B * (L + 256),
+                             max_batch=B, max_seq_len=L + 256, max_step_tokens=min(B, 8) * L)
+    eng.decoder.use_graphs = False
+    g = torch.Generator().manual_seed(0)
+    ps = [torch.randint(0, cfg.vocab_size, (L,), generator=g).tolist() for _ in range(B)]
+    slots = [eng.new_sequence() for _ in ps]
+    rt = torch.cuda.cudart()
+    greedy = SamplingParams()
+    if args.profile == "prefill":
+        eng.step([StepEntry(slots[0], ps[0], [L - 1])])          # warm
+        eng.release(slots[0])
+        slots[0] = eng.new_sequence()
+        torch.cuda.synchronize()
+        rt.cudaProfilerStart()
+        eng.step([StepEntry(slots[0], ps[0], [L - 1])])
+        torch.cuda.synchronize()
+        rt.cudaProfilerStop()
+    else:
+        first = []
+        for i in range(0, B, 8):
+            first += eng.prefill_sample(slots[i:i + 8], ps[i:i + 8], greedy, list(range(i, min(B, i + 8))))
+        eng.decoder.step(slots, first, greedy)
+        eng.decoder.step(slots, None, greedy)
+        torch.cuda.synchronize()
+        rt.cudaProfilerStart()
+        for _ in range(args.steps):
+            eng.decoder.step(slots, None, greedy)
+        torch.cuda.synchronize()
+        rt.cudaProfilerStop()
+    print(f"profiled {args.profile}: layers={args.layers} batch={B} prompt_len={L} steps={args.steps}")
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -253,6 +298,8 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=FULL_LAYERS)
     ap.add_argument("--point-steps", type=int, default=64)
     ap.add_argument("--no-points", action="store_true")
+    ap.add_argument("--profile", choices=["decode", "prefill"], help="run a small case for ncu and exit")
+    ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN)
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
@@ -262,6 +309,8 @@ def main() -> int:
     if args.gpus != 1:
         print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
+    if args.profile:
+        return profile(args)
     args.warmup = max(3, args.warmup)
     print(json.dumps(run(args)))
     return 0

@@ -205,3 +205,46 @@ def test_argmax_ties_to_lowest_index(K):
     want = torch.empty(5, dtype=torch.int32)
     PlainKernels().argmax(want, logits)
     assert out.cpu().tolist() == want.tolist() == [int(logits[0].argmax()), 700, 0, V - 1, 0]
+
+
+class FakePlan:
+    """What the attention kernel wants to know about a step."""
+
+    def __init__(self, len_bucket):
+        self.is_decode, self.len_bucket = True, len_bucket
+        self.bufs = {}
+
+    def scratch(self, name, shape, dtype):
+        self.bufs[name] = torch.empty(shape, dtype=dtype, device="cuda")
+        return self.bufs[name]
+
+
+@pytest.mark.parametrize("len_bucket", [1, 8, 64, 1024])
+@pytest.mark.parametrize("nq,nkv,hd,window", [(4, 2, 16, 0), (6, 2, 48, 24), (5, 5, 80, 0), (8, 1, 128, 100),
+                                              (32, 8, 128, 0), (16, 1, 64, 0), (6, 3, 32, 70)])
+def test_attention_decode_kernel(K, nq, nkv, hd, window, len_bucket):
+    """The split-KV decode kernel (one query per sequence) for several numbers of
+    splits, with a far key that dominates one head and a sequence that ends exactly
+    at a page's edge."""
+    from zlm_b200.kernels import decode_splits
+    dt = torch.bfloat16
+    lens = [700, 5, 129, 64, 65]
+    pool, table, slots = make_paged(nkv, hd, lens, dt, 50, n_pages=40)
+    pos = torch.tensor([n - 1 for n in lens], dtype=torch.int32)
+    slot = torch.tensor(slots, dtype=torch.int32)
+    T = pos.numel()
+    q = rnd((T, nq * hd), dt, 51)
+    scale = 1.0 / math.sqrt(hd)
+    far = 17 if window == 0 else 700 - window          # the oldest key the query may see
+    page = int(table[slots[0], far // PAGE])
+    qh = q[0, (nq - 1) * hd:].float()                  # last head -> last kv head
+    pool[page, 0, nkv - 1, far % PAGE, :] = (qh * (30.0 / (float(qh @ qh) * scale))).to(dt)
+    want = torch.empty(T, nq * hd, dtype=dt)
+    PlainKernels().attention(want, q, pool, table, pos, slot, nq, nkv, hd, scale, window)
+    got = torch.empty(T, nq * hd, dtype=dt, device="cuda")
+    plan = FakePlan(len_bucket)
+    K.attention(got, q.cuda(), pool.cuda(), table.cuda(), pos.cuda(), slot.cuda(), nq, nkv, hd, scale, window, plan)
+    assert (decode_splits(T, nkv, len_bucket) > 1) == bool(plan.bufs)
+    close(got, want, dt, atol=3e-2, rtol=3e-2)
+    vfar = pool[page, 1, nkv - 1, far % PAGE, :].float()
+    assert (got[0, (nq - 1) * hd:].float().cpu() - vfar).abs().max() < 0.05 * vfar.abs().max() + 0.05

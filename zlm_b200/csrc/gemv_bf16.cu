@@ -1,11 +1,25 @@
-// Weight-streaming bf16 matrix-vector product for decode steps of up to 8 tokens:
-// Y[t, n] = sum_k X[t, k] W[n, k].  Each warp owns ROWS rows of W and streams them
-// once with 16-byte loads that bypass L1; the few activation rows stay in L1/L2.
-// Products and sums are fp32; the warp reduction is a fixed butterfly.
-// (src/kernels/linear/matvec/kernels/bfloat.zig:43-67: bf16 widened by a 16-bit
-// shift, fp32 accumulate; src/gpu/kernels/shaders/matvec_bf16.comp:56-121: rows
-// per group, lanes stride over K, subgroup reduction.)
+// Weight-streaming bf16 product for decode steps of up to 16 tokens:
+// Y[t, n] = sum_k X[t, k] W[n, k], fp32 accumulation.
+//
+// The step is bound by reading W once.  A block owns 16 rows of W; its 8 warps
+// split K between them.  Every thread loads 16 bytes (8 consecutive k) of row g
+// and of row g+8 straight from global memory into registers, and the 8 matching
+// k of token g of X; these registers are, as they are, the A and B fragments of
+// two m16n8k16 tensor-core products: a sum over k does not care in which order
+// the k are visited, so the k of a fragment are taken where a 16-byte load puts
+// them instead of where the instruction's layout would want them.  No shared
+// memory is needed for the operands, W is read in whole 32-byte sectors, and the
+// activations cost half the weight's load traffic instead of a multiple of it.
+// The warps' partial sums are added in a fixed order.
+// (src/kernels/linear/matvec/kernels/bfloat.zig:43-67: bf16 widened, fp32 sum;
+// src/gpu/kernels/shaders/matvec_bf16.comp:56-121: rows per group, lanes stride
+// over K, tree reduction.)
 #include "common.cuh"
+
+#define GEMV_WARPS 8
+#define GEMV_THREADS (GEMV_WARPS * 32)
+#define GEMV_ROWS 16
+#define GEMV_UNROLL 4
 
 __device__ __forceinline__ uint4 ld_stream16(const void* p) {
     uint4 v;
@@ -14,90 +28,114 @@ __device__ __forceinline__ uint4 ld_stream16(const void* p) {
                  : "l"(p));
     return v;
 }
-__device__ __forceinline__ void unpack8(const uint4& v, float* f) {
-    // bf16 -> fp32 is a 16-bit shift
-    f[0] = __uint_as_float(v.x << 16); f[1] = __uint_as_float(v.x & 0xffff0000u);
-    f[2] = __uint_as_float(v.y << 16); f[3] = __uint_as_float(v.y & 0xffff0000u);
-    f[4] = __uint_as_float(v.z << 16); f[5] = __uint_as_float(v.z & 0xffff0000u);
-    f[6] = __uint_as_float(v.w << 16); f[7] = __uint_as_float(v.w & 0xffff0000u);
+__device__ __forceinline__ void gemv_mma(float* c, unsigned a0, unsigned a1, unsigned a2, unsigned a3,
+                                         unsigned b0, unsigned b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-#define GEMV_WARPS 4
-
-// MODE 0: Y bf16 = acc; MODE 1: Y fp32 += acc; MODE 2: Y fp32 = acc
-template <int TT, int ROWS, int MODE>
-__global__ void __launch_bounds__(GEMV_WARPS * 32)
+// MODE 0: Y bf16 = acc; MODE 1: Y fp32 += acc; MODE 2: Y fp32 = acc.  NT: token tiles of 8.
+template <int NT, int MODE>
+__global__ void __launch_bounds__(GEMV_THREADS)
 gemv_bf16_kernel(void* __restrict__ Y, const __nv_bfloat16* __restrict__ X,
                  const __nv_bfloat16* __restrict__ W, int T, int N, int K, int ldx, int ldy) {
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int n0 = (blockIdx.x * GEMV_WARPS + warp) * ROWS;
-    if (n0 >= N) return;
-    float acc[ROWS][TT];
+    __shared__ float red[GEMV_WARPS][NT][GEMV_ROWS][8];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int g = lane >> 2, q = lane & 3;
+    const int n0 = blockIdx.x * GEMV_ROWS;
+    const __nv_bfloat16* w0 = W + (size_t)min(n0 + g, N - 1) * K + q * 8;
+    const __nv_bfloat16* w1 = W + (size_t)min(n0 + g + 8, N - 1) * K + q * 8;
+    const __nv_bfloat16* xr[NT];
+    bool xok[NT];
 #pragma unroll
-    for (int r = 0; r < ROWS; ++r)
+    for (int j = 0; j < NT; ++j) {
+        xok[j] = j * 8 + g < T;
+        xr[j] = X + (size_t)(xok[j] ? j * 8 + g : 0) * ldx + q * 8;
+    }
+    float acc[NT][4];
 #pragma unroll
-        for (int t = 0; t < TT; ++t) acc[r][t] = 0.f;
+    for (int j = 0; j < NT; ++j)
+#pragma unroll
+        for (int r = 0; r < 4; ++r) acc[j][r] = 0.f;
 
-    const __nv_bfloat16* wrow[ROWS];
+    // warp w takes the 32-wide k blocks w, w + 8, ...; GEMV_UNROLL of them in flight
+    const int step = GEMV_WARPS * 32;
+    int kb = warp * 32;
+    for (; kb + (GEMV_UNROLL - 1) * step + 32 <= K; kb += GEMV_UNROLL * step) {
+        uint4 a[GEMV_UNROLL], b[GEMV_UNROLL], x[GEMV_UNROLL][NT];
 #pragma unroll
-    for (int r = 0; r < ROWS; ++r) wrow[r] = W + (size_t)min(n0 + r, N - 1) * K;
-
-    for (int k = lane * 8; k < K; k += 32 * 8) {
-        uint4 wv[ROWS];
+        for (int u = 0; u < GEMV_UNROLL; ++u) {
+            a[u] = ld_stream16(w0 + kb + u * step);
+            b[u] = ld_stream16(w1 + kb + u * step);
+        }
 #pragma unroll
-        for (int r = 0; r < ROWS; ++r) wv[r] = ld_stream16(wrow[r] + k);
-        float wf[ROWS][8];
+        for (int u = 0; u < GEMV_UNROLL; ++u)
 #pragma unroll
-        for (int r = 0; r < ROWS; ++r) unpack8(wv[r], wf[r]);
+            for (int j = 0; j < NT; ++j)
+                x[u][j] = xok[j] ? __ldg((const uint4*)(xr[j] + kb + u * step)) : make_uint4(0, 0, 0, 0);
 #pragma unroll
-        for (int t = 0; t < TT; ++t) {
-            if (t < T) {
-                const uint4 xv = __ldg((const uint4*)(X + (size_t)t * ldx + k));
-                float xf[8];
-                unpack8(xv, xf);
+        for (int u = 0; u < GEMV_UNROLL; ++u)
 #pragma unroll
-                for (int r = 0; r < ROWS; ++r)
-#pragma unroll
-                    for (int e = 0; e < 8; ++e) acc[r][t] = fmaf(wf[r][e], xf[e], acc[r][t]);
+            for (int j = 0; j < NT; ++j) {
+                gemv_mma(acc[j], a[u].x, b[u].x, a[u].y, b[u].y, x[u][j].x, x[u][j].y);
+                gemv_mma(acc[j], a[u].z, b[u].z, a[u].w, b[u].w, x[u][j].z, x[u][j].w);
             }
+    }
+    for (; kb < K; kb += step) {
+        // K is a multiple of 8, so a thread's 8 k are all inside or all outside
+        const bool in = kb + q * 8 < K;
+        const uint4 z = make_uint4(0, 0, 0, 0);
+        const uint4 a = in ? ld_stream16(w0 + kb) : z;
+        const uint4 b = in ? ld_stream16(w1 + kb) : z;
+#pragma unroll
+        for (int j = 0; j < NT; ++j) {
+            const uint4 x = (in && xok[j]) ? __ldg((const uint4*)(xr[j] + kb)) : z;
+            gemv_mma(acc[j], a.x, b.x, a.y, b.y, x.x, x.y);
+            gemv_mma(acc[j], a.z, b.z, a.w, b.w, x.z, x.w);
         }
     }
+    // acc[j][0..1]: row g, tokens 8j + 2q, 2q+1; acc[j][2..3]: row g + 8
 #pragma unroll
-    for (int r = 0; r < ROWS; ++r)
+    for (int j = 0; j < NT; ++j) {
+        red[warp][j][g][2 * q] = acc[j][0];
+        red[warp][j][g][2 * q + 1] = acc[j][1];
+        red[warp][j][g + 8][2 * q] = acc[j][2];
+        red[warp][j][g + 8][2 * q + 1] = acc[j][3];
+    }
+    __syncthreads();
+    for (int idx = tid; idx < NT * GEMV_ROWS * 8; idx += GEMV_THREADS) {
+        const int j = idx / (GEMV_ROWS * 8), rem = idx % (GEMV_ROWS * 8);
+        const int tok = j * 8 + rem / GEMV_ROWS, row = rem % GEMV_ROWS;   // rows fastest: coalesced stores
+        const int n = n0 + row;
+        if (tok >= T || n >= N) continue;
+        float s = 0.f;
 #pragma unroll
-        for (int t = 0; t < TT; ++t) acc[r][t] = warp_sum(acc[r][t]);
-    if (lane == 0) {
-#pragma unroll
-        for (int r = 0; r < ROWS; ++r) {
-            const int n = n0 + r;
-            if (n >= N) continue;
-#pragma unroll
-            for (int t = 0; t < TT; ++t) {
-                if (t >= T) continue;
-                const size_t idx = (size_t)t * ldy + n;
-                if (MODE == 0) ((__nv_bfloat16*)Y)[idx] = __float2bfloat16_rn(acc[r][t]);
-                else if (MODE == 1) ((float*)Y)[idx] += acc[r][t];
-                else ((float*)Y)[idx] = acc[r][t];
-            }
-        }
+        for (int w = 0; w < GEMV_WARPS; ++w) s += red[w][j][row][tok & 7];
+        const size_t o = (size_t)tok * ldy + n;
+        if (MODE == 0) ((__nv_bfloat16*)Y)[o] = __float2bfloat16_rn(s);
+        else if (MODE == 1) ((float*)Y)[o] += s;
+        else ((float*)Y)[o] = s;
     }
 }
 
-template <int TT, int ROWS>
+template <int NT>
 static int launch_gemv(void* Y, const __nv_bfloat16* X, const __nv_bfloat16* W, int T, int N, int K,
                        int ldx, int ldy, int mode, cudaStream_t st) {
-    const int rows_per_block = GEMV_WARPS * ROWS;
-    const int blocks = (N + rows_per_block - 1) / rows_per_block;
-    if (mode == 0) gemv_bf16_kernel<TT, ROWS, 0><<<blocks, GEMV_WARPS * 32, 0, st>>>(Y, X, W, T, N, K, ldx, ldy);
-    else if (mode == 1) gemv_bf16_kernel<TT, ROWS, 1><<<blocks, GEMV_WARPS * 32, 0, st>>>(Y, X, W, T, N, K, ldx, ldy);
-    else gemv_bf16_kernel<TT, ROWS, 2><<<blocks, GEMV_WARPS * 32, 0, st>>>(Y, X, W, T, N, K, ldx, ldy);
+    const int blocks = (N + GEMV_ROWS - 1) / GEMV_ROWS;
+    if (mode == 0) gemv_bf16_kernel<NT, 0><<<blocks, GEMV_THREADS, 0, st>>>(Y, X, W, T, N, K, ldx, ldy);
+    else if (mode == 1) gemv_bf16_kernel<NT, 1><<<blocks, GEMV_THREADS, 0, st>>>(Y, X, W, T, N, K, ldx, ldy);
+    else gemv_bf16_kernel<NT, 2><<<blocks, GEMV_THREADS, 0, st>>>(Y, X, W, T, N, K, ldx, ldy);
     return zlm_check_launch("gemv_bf16");
 }
+
+extern "C" int zlm_gemv_max_tokens() { return 16; }
 
 extern "C" int zlm_gemv_bf16(void* Y, const void* X, const void* W, int T, int N, int K, int ldx,
                              int ldy, int mode, cudaStream_t st) {
     if (T == 0 || N == 0) return ZLM_OK;
-    ZLM_REQUIRE(T > 0 && T <= 8, "gemv_bf16: takes 1 to 8 tokens, got %d", T);
+    ZLM_REQUIRE(T > 0 && T <= 16, "gemv_bf16: takes 1 to 16 tokens, got %d", T);
     ZLM_REQUIRE(N > 0 && K > 0, "gemv_bf16: bad sizes N=%d K=%d", N, K);
     ZLM_REQUIRE(K % 8 == 0 && ldx % 8 == 0,
                 "gemv_bf16: the inner size K=%d (row stride %d) must be a multiple of 8 for bf16 kernels", K, ldx);
@@ -105,8 +143,6 @@ extern "C" int zlm_gemv_bf16(void* Y, const void* X, const void* W, int T, int N
     ZLM_REQUIRE(mode >= 0 && mode <= 2, "gemv_bf16: mode %d", mode);
     const __nv_bfloat16* x = (const __nv_bfloat16*)X;
     const __nv_bfloat16* w = (const __nv_bfloat16*)W;
-    if (T == 1) return launch_gemv<1, 4>(Y, x, w, T, N, K, ldx, ldy, mode, st);
-    if (T == 2) return launch_gemv<2, 4>(Y, x, w, T, N, K, ldx, ldy, mode, st);
-    if (T <= 4) return launch_gemv<4, 4>(Y, x, w, T, N, K, ldx, ldy, mode, st);
-    return launch_gemv<8, 2>(Y, x, w, T, N, K, ldx, ldy, mode, st);
+    if (T <= 8) return launch_gemv<1>(Y, x, w, T, N, K, ldx, ldy, mode, st);
+    return launch_gemv<2>(Y, x, w, T, N, K, ldx, ldy, mode, st);
 }

@@ -153,10 +153,16 @@ def plan_step(entries: Sequence[StepEntry], lengths, vocab_size: int, layout: Me
     return arrays, T, R, len(want)
 
 
-def make_context(stager: MetaStager, arrays, T: int, R: int) -> StepContext:
+def make_context(stager: MetaStager, arrays, T: int, R: int, workspace=None) -> StepContext:
     s_new = arrays["seq_new"]
     s_start = arrays["seq_start"]
+    max_len = int((s_start + s_new).max())
+    pages = (max_len + 63) // 64
+    bucket = 1
+    while bucket < pages:
+        bucket *= 2
     return StepContext(
+        len_bucket=bucket, workspace=workspace,
         T=T, R=R,
         token_ids=stager.view("token_ids", T), token_pos=stager.view("token_pos", T),
         token_slot=stager.view("token_slot", T), token_seq=stager.view("token_seq", T),
@@ -164,4 +170,4 @@ def make_context(stager: MetaStager, arrays, T: int, R: int) -> StepContext:
         seq_new=stager.view("seq_new", R), cu_seqlens=stager.view("cu_seqlens", R + 1),
         h_seq_slot=arrays["seq_slot"].tolist(), h_seq_start=s_start.tolist(), h_seq_new=s_new.tolist(),
         is_decode=bool((s_new == 1).all()), max_new=int(s_new.max()),
-        max_len=int((s_start + s_new).max()))
+        max_len=max_len)

@@ -74,7 +74,7 @@ class DecodeRunner:
             meta = torch.from_numpy(np.stack([req, start + 1]))
             e._sample_meta[:, :R].copy_(meta)
         arrays.setdefault("token_ids", ar)   # make_context only needs the shapes
-        ctx = make_context(e.stager, arrays, R, R)
+        ctx = make_context(e.stager, arrays, R, R, e.rt.ws)
         if self.use_graphs:
             self._replay(ctx, R, params)
         else:
@@ -97,7 +97,7 @@ class DecodeRunner:
 
     def _replay(self, ctx, R: int, params: SamplingParams) -> None:
         e = self.e
-        key = (R, ctx.extras.get("graph_key"), params)
+        key = (R, ctx.len_bucket, params)
         if self.graph_generation != e.rt.ws.generation:
             self.graphs.clear()
         g = self.graphs.get(key)

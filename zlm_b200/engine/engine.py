@@ -116,7 +116,7 @@ class Engine:
         growth = [(e.slot, len(e.tokens)) for e in entries]
         self.cache.reserve(growth)            # raises before anything is launched
         self.stager.upload(arrays, T, R)
-        ctx = make_context(self.stager, arrays, T, R)
+        ctx = make_context(self.stager, arrays, T, R, self.rt.ws)
         logits = self.run_model(ctx, W)
         self.cache.commit(growth)
         self.steps_run += 1

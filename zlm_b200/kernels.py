@@ -25,6 +25,15 @@ class KernelError(RuntimeError):
     pass
 
 
+def decode_splits(rows: int, nkv: int, len_bucket: int) -> int:
+    """Into how many parts the decode attention cuts a sequence's keys: enough blocks
+    for a few waves over the GPU's 148 SMs (3 blocks each), but at least 4 pages a
+    part.  ``len_bucket`` is the longest sequence of the step in pages, rounded up to
+    a power of two, so that the choice (and a captured graph) holds for many steps."""
+    want = -(-1776 // max(1, rows * nkv))
+    return max(1, min(want, len_bucket // 4))
+
+
 def _dt(t: torch.Tensor) -> int:
     try:
         return _DT[t.dtype]
@@ -123,7 +132,7 @@ class CudaKernels:
         mode = ACCUM if accumulate else (STORE_F32 if out.dtype == torch.float32 else STORE)
         if mode == STORE:
             assert out.dtype == torch.bfloat16
-        name = "zlm_gemv_bf16" if T <= 8 else "zlm_gemm_bf16_mma"
+        name = "zlm_gemv_bf16" if T <= 16 else "zlm_gemm_bf16_mma"
         self._call(name, c_void_p(out.data_ptr()), c_void_p(x.data_ptr()), c_void_p(w.data_ptr()),
                    c_int(T), c_int(N), c_int(K), c_int(ldx), c_int(ldy), c_int(mode), self._stream())
 
@@ -169,6 +178,20 @@ class CudaKernels:
         assert out.shape == (T, nq * hd) and q.shape[1] == nq * hd and q.dtype == out.dtype == pool.dtype
         assert q.stride(1) == 1 and out.stride(1) == 1 and pool.is_contiguous()
         assert tuple(pool.shape[1:]) == (2, nkv, PAGE_TOKENS, hd)
+        if (plan is not None and plan.is_decode and q.dtype == torch.bfloat16
+                and self.lib.zlm_attention_decode_supported(nq, nkv, hd)):
+            splits = decode_splits(T, nkv, plan.len_bucket)
+            part_o = part_ml = None
+            if splits > 1:
+                part_o = plan.scratch("attn.part_o", (T * nq * splits * hd,), torch.float32)
+                part_ml = plan.scratch("attn.part_ml", (T * nq * splits * 2,), torch.float32)
+            self._call("zlm_attention_decode", c_void_p(out.data_ptr()), c_int(out.stride(0)),
+                       c_void_p(q.data_ptr()), c_int(q.stride(0)), c_void_p(pool.data_ptr()),
+                       c_void_p(block_table.data_ptr()), c_int(block_table.stride(0)),
+                       c_void_p(token_pos.data_ptr()), c_void_p(token_slot.data_ptr()), c_int(T), c_int(nq),
+                       c_int(nkv), c_int(hd), c_float(scale), c_int(window), c_int(splits),
+                       c_void_p(_ptr(part_o)), c_void_p(_ptr(part_ml)), self._stream())
+            return
         self._call("zlm_attention_generic", c_void_p(out.data_ptr()), c_int(out.stride(0)),
                    c_void_p(q.data_ptr()), c_int(q.stride(0)), c_int(_dt(q)), c_void_p(pool.data_ptr()),
                    c_void_p(block_table.data_ptr()), c_int(block_table.stride(0)),

@@ -130,7 +130,13 @@ class StepContext:
     is_decode: bool = False
     max_new: int = 0
     max_len: int = 0          # longest sequence after this step
+    len_bucket: int = 1       # max_len in pages, rounded up to a power of two
+    workspace: Any = None     # the runtime's Workspace
     extras: Dict[str, Any] = field(default_factory=dict)
+
+    def scratch(self, name: str, shape, dtype) -> torch.Tensor:
+        """A scratch buffer that lives until the next kernel asks for the same name."""
+        return self.workspace.get(name, shape, dtype)
 
 
 class Part:
