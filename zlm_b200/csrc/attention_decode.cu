@@ -331,3 +331,53 @@ extern "C" int zlm_attention_decode(void* out, int out_stride, const void* q, in
 #undef ZLM_DEC_CASE
     ZLM_REQUIRE(false, "attention_decode: head_dim=%d", hd);
 }
+
+// ---------------------------------------------------------------------------
+// The same decode attention for callers that must not allocate (declared in
+// zlm_no_alloc.h).  The split partials go to a fixed array that is part of the
+// library's image on every GPU that loads it, instead of to scratch that the
+// caller allocates.
+// ---------------------------------------------------------------------------
+#include "zlm_no_alloc.h"
+
+static __device__ __align__(256) float g_decode_scratch[ZLM_NO_ALLOC_SCRATCH_FLOATS];
+
+#define ZLM_MAX_DEVICES 64
+static float* g_decode_scratch_ptr[ZLM_MAX_DEVICES];     // device address of the array, per device
+
+extern "C" int zlm_attention_decode_static(void* out, int out_stride, const void* q, int q_stride,
+                                           const void* pool, const int* block_table, int table_stride,
+                                           const int* token_pos, const int* token_slot, int T, int nq,
+                                           int nkv, int hd, float scale, int window, int splits,
+                                           cudaStream_t st) {
+    if (T == 0) return ZLM_OK;
+    ZLM_REQUIRE(T > 0 && nq > 0 && hd > 0 && splits >= 1, "attention_decode_static: bad sizes T=%d nq=%d hd=%d splits=%d",
+                T, nq, hd, splits);
+    const unsigned long long need = (unsigned long long)T * nq * splits * ((unsigned long long)hd + 2);
+    ZLM_REQUIRE(splits == 1 || need <= (unsigned long long)ZLM_NO_ALLOC_SCRATCH_FLOATS,
+                "attention_decode_static: T*heads*splits*(head_dim+2) = %llu floats of split partials exceed the "
+                "built-in scratch of %llu floats; use fewer splits or tokens, or zlm_attention_decode with your own scratch",
+                need, (unsigned long long)ZLM_NO_ALLOC_SCRATCH_FLOATS);
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= ZLM_MAX_DEVICES) {
+        zlm_set_error("attention_decode_static: cannot tell the current device (%s)", cudaGetErrorString(e));
+        return ZLM_ERR_CUDA;
+    }
+    if (!g_decode_scratch_ptr[dev]) {
+        // once per device, with that device current: in host code the array's name is
+        // only a handle; the address a kernel can use has to be asked for
+        float* p = nullptr;
+        e = cudaGetSymbolAddress((void**)&p, g_decode_scratch);
+        if (e != cudaSuccess || !p) {
+            zlm_set_error("attention_decode_static: cudaGetSymbolAddress failed on device %d: %s", dev,
+                          cudaGetErrorString(e));
+            return ZLM_ERR_CUDA;
+        }
+        g_decode_scratch_ptr[dev] = p;
+    }
+    float* part_o = g_decode_scratch_ptr[dev];
+    float* part_ml = part_o + (size_t)T * nq * splits * hd;
+    return zlm_attention_decode(out, out_stride, q, q_stride, pool, block_table, table_stride, token_pos,
+                                token_slot, T, nq, nkv, hd, scale, window, splits, part_o, part_ml, st);
+}
