@@ -1,0 +1,255 @@
+"""Parts of (c) alone, and the proof that the framework is open: a toy mixer with
+state of its own and a toy architecture that mixes it with attention, both
+defined here, are registered, built and stepped without a change to any file of
+the package.  (Toy parts only: they are no model of anyone's.)"""
+from dataclasses import dataclass
+
+import pytest
+import torch
+
+import plain_qwen3 as P
+from cpu_kernels import PlainKernels
+
+pytestmark = pytest.mark.gpu
+
+
+def _register_toys():
+    from zlm_b200.config import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
+    from zlm_b200.parts.base import Mixer, ParamSpec, StateRequest
+    from zlm_b200.registry import ARCHITECTURES, MIXERS, register_architecture, register_mixer
+
+    if "toy_running_mean" not in MIXERS:
+        @register_mixer("toy_running_mean")
+        class RunningMean(Mixer):
+            """y_t = W . mean(x_0 .. x_t); the running sum is the sequence's state."""
+            graph_safe = False
+
+            def __init__(self, hidden_size, gain=1.0):
+                self.h, self.gain = hidden_size, gain
+
+            def param_specs(self):
+                return {"mix.weight": ParamSpec((self.h, self.h))}
+
+            def state_request(self):
+                return StateRequest((self.h,), torch.float32)
+
+            def bind(self, params):
+                self.w = params["mix.weight"].float()
+
+            def forward(self, x, residual, ctx, io):
+                t = 0
+                for slot, start, n in zip(ctx.h_seq_slot, ctx.h_seq_start, ctx.h_seq_new):
+                    sums = io.state[slot][None, :] + torch.cumsum(x[t:t + n].float(), 0)
+                    count = torch.arange(start + 1, start + n + 1, device=x.device, dtype=torch.float32)[:, None]
+                    residual[t:t + n] += self.gain * ((sums / count) @ self.w.t())
+                    io.state[slot] = sums[-1]
+                    t += n
+
+    if "ToyForCausalLM" not in ARCHITECTURES:
+        @register_architecture("ToyForCausalLM")
+        @dataclass(frozen=True)
+        class ToyConfig:
+            hidden: int = 48
+            vocab: int = 90
+            eos_token_ids: tuple = ()
+
+            @classmethod
+            def from_dict(cls, d):
+                return cls(d.get("hidden", 48), d.get("vocab", 90))
+
+            def to_dict(self):
+                return {"architectures": ["ToyForCausalLM"], "hidden": self.hidden, "vocab": self.vocab}
+
+            def to_model_spec(self):
+                H = self.hidden
+                norm = lambda p: PartSpec("rms_norm", {"eps": 1e-5}, prefix=p)
+                toy = LayerSpec("pre_norm", PartSpec("toy_running_mean", {"gain": 0.5}, prefix="l0.toy."),
+                                PartSpec("swiglu", {"intermediate_size": 64}, prefix="l0.ffn."),
+                                norm("l0.n1."), norm("l0.n2."))
+                att = LayerSpec("pre_norm", PartSpec("gqa_attention", {
+                    "num_heads": 3, "num_kv_heads": 1, "head_dim": 16, "qk_norm": False,
+                    "position": {"kind": "rope_half_split", "theta": 100.0, "head_dim": 16, "n_rot": 8}},
+                    prefix="l1.att."), PartSpec("swiglu", {"intermediate_size": 32}, prefix="l1.ffn."),
+                    norm("l1.n1."), norm("l1.n2."))
+                return ModelSpec("ToyForCausalLM", H, self.vocab, 512, (toy, att),
+                                 (ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(0)),
+                                 PartSpec("token_embedding", {}, prefix="emb."), norm("out_norm."),
+                                 PartSpec("lm_head", {"tied": True}, prefix="head."))
+    return ARCHITECTURES["ToyForCausalLM"]
+
+
+def toy_reference(t, ids, H):
+    """Whole-sequence plain forward of the toy model (float32, CPU)."""
+    T = len(ids)
+    h = P.embed(t["emb.weight"], ids)
+    pos = torch.arange(T)
+
+    def toy_layer(h):
+        x = P.rms_norm(h, t["l0.n1.weight"], 1e-5)
+        mean = torch.cumsum(x, 0) / torch.arange(1, T + 1)[:, None]
+        h = h + 0.5 * (mean @ t["l0.toy.mix.weight"].t())
+        x = P.rms_norm(h, t["l0.n2.weight"], 1e-5)
+        return h + P.linear(P.swiglu(P.linear(x, t["l0.ffn.gate_proj.weight"]), P.linear(x, t["l0.ffn.up_proj.weight"])),
+                            t["l0.ffn.down_proj.weight"])
+
+    def att_layer(h):
+        x = P.rms_norm(h, t["l1.n1.weight"], 1e-5)
+        q = P.linear(x, t["l1.att.q_proj.weight"]).reshape(T, 3, 16)
+        k = P.linear(x, t["l1.att.k_proj.weight"]).reshape(T, 1, 16)
+        v = P.linear(x, t["l1.att.v_proj.weight"]).reshape(T, 1, 16)
+        q, k = P.rope_half_split(q, pos, 100.0, 8), P.rope_half_split(k, pos, 100.0, 8)
+        h = h + P.linear(P.causal_attention(q, k, v).reshape(T, 48), t["l1.att.o_proj.weight"])
+        x = P.rms_norm(h, t["l1.n2.weight"], 1e-5)
+        return h + P.linear(P.swiglu(P.linear(x, t["l1.ffn.gate_proj.weight"]), P.linear(x, t["l1.ffn.up_proj.weight"])),
+                            t["l1.ffn.down_proj.weight"])
+
+    h = toy_layer(att_layer(toy_layer(h)))
+    return P.linear(P.rms_norm(h, t["out_norm.weight"], 1e-5), t["emb.weight"])
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_toy_mixer_with_state_is_registered_built_and_stepped(dtype):
+    from zlm_b200 import Engine, StepEntry
+    from zlm_b200.parts.model import DecoderModel
+    from zlm_b200.registry import config_from_dict
+    from zlm_b200.weights import random_tensors
+    _register_toys()
+    cfg = config_from_dict({"architectures": ["ToyForCausalLM"], "hidden": 48, "vocab": 90})
+    t = random_tensors(DecoderModel(cfg.to_model_spec()).param_specs(), 3)
+    for n in t:
+        if "toy.mix" in n:
+            t[n] = t[n] * 10        # make the state matter
+    dev = {n: (v.to(dtype) if v.dim() == 2 else v).cuda() for n, v in t.items()}
+    ref = {n: (v.to(dtype).float() if v.dim() == 2 else v) for n, v in t.items()}
+    eng = Engine(cfg, dev, dtype, "cuda:0", max_tokens=1024, max_batch=4)
+    assert not eng.decoder.use_graphs                       # the toy branches on the host
+    assert sum(io.state is not None for io in eng.cache.ios) == 2
+    g = torch.Generator().manual_seed(4)
+    seqs = [torch.randint(0, 90, (n,), generator=g).tolist() for n in (70, 9)]
+    want = [toy_reference(ref, s, 48) for s in seqs]
+    tol = dict(atol=2e-5, rtol=1e-4) if dtype == torch.float32 else dict(atol=3e-2, rtol=3e-2)
+    for round_ in range(2):                                 # the second round reuses slots: state starts at zero again
+        slots = [eng.new_sequence() for _ in seqs]
+        got = eng.step([StepEntry(sl, s[:5], list(range(5))) for sl, s in zip(slots, seqs)]).float().cpu()
+        torch.testing.assert_close(got[:5], want[0][:5], **tol)
+        torch.testing.assert_close(got[5:], want[1][:5], **tol)
+        for i in range(5, 70):
+            ents = [StepEntry(slots[0], [seqs[0][i]], [0])]
+            if i < 9:
+                ents.append(StepEntry(slots[1], [seqs[1][i]], [0]))
+            got = eng.step(ents).float().cpu()
+            torch.testing.assert_close(got[0], want[0][i], **tol)
+            if i < 9:
+                torch.testing.assert_close(got[1], want[1][i], **tol)
+        toks = eng.generate([seqs[1][:4]], max_tokens=3).tokens     # the loop runs the toy too, without graphs
+        assert len(toks[0]) == 3
+        for sl in slots:
+            eng.release(sl)
+    eng.cache.check()
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_parts_alone(dtype):
+    """Norm, feed-forward, embedding and head built from the registries at sizes of
+    their own and run outside any model."""
+    from zlm_b200.kernels import get_kernels
+    from zlm_b200.parts.base import Runtime, StepContext
+    from zlm_b200.registry import EMBEDDINGS, FEED_FORWARDS, HEADS, NORMS
+    rt = Runtime(torch.device("cuda:0"), dtype, get_kernels())
+    pk = PlainKernels()
+    g = torch.Generator().manual_seed(5)
+    H, I, V, T = 88, 136, 203, 11
+    x32 = torch.randn(T, H, generator=g)
+    tol = dict(atol=1e-5, rtol=1e-5) if dtype == torch.float32 else dict(atol=3e-2, rtol=3e-2)
+
+    norm = NORMS["rms_norm"](size=H, eps=1e-4)
+    norm.attach(rt)
+    w = 1 + 0.1 * torch.randn(H, generator=g)
+    norm.bind({"weight": w.cuda()})
+    out = torch.empty(T, H, dtype=dtype, device="cuda")
+    norm.forward(out, x32.cuda())
+    torch.testing.assert_close(out.float().cpu(), P.rms_norm(x32, w, 1e-4), **tol)
+
+    ffn = FEED_FORWARDS["swiglu"](hidden_size=H, intermediate_size=I)
+    ffn.attach(rt)
+    wg, wu, wd = (torch.randn(s, generator=g).mul(0.1).to(dtype) for s in ((I, H), (I, H), (H, I)))
+    ffn.bind({"gate_proj.weight": wg.cuda(), "up_proj.weight": wu.cuda(), "down_proj.weight": wd.cuda()})
+    xin = x32.to(dtype)
+    res = torch.ones(T, H, device="cuda")
+    ffn.forward(xin.cuda(), res, None)
+    mid = P.swiglu(P.linear(xin.float(), wg.float()), P.linear(xin.float(), wu.float()))
+    if dtype == torch.bfloat16:
+        mid = mid.to(dtype).float()
+    torch.testing.assert_close(res.cpu(), 1 + P.linear(mid, wd.float()), **tol)
+
+    emb = EMBEDDINGS["token_embedding"](vocab_size=V, hidden_size=H)
+    emb.attach(rt)
+    table = torch.randn(V, H, generator=g).to(dtype)
+    emb.bind({"weight": table.cuda()})
+    ids = torch.tensor([0, V - 1, 17], dtype=torch.int32).cuda()
+    e = torch.empty(3, H, device="cuda")
+    emb.forward(e, ids)
+    assert torch.equal(e.cpu(), table[[0, V - 1, 17]].float())
+
+    head = HEADS["lm_head"](vocab_size=V, hidden_size=H, tied=True)
+    head.attach(rt)
+    head.tie(table.cuda())
+    logits = torch.empty(T, V, device="cuda")
+    head.forward(logits, xin.cuda())
+    torch.testing.assert_close(logits.cpu(), P.linear(xin.float(), table.float()), atol=1e-4 if dtype == torch.float32 else 5e-2, rtol=1e-2)
+
+
+def test_attention_part_alone_with_another_position_encoding():
+    """The attention mixer with a position encoding that is not fused: a toy one
+    that scales q and k by a position-dependent factor, applied between the norm
+    and the cache write."""
+    from zlm_b200.kernels import get_kernels
+    from zlm_b200.cache import KVCache
+    from zlm_b200.config import ScheduleEntry
+    from zlm_b200.engine.batch import MetaLayout, MetaStager, StepEntry, make_context, plan_step
+    from zlm_b200.parts.base import PositionEncoding, Runtime
+    from zlm_b200.registry import MIXERS, POSITION_ENCODINGS, register_position_encoding
+
+    if "toy_scale" not in POSITION_ENCODINGS:
+        @register_position_encoding("toy_scale")
+        class ToyScale(PositionEncoding):
+            fused = False
+
+            def __init__(self, rate):
+                self.rate = rate
+
+            def apply(self, q, k, ctx):
+                f = (1.0 + self.rate * ctx.token_pos.float())[:, None]
+                q.copy_((q.float() * f).to(q.dtype))
+                if k is not None:
+                    k.copy_((k.float() / f).to(k.dtype))
+
+    H, nq, nkv, hd = 40, 4, 2, 16
+    rt = Runtime(torch.device("cuda:0"), torch.float32, get_kernels())
+    att = MIXERS["gqa_attention"](hidden_size=H, num_heads=nq, num_kv_heads=nkv, head_dim=hd, qk_norm=True,
+                                  qk_norm_eps=1e-6, position={"kind": "toy_scale", "rate": 0.01})
+    att.attach(rt)
+    g = torch.Generator().manual_seed(6)
+    w = {n: torch.randn(s.shape, generator=g) * (0.2 if len(s.shape) == 2 else 1.0) for n, s in att.param_specs().items()}
+    att.bind({n: v.cuda() for n, v in w.items()})
+    cache = KVCache([ScheduleEntry(0)], [att.cache_request()], [None], 256, 2, 256, torch.float32, "cuda:0")
+    slot = cache.alloc_slot()
+    layout = MetaLayout(256, 2)
+    stager = MetaStager(layout, "cuda:0")
+    T = 70
+    x = torch.randn(T, H, generator=g)
+    res = torch.zeros(T, H, device="cuda")
+    for a, b in ((0, 50), (50, 70)):                       # two steps: the second reads what the first cached
+        arrays, t, r, _ = plan_step([StepEntry(slot, [0] * (b - a), [])], cache.lengths, 10, layout)
+        cache.reserve([(slot, b - a)])
+        stager.upload(arrays, t, r)
+        ctx = make_context(stager, arrays, t, r, rt.ws)
+        att.forward(x[a:b].cuda(), res[a:b], ctx, cache.ios[0])
+        cache.commit([(slot, b - a)])
+    pos = torch.arange(T)
+    q = P.head_rms_norm(P.linear(x, w["q_proj.weight"]).reshape(T, nq, hd), w["q_norm.weight"], 1e-6)
+    k = P.head_rms_norm(P.linear(x, w["k_proj.weight"]).reshape(T, nkv, hd), w["k_norm.weight"], 1e-6)
+    v = P.linear(x, w["v_proj.weight"]).reshape(T, nkv, hd)
+    f = (1.0 + 0.01 * pos.float())[:, None, None]
+    want = P.linear(P.causal_attention(q * f, k / f, v).reshape(T, nq * hd), w["o_proj.weight"])
+    torch.testing.assert_close(res.cpu(), want, atol=2e-5, rtol=1e-4)
