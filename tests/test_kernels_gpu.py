@@ -248,3 +248,49 @@ def test_attention_decode_kernel(K, nq, nkv, hd, window, len_bucket):
     close(got, want, dt, atol=3e-2, rtol=3e-2)
     vfar = pool[page, 1, nkv - 1, far % PAGE, :].float()
     assert (got[0, (nq - 1) * hd:].float().cpu() - vfar).abs().max() < 0.05 * vfar.abs().max() + 0.05
+
+
+class PrefillPlan:
+    """A step of several sequences with several new tokens each, as the engine's
+    StepContext describes it."""
+    is_decode = False
+
+    def __init__(self, slots, starts, news):
+        cu = [0]
+        for n in news:
+            cu.append(cu[-1] + n)
+        self.R, self.max_new = len(slots), max(news)
+        self.cu_seqlens = torch.tensor(cu, dtype=torch.int32).cuda()
+        self.seq_slot = torch.tensor(slots, dtype=torch.int32).cuda()
+        self.seq_start = torch.tensor(starts, dtype=torch.int32).cuda()
+        self.len_bucket = 1
+
+
+@pytest.mark.parametrize("nq,nkv,hd,window", [(4, 2, 16, 0), (6, 2, 48, 24), (5, 5, 80, 0), (8, 1, 128, 100),
+                                              (32, 8, 128, 0), (6, 3, 32, 70), (4, 1, 64, 64)])
+def test_attention_prefill_kernel(K, nq, nkv, hd, window):
+    """Tiles of query tokens over the paged cache: whole prompts, a chunk that
+    continues a cached prefix, a single token, tile and page edges; a far key
+    dominates one head of the last query of the first sequence."""
+    dt = torch.bfloat16
+    lens = [300, 5, 129, 64, 65]          # lengths after the step
+    news = [300, 5, 70, 1, 65]            # of which new in this step
+    pool, table, slots = make_paged(nkv, hd, lens, dt, 60, n_pages=40)
+    starts = [l - n for l, n in zip(lens, news)]
+    pos = torch.tensor([p for s, n in zip(starts, news) for p in range(s, s + n)], dtype=torch.int32)
+    slot = torch.tensor([sl for sl, n in zip(slots, news) for _ in range(n)], dtype=torch.int32)
+    T = pos.numel()
+    q = rnd((T, nq * hd), dt, 61)
+    scale = 1.0 / math.sqrt(hd)
+    far = 17 if window == 0 else 300 - window
+    page = int(table[slots[0], far // PAGE])
+    qh = q[299, (nq - 1) * hd:].float()
+    pool[page, 0, nkv - 1, far % PAGE, :] = (qh * (30.0 / (float(qh @ qh) * scale))).to(dt)
+    want = torch.empty(T, nq * hd, dtype=dt)
+    PlainKernels().attention(want, q, pool, table, pos, slot, nq, nkv, hd, scale, window)
+    got = torch.empty(T, nq * hd, dtype=dt, device="cuda")
+    K.attention(got, q.cuda(), pool.cuda(), table.cuda(), pos.cuda(), slot.cuda(), nq, nkv, hd, scale, window,
+                PrefillPlan(slots, starts, news))
+    close(got, want, dt, atol=3e-2, rtol=3e-2)
+    vfar = pool[page, 1, nkv - 1, far % PAGE, :].float()
+    assert (got[299, (nq - 1) * hd:].float().cpu() - vfar).abs().max() < 0.05 * vfar.abs().max() + 0.05

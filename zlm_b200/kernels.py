@@ -192,6 +192,16 @@ class CudaKernels:
                        c_int(nkv), c_int(hd), c_float(scale), c_int(window), c_int(splits),
                        c_void_p(_ptr(part_o)), c_void_p(_ptr(part_ml)), self._stream())
             return
+        if (plan is not None and not plan.is_decode and q.dtype == torch.bfloat16
+                and getattr(plan, "cu_seqlens", None) is not None
+                and self.lib.zlm_attention_prefill_supported(nq, nkv, hd)):
+            self._call("zlm_attention_prefill", c_void_p(out.data_ptr()), c_int(out.stride(0)),
+                       c_void_p(q.data_ptr()), c_int(q.stride(0)), c_void_p(pool.data_ptr()),
+                       c_void_p(block_table.data_ptr()), c_int(block_table.stride(0)),
+                       c_void_p(plan.cu_seqlens.data_ptr()), c_void_p(plan.seq_slot.data_ptr()),
+                       c_void_p(plan.seq_start.data_ptr()), c_int(plan.R), c_int(plan.max_new), c_int(nq),
+                       c_int(nkv), c_int(hd), c_float(scale), c_int(window), self._stream())
+            return
         self._call("zlm_attention_generic", c_void_p(out.data_ptr()), c_int(out.stride(0)),
                    c_void_p(q.data_ptr()), c_int(q.stride(0)), c_int(_dt(q)), c_void_p(pool.data_ptr()),
                    c_void_p(block_table.data_ptr()), c_int(block_table.stride(0)),
