@@ -294,3 +294,33 @@ def test_attention_prefill_kernel(K, nq, nkv, hd, window):
     close(got, want, dt, atol=3e-2, rtol=3e-2)
     vfar = pool[page, 1, nkv - 1, far % PAGE, :].float()
     assert (got[299, (nq - 1) * hd:].float().cpu() - vfar).abs().max() < 0.05 * vfar.abs().max() + 0.05
+
+
+@pytest.mark.parametrize("T,N,K_", [(128, 256, 64), (130, 300, 72), (200, 151, 1000), (128, 8, 64), (1, 40, 24),
+                                    (300, 1000, 520), (512, 768, 2048)])
+def test_linear_bf16_tcgen05(K, T, N, K_):
+    """The TMA + tcgen05 product at aligned and ragged shapes (tails in T, N and K are
+    zero-filled by the tensor maps), in all three output modes; no bounded wait gave up."""
+    x, w = rnd((T, K_), torch.bfloat16, 70), rnd((N, K_), torch.bfloat16, 71, 0.05)
+    want = x.double() @ w.double().t()
+    for out_dtype in (torch.bfloat16, torch.float32):
+        got = torch.full((T, N), 7.0, dtype=out_dtype, device="cuda")
+        K.linear(got, x.cuda(), w.cuda(), impl="tc")
+        close(got, want, out_dtype, atol=1e-3 if out_dtype == torch.float32 else 3e-2, rtol=1e-2)
+    base = rnd((T, N), torch.float32, 72)
+    acc = base.clone().cuda()
+    K.linear(acc, x.cuda(), w.cuda(), accumulate=True, impl="tc")
+    close(acc, base.double() + want, torch.float32, atol=1e-3, rtol=1e-3)
+    assert K.gemm_tc_status() == 0
+
+
+def test_linear_bf16_kernels_agree(K):
+    """The three bf16 products give the same numbers up to the order of their sums."""
+    x, w = rnd((16, 512), torch.bfloat16, 73), rnd((384, 512), torch.bfloat16, 74, 0.05)
+    outs = []
+    for impl in ("gemv", "mma", "tc"):
+        o = torch.empty(16, 384, dtype=torch.float32, device="cuda")
+        K.linear(o, x.cuda(), w.cuda(), impl=impl)
+        outs.append(o.cpu())
+    torch.testing.assert_close(outs[0], outs[1], atol=1e-4, rtol=1e-4)
+    torch.testing.assert_close(outs[0], outs[2], atol=1e-4, rtol=1e-4)

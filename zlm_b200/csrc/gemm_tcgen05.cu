@@ -1,0 +1,322 @@
+// bf16 matrix product Y[T,N] = X[T,K] . W[N,K]^T for prefill-sized T on the
+// 5th-generation tensor cores: operands staged in shared memory by TMA
+// (cp.async.bulk.tensor, 128-byte swizzle), products issued by one thread with
+// tcgen05.mma (128 x 256 x 16 per instruction), fp32 accumulators in tensor
+// memory, read back with tcgen05.ld for the epilogue.
+//
+// One block computes one 128 x 256 tile of Y.  Warp 0 is the TMA producer, warp 1
+// allocates tensor memory and issues the products, warps 2..5 are the epilogue.
+// A 4-stage ring of (X tile 128x64, W tile 256x64) is handed back and forth with
+// mbarriers: `full` is completed by the TMA's byte count, `empty` by
+// tcgen05.commit when the products that read a stage have retired.
+//
+// Every wait is bounded: a wait that does not come true sets an error word that
+// the host reads (zlm_gemm_tc_status) and makes every role leave its loop; the
+// block then waits, again bounded, for copies still in flight, frees its tensor
+// memory and returns.
+//
+// out_i = sum_j W[i,j] x_j with bf16 operands and fp32 accumulation
+// (src/kernels/linear/matvec/kernels/bfloat.zig:43-67; the reference's batched
+// product: src/kernels/linear/matmul/root.zig:62-81).
+#include "common.cuh"
+#include <cuda.h>
+
+#define TC_BM 128
+#define TC_BK 64
+#define TC_STAGES 4
+#define TC_THREADS 192
+#define TC_WAIT_LIMIT (1u << 24)
+
+__device__ int g_gemm_tc_error = 0;
+
+// ---------------------------------------------------------------- PTX wrappers
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint64_t* bar, unsigned parity) {
+    unsigned ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// bounded wait; false if it gave up (or another role already did)
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity, volatile int* abort_flag, int where) {
+    for (unsigned it = 0; it < TC_WAIT_LIMIT; ++it) {
+        if (mbar_try(bar, parity)) return true;
+        if (*abort_flag) return false;
+    }
+    *abort_flag = where;
+    atomicCAS(&g_gemm_tc_error, 0, where);
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_mma(unsigned tmem_d, uint64_t desc_a, uint64_t desc_b, unsigned idesc, unsigned accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tc_ld16(unsigned taddr, float* v) {
+    unsigned r[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// shared-memory operand descriptor: K-major tile whose rows are 128 bytes, 128-byte
+// swizzle; 8-row groups are 1024 bytes apart.  Fields in units of 16 bytes.
+__device__ __forceinline__ uint64_t make_desc(unsigned smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);     // start address
+    d |= (uint64_t)1 << 16;                          // leading byte offset (unused for this layout)
+    d |= (uint64_t)(1024 >> 4) << 32;                // stride byte offset: 8 rows x 128 bytes
+    d |= (uint64_t)1 << 46;                          // descriptor version of this architecture
+    d |= (uint64_t)2 << 61;                          // 128-byte swizzle
+    return d;
+}
+
+// MODE 0: Y bf16 = acc; MODE 1: Y fp32 += acc; MODE 2: Y fp32 = acc
+template <int BN, int MODE>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+               void* __restrict__ Y, int T, int N, int K, int ldy) {
+    constexpr unsigned A_BYTES = TC_BM * TC_BK * 2, B_BYTES = BN * TC_BK * 2;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    unsigned char* sA = smem;
+    unsigned char* sB = smem + TC_STAGES * A_BYTES;
+    uint64_t* full = (uint64_t*)(sB + TC_STAGES * B_BYTES);
+    uint64_t* empty = full + TC_STAGES;
+    uint64_t* acc_full = empty + TC_STAGES;
+    unsigned* tmem_slot = (unsigned*)(acc_full + 1);
+    volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = blockIdx.x * TC_BM, n0 = blockIdx.y * BN;
+    const int KB = (K + TC_BK - 1) / TC_BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < TC_STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        mbar_init(acc_full, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n"
+                     ::"r"(smem_u32(tmem_slot)), "r"((unsigned)BN) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const unsigned tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int issued = 0;
+            for (int kb = 0; kb < KB; ++kb) {
+                const int s = kb % TC_STAGES;
+                const unsigned round = kb / TC_STAGES;
+                if (!mbar_wait(&empty[s], (round & 1) ^ 1, abort_flag, 1)) break;
+                mbar_expect_tx(&full[s], A_BYTES + B_BYTES);
+                tma_load_2d(sA + s * A_BYTES, &map_x, kb * TC_BK, m0, &full[s]);
+                tma_load_2d(sB + s * B_BYTES, &map_w, kb * TC_BK, n0, &full[s]);
+                issued = kb + 1;
+            }
+            if (*abort_flag) {
+                // copies may still be landing in this block's shared memory: wait for them (bounded)
+                for (int kb = max(0, issued - TC_STAGES); kb < issued; ++kb)
+                    for (unsigned it = 0; it < TC_WAIT_LIMIT; ++it)
+                        if (mbar_try(&full[kb % TC_STAGES], (kb / TC_STAGES) & 1)) break;
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // instruction descriptor: fp32 accumulate, bf16 x bf16, both K-major, N = BN, M = 128
+            const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(BN >> 3) << 17) |
+                                   ((unsigned)(TC_BM >> 4) << 24);
+            bool ok = true;
+            for (int kb = 0; kb < KB && ok; ++kb) {
+                const int s = kb % TC_STAGES;
+                const unsigned round = kb / TC_STAGES;
+                ok = mbar_wait(&full[s], round & 1, abort_flag, 2);
+                if (!ok) break;
+                tc_fence_after();
+                const unsigned a0 = smem_u32(sA + s * A_BYTES), b0 = smem_u32(sB + s * B_BYTES);
+#pragma unroll
+                for (int k = 0; k < TC_BK / 16; ++k)
+                    tc_mma(tmem_base, make_desc(a0 + k * 32), make_desc(b0 + k * 32), idesc, (kb | k) != 0);
+                tc_commit(&empty[s]);          // the stage is free once these products have read it
+            }
+            tc_commit(acc_full);               // arrives when every product issued so far has retired
+        }
+    } else {
+        // epilogue: warp w may touch tensor-memory lanes 32 (w % 4) .. + 31; lane = row of the tile
+        const int lg = warp & 3;
+        const bool ok = mbar_wait(acc_full, 0, abort_flag, 3);
+        tc_fence_after();
+        const int row = m0 + lg * 32 + lane;
+        if (ok && !*abort_flag) {
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 16) {
+                float v[16];
+                tc_ld16(tmem_base + ((unsigned)(lg * 32) << 16) + (unsigned)c, v);     // warp-wide
+                const int n = n0 + c;
+                if (row >= T || n >= N) continue;
+                const size_t off = (size_t)row * ldy + n;
+                const bool whole = n + 16 <= N;
+                if (MODE == 0) {
+                    __nv_bfloat16* y = (__nv_bfloat16*)Y + off;
+                    if (whole && ((uintptr_t)y & 15) == 0) {
+                        uint4 p0, p1;
+                        __nv_bfloat162 t;
+#define ZLM_PK(a, b) (t = __floats2bfloat162_rn(a, b), *(unsigned*)&t)
+                        p0.x = ZLM_PK(v[0], v[1]); p0.y = ZLM_PK(v[2], v[3]); p0.z = ZLM_PK(v[4], v[5]); p0.w = ZLM_PK(v[6], v[7]);
+                        p1.x = ZLM_PK(v[8], v[9]); p1.y = ZLM_PK(v[10], v[11]); p1.z = ZLM_PK(v[12], v[13]); p1.w = ZLM_PK(v[14], v[15]);
+#undef ZLM_PK
+                        *(uint4*)y = p0;
+                        *(uint4*)(y + 8) = p1;
+                    } else {
+                        for (int i = 0; i < 16 && n + i < N; ++i) y[i] = __float2bfloat16_rn(v[i]);
+                    }
+                } else {
+                    float* y = (float*)Y + off;
+                    if (whole && ((uintptr_t)y & 15) == 0) {
+#pragma unroll
+                        for (int i = 0; i < 16; i += 4) {
+                            float4 o = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+                            if (MODE == 1) {
+                                const float4 old = *(const float4*)(y + i);
+                                o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+                            }
+                            *(float4*)(y + i) = o;
+                        }
+                    } else {
+                        for (int i = 0; i < 16 && n + i < N; ++i) y[i] = MODE == 1 ? y[i] + v[i] : v[i];
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"((unsigned)BN) : "memory");
+    }
+}
+
+// ---------------------------------------------------------------- host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode() {
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+
+// rows x K bf16 matrix, row stride ld elements; box = box_rows x 64 elements, 128-byte swizzle, zero fill
+static int make_map(CUtensorMap* m, const void* ptr, int rows, int K, int ld, int box_rows) {
+    EncodeTiledFn enc = get_encode();
+    if (!enc) {
+        zlm_set_error("gemm_tc: the driver does not provide cuTensorMapEncodeTiled");
+        return ZLM_ERR_CUDA;
+    }
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {TC_BK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void*)ptr, dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) {
+        zlm_set_error("gemm_tc: cuTensorMapEncodeTiled failed with %d (rows=%d K=%d ld=%d)", (int)r, rows, K, ld);
+        return ZLM_ERR_CUDA;
+    }
+    return ZLM_OK;
+}
+
+template <int BN>
+static int launch_tc(void* Y, const void* X, const void* W, int T, int N, int K, int ldx, int ldy, int mode,
+                     cudaStream_t st) {
+    CUtensorMap mx, mw;
+    int rc = make_map(&mx, X, T, K, ldx, TC_BM);
+    if (rc) return rc;
+    rc = make_map(&mw, W, N, K, K, BN);
+    if (rc) return rc;
+    const size_t smem = (size_t)TC_STAGES * (TC_BM + BN) * TC_BK * 2 + 1024 + 256;
+    dim3 grid((T + TC_BM - 1) / TC_BM, (N + BN - 1) / BN);
+    ZLM_REQUIRE(grid.y <= 65535, "gemm_tc: N=%d is too large", N);
+#define ZLM_TC_LAUNCH(M)                                                                                   \
+    {                                                                                                      \
+        auto kern = gemm_tc_kernel<BN, M>;                                                                 \
+        static bool attr_set = false;                                                                      \
+        if (!attr_set) {                                                                                   \
+            cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            if (e != cudaSuccess) {                                                                        \
+                zlm_set_error("gemm_tc: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e)); \
+                return ZLM_ERR_CUDA;                                                                       \
+            }                                                                                              \
+            attr_set = true;                                                                               \
+        }                                                                                                  \
+        kern<<<grid, TC_THREADS, smem, st>>>(mx, mw, Y, T, N, K, ldy);                                     \
+    }
+    if (mode == 0) ZLM_TC_LAUNCH(0)
+    else if (mode == 1) ZLM_TC_LAUNCH(1)
+    else ZLM_TC_LAUNCH(2)
+#undef ZLM_TC_LAUNCH
+    return zlm_check_launch("gemm_tc");
+}
+
+// 1 if the tensor-memory kernel takes this product (else use zlm_gemm_bf16_mma)
+extern "C" int zlm_gemm_tc_supported(int T, int N, int K, int ldx) {
+    return (T >= 1 && N >= 8 && K >= 8 && K % 8 == 0 && ldx % 8 == 0) ? 1 : 0;
+}
+
+// mode 0: Y bf16 = X W^T; mode 1: Y fp32 += X W^T; mode 2: Y fp32 = X W^T
+extern "C" int zlm_gemm_tc(void* Y, const void* X, const void* W, int T, int N, int K, int ldx, int ldy, int mode,
+                           cudaStream_t st) {
+    if (T == 0 || N == 0) return ZLM_OK;
+    ZLM_REQUIRE(zlm_gemm_tc_supported(T, N, K, ldx), "gemm_tc: shape T=%d N=%d K=%d (row stride %d) is not taken", T, N, K, ldx);
+    ZLM_REQUIRE(((uintptr_t)X % 16 == 0) && ((uintptr_t)W % 16 == 0), "gemm_tc: operands must be 16-byte aligned");
+    ZLM_REQUIRE(mode >= 0 && mode <= 2, "gemm_tc: mode %d", mode);
+    return launch_tc<256>(Y, X, W, T, N, K, ldx, ldy, mode, st);
+}
+
+// 0 if no bounded wait of the kernel ever gave up; else 1 (producer), 2 (product issuer) or 3 (epilogue).
+// Synchronises the device.
+extern "C" int zlm_gemm_tc_status() {
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, g_gemm_tc_error, sizeof(int)) != cudaSuccess) return -1;
+    return v;
+}

@@ -111,9 +111,13 @@ class CudaKernels:
         self._call("zlm_swiglu", c_void_p(out.data_ptr()), c_void_p(gu.data_ptr()), c_int(_dt(out)),
                    c_int(T), c_int(I), self._stream())
 
-    def linear(self, out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, accumulate: bool = False) -> None:
+    def linear(self, out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, accumulate: bool = False,
+               impl: Optional[str] = None) -> None:
         """out = x @ w.T (out in x's dtype, or fp32), or out += x @ w.T into the fp32
-        residual stream when ``accumulate``.  w is [N, K] row-major."""
+        residual stream when ``accumulate``.  w is [N, K] row-major.  bf16 products pick
+        their kernel by the number of tokens: "gemv" (register-fragment streaming, up to
+        16), "tc" (TMA + tcgen05, 128 and more), "mma" (mma.sync, everything else);
+        ``impl`` forces one (tests)."""
         T, K = x.shape
         N = w.shape[0]
         assert w.shape[1] == K and out.shape == (T, N) and w.dtype == x.dtype
@@ -132,7 +136,9 @@ class CudaKernels:
         mode = ACCUM if accumulate else (STORE_F32 if out.dtype == torch.float32 else STORE)
         if mode == STORE:
             assert out.dtype == torch.bfloat16
-        name = "zlm_gemv_bf16" if T <= 16 else "zlm_gemm_bf16_mma"
+        if impl is None:
+            impl = "gemv" if T <= 16 else ("tc" if T >= 128 and self.lib.zlm_gemm_tc_supported(T, N, K, ldx) else "mma")
+        name = {"gemv": "zlm_gemv_bf16", "mma": "zlm_gemm_bf16_mma", "tc": "zlm_gemm_tc"}[impl]
         self._call(name, c_void_p(out.data_ptr()), c_void_p(x.data_ptr()), c_void_p(w.data_ptr()),
                    c_int(T), c_int(N), c_int(K), c_int(ldx), c_int(ldy), c_int(mode), self._stream())
 
@@ -214,6 +220,10 @@ class CudaKernels:
         assert logits.dtype == torch.float32 and logits.stride(1) == 1 and out.dtype == torch.int32
         self._call("zlm_argmax", c_void_p(out.data_ptr()), c_void_p(logits.data_ptr()), c_int(R), c_int(V),
                    c_int(logits.stride(0)), self._stream())
+
+    def gemm_tc_status(self) -> int:
+        """0 unless a bounded wait inside the tcgen05 GEMM ever gave up (synchronises)."""
+        return int(self.lib.zlm_gemm_tc_status())
 
     def sample(self, out: torch.Tensor, logits: torch.Tensor, temperature: float, top_k: int, top_p: float,
                seed: int, request: torch.Tensor, position: torch.Tensor) -> None:
