@@ -324,3 +324,42 @@ def test_linear_bf16_kernels_agree(K):
         outs.append(o.cpu())
     torch.testing.assert_close(outs[0], outs[1], atol=1e-4, rtol=1e-4)
     torch.testing.assert_close(outs[0], outs[2], atol=1e-4, rtol=1e-4)
+
+
+@pytest.mark.parametrize("T", [1, 3, 8, 16, 17, 40, 64, 100, 128, 300, 500])
+@pytest.mark.parametrize("I,K_", [(64, 40), (200, 1000), (1536, 512)])
+def test_linear_swiglu_fused(K, T, I, K_):
+    """silu(x . gate) * (x . up) in the product's epilogue, for every kernel that has
+    the epilogue, against the plain formula on the same bf16 inputs."""
+    from zlm_b200.kernels import interleave_gate_up
+    x = rnd((T, K_), torch.bfloat16, 80)
+    gate, up = rnd((I, K_), torch.bfloat16, 81, 0.08), rnd((I, K_), torch.bfloat16, 82, 0.08)
+    g, u = x.double() @ gate.double().t(), x.double() @ up.double().t()
+    want = (g / (1 + torch.exp(-g))) * u
+    w = interleave_gate_up(gate.cuda(), up.cuda())
+    assert torch.equal(w[:8].cpu(), gate[:8]) and torch.equal(w[8:16].cpu(), up[:8]) and torch.equal(w[16:24].cpu(), gate[8:16])
+    impls = [None, "tc", "mma"] + (["gemv"] if T <= 16 else [])
+    for impl in impls:
+        got = torch.full((T, I), 7.0, dtype=torch.bfloat16, device="cuda")
+        K.linear_swiglu(got, x.cuda(), w, impl=impl)
+        close(got, want, torch.bfloat16, atol=3e-2, rtol=3e-2)
+    assert K.gemm_tc_status() == 0
+
+
+@pytest.mark.parametrize("T", [17, 33, 64, 65, 129, 384, 385])
+def test_linear_bf16_tcgen05_few_tokens(K, T):
+    """The swapped-operand form (W is the 128-row operand) for decode-sized batches."""
+    N, K_ = 712, 520
+    x, w = rnd((T, K_), torch.bfloat16, 83), rnd((N, K_), torch.bfloat16, 84, 0.05)
+    want = x.double() @ w.double().t()
+    got = torch.full((T, N), 7.0, dtype=torch.bfloat16, device="cuda")
+    K.linear(got, x.cuda(), w.cuda(), impl="tc")
+    close(got, want, torch.bfloat16, atol=3e-2, rtol=1e-2)
+    base = rnd((T, N), torch.float32, 85)
+    acc = base.clone().cuda()
+    K.linear(acc, x.cuda(), w.cuda(), accumulate=True, impl="tc")
+    close(acc, base.double() + want, torch.float32, atol=1e-3, rtol=1e-3)
+    lg = torch.empty((T, N), dtype=torch.float32, device="cuda")
+    K.linear(lg, x.cuda(), w.cuda(), impl="tc")
+    close(lg, want, torch.float32, atol=1e-3, rtol=1e-3)
+    assert K.gemm_tc_status() == 0

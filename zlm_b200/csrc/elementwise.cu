@@ -126,9 +126,12 @@ extern "C" int zlm_rmsnorm(void* out, int out_dtype, const float* x, const void*
     ZLM_REQUIRE(R > 0 && H > 0, "rmsnorm: bad sizes R=%d H=%d", R, H);
     ZLM_REQUIRE(w_dtype == ZLM_DTYPE_F32 || w_dtype == ZLM_DTYPE_BF16, "rmsnorm: weight dtype %d", w_dtype);
     VecW vw{w, w_dtype};
-    // a function of H only: the order of the sum must not depend on the batch
+    // 32-bit output (the 32-bit path): a function of H only, so that the order of the sum
+    // never depends on the batch.  bf16 output: rows of a long step share an SM better
+    // with 256 threads each; the difference is in the last bit of the sum.
     int threads = 128;
     while (threads < 1024 && threads * 4 < H) threads *= 2;
+    if (out_dtype == ZLM_DTYPE_BF16 && R >= 512 && H % 4 == 0 && H <= 256 * 4 * NORM_MAX_V4 && threads > 256) threads = 256;
     if (out_dtype == ZLM_DTYPE_F32)
         rmsnorm_kernel<float><<<R, threads, 0, st>>>((float*)out, x, vw, rows, H, eps);
     else if (out_dtype == ZLM_DTYPE_BF16)

@@ -41,7 +41,7 @@ template <int MODE>
 __device__ __forceinline__ void store_out(void* Y, size_t idx, float v) {
     if (MODE == 0) ((__nv_bfloat16*)Y)[idx] = __float2bfloat16_rn(v);
     else if (MODE == 1) ((float*)Y)[idx] += v;
-    else ((float*)Y)[idx] = v;
+    else if (MODE == 2) ((float*)Y)[idx] = v;
 }
 
 template <int BM, int BN, int WARPS_M, int WARPS_N, int MODE>
@@ -126,6 +126,28 @@ gemm_bf16_mma_kernel(void* __restrict__ Y, const __nv_bfloat16* __restrict__ X,
     cp_async_wait<0>();
 
     const int g = lane >> 2, q = lane & 3;
+    if (MODE == 3) {
+        // n-tiles come in pairs: 8 gate channels, then the 8 matching up channels
+#pragma unroll
+        for (int i = 0; i < MT; ++i)
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {
+                const int m = m0 + wm * WM + i * 16 + g + half * 8;
+                if (m >= T) continue;
+#pragma unroll
+                for (int j = 0; j < NT; j += 2) {
+                    const int n = n0 + wn * WN + j * 8;              // first gate channel of the pair of tiles
+                    if (n + 16 > N) continue;
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        const float gt = acc[i][j][half * 2 + e], up = acc[i][j + 1][half * 2 + e];
+                        ((__nv_bfloat16*)Y)[(size_t)m * ldy + n / 2 + q * 2 + e] =
+                            __float2bfloat16_rn((gt / (1.0f + expf(-gt))) * up);
+                    }
+                }
+            }
+        return;
+    }
 #pragma unroll
     for (int i = 0; i < MT; ++i) {
 #pragma unroll
@@ -166,12 +188,14 @@ static int launch_mma(void* Y, const __nv_bfloat16* X, const __nv_bfloat16* W, i
     }
     if (mode == 0) ZLM_LAUNCH_MODE(0)
     else if (mode == 1) ZLM_LAUNCH_MODE(1)
-    else ZLM_LAUNCH_MODE(2)
+    else if (mode == 2) ZLM_LAUNCH_MODE(2)
+    else ZLM_LAUNCH_MODE(3)
 #undef ZLM_LAUNCH_MODE
     return zlm_check_launch("gemm_bf16_mma");
 }
 
-// mode 0: Y bf16 = X W^T; mode 1: Y fp32 += X W^T; mode 2: Y fp32 = X W^T
+// mode 0: Y bf16 = X W^T; mode 1: Y fp32 += X W^T; mode 2: Y fp32 = X W^T;
+// mode 3: Y bf16 [T, N/2] = silu(gate) * up with W's rows in groups of 8 gate + 8 up
 extern "C" int zlm_gemm_bf16_mma(void* Y, const void* X, const void* W, int T, int N, int K, int ldx,
                                  int ldy, int mode, cudaStream_t st) {
     if (T == 0 || N == 0) return ZLM_OK;
@@ -179,7 +203,8 @@ extern "C" int zlm_gemm_bf16_mma(void* Y, const void* X, const void* W, int T, i
     ZLM_REQUIRE(K % 8 == 0 && ldx % 8 == 0,
                 "gemm_bf16: the inner size K=%d (row stride %d) must be a multiple of 8 for bf16 kernels", K, ldx);
     ZLM_REQUIRE(((uintptr_t)X % 16 == 0) && ((uintptr_t)W % 16 == 0), "gemm_bf16: operands must be 16-byte aligned");
-    ZLM_REQUIRE(mode >= 0 && mode <= 2, "gemm_bf16: mode %d", mode);
+    ZLM_REQUIRE(mode >= 0 && mode <= 3, "gemm_bf16: mode %d", mode);
+    ZLM_REQUIRE(mode != 3 || N % 16 == 0, "gemm_bf16: the fused gate/up product needs N=%d to be a multiple of 16", N);
     const __nv_bfloat16* x = (const __nv_bfloat16*)X;
     const __nv_bfloat16* w = (const __nv_bfloat16*)W;
     if (T > 64) return launch_mma<128, 128, 2, 4>(Y, x, w, T, N, K, ldx, ldy, mode, st);

@@ -4,11 +4,15 @@
 // tcgen05.mma (128 x 256 x 16 per instruction), fp32 accumulators in tensor
 // memory, read back with tcgen05.ld for the epilogue.
 //
-// One block computes one 128 x 256 tile of Y.  Warp 0 is the TMA producer, warp 1
-// allocates tensor memory and issues the products, warps 2..5 are the epilogue.
-// A 4-stage ring of (X tile 128x64, W tile 256x64) is handed back and forth with
-// mbarriers: `full` is completed by the TMA's byte count, `empty` by
-// tcgen05.commit when the products that read a stage have retired.
+// One block computes one tile of Y.  For many tokens the 128 rows of the product's
+// first operand are tokens and its up to 256 columns are outputs; for few tokens
+// (decode batches of 17 to a few hundred) the operands swap places: 128 rows of W
+// against a tile of 32, 64 or 128 tokens, so that W, which is what the step has to
+// read, still streams through full-height products.  Warp 0 is the TMA producer,
+// warp 1 allocates tensor memory and issues the products, warps 2..5 are the
+// epilogue.  A ring of (first-operand tile 128x64, second-operand tile BNx64) is
+// handed back and forth with mbarriers: `full` is completed by the TMA's byte
+// count, `empty` by tcgen05.commit when the products that read a stage have retired.
 //
 // Every wait is bounded: a wait that does not come true sets an error word that
 // the host reads (zlm_gemm_tc_status) and makes every role leave its loop; the
@@ -23,7 +27,6 @@
 
 #define TC_BM 128
 #define TC_BK 64
-#define TC_STAGES 4
 #define TC_THREADS 192
 #define TC_WAIT_LIMIT (1u << 24)
 
@@ -95,28 +98,32 @@ __device__ __forceinline__ uint64_t make_desc(unsigned smem_addr) {
     return d;
 }
 
-// MODE 0: Y bf16 = acc; MODE 1: Y fp32 += acc; MODE 2: Y fp32 = acc
-template <int BN, int MODE>
+__device__ __forceinline__ float silu_mul(float g, float u) { return (g / (1.0f + expf(-g))) * u; }
+
+// MODE 0: Y bf16 = acc; MODE 1: Y fp32 += acc; MODE 2: Y fp32 = acc;
+// MODE 3: the outputs come in groups of 16 = 8 gate + 8 up channels; Y bf16 [T, N/2] = silu(gate) * up.
+// SWAP false: first operand = X (rows are tokens), second = W; true: first = W, second = X.
+template <int BN, int STAGES, bool SWAP, int MODE>
 __global__ void __launch_bounds__(TC_THREADS, 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                void* __restrict__ Y, int T, int N, int K, int ldy) {
     constexpr unsigned A_BYTES = TC_BM * TC_BK * 2, B_BYTES = BN * TC_BK * 2;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     unsigned char* sA = smem;
-    unsigned char* sB = smem + TC_STAGES * A_BYTES;
-    uint64_t* full = (uint64_t*)(sB + TC_STAGES * B_BYTES);
-    uint64_t* empty = full + TC_STAGES;
-    uint64_t* acc_full = empty + TC_STAGES;
+    unsigned char* sB = smem + STAGES * A_BYTES;
+    uint64_t* full = (uint64_t*)(sB + STAGES * B_BYTES);
+    uint64_t* empty = full + STAGES;
+    uint64_t* acc_full = empty + STAGES;
     unsigned* tmem_slot = (unsigned*)(acc_full + 1);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.x * TC_BM, n0 = blockIdx.y * BN;
+    const int a0row = blockIdx.x * TC_BM, b0row = blockIdx.y * BN;
     const int KB = (K + TC_BK - 1) / TC_BK;
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < TC_STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
         mbar_init(acc_full, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
@@ -135,19 +142,19 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
         if (lane == 0) {
             int issued = 0;
             for (int kb = 0; kb < KB; ++kb) {
-                const int s = kb % TC_STAGES;
-                const unsigned round = kb / TC_STAGES;
+                const int s = kb % STAGES;
+                const unsigned round = kb / STAGES;
                 if (!mbar_wait(&empty[s], (round & 1) ^ 1, abort_flag, 1)) break;
                 mbar_expect_tx(&full[s], A_BYTES + B_BYTES);
-                tma_load_2d(sA + s * A_BYTES, &map_x, kb * TC_BK, m0, &full[s]);
-                tma_load_2d(sB + s * B_BYTES, &map_w, kb * TC_BK, n0, &full[s]);
+                tma_load_2d(sA + s * A_BYTES, &map_a, kb * TC_BK, a0row, &full[s]);
+                tma_load_2d(sB + s * B_BYTES, &map_b, kb * TC_BK, b0row, &full[s]);
                 issued = kb + 1;
             }
             if (*abort_flag) {
                 // copies may still be landing in this block's shared memory: wait for them (bounded)
-                for (int kb = max(0, issued - TC_STAGES); kb < issued; ++kb)
+                for (int kb = max(0, issued - STAGES); kb < issued; ++kb)
                     for (unsigned it = 0; it < TC_WAIT_LIMIT; ++it)
-                        if (mbar_try(&full[kb % TC_STAGES], (kb / TC_STAGES) & 1)) break;
+                        if (mbar_try(&full[kb % STAGES], (kb / STAGES) & 1)) break;
             }
         }
     } else if (warp == 1) {
@@ -157,8 +164,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
                                    ((unsigned)(TC_BM >> 4) << 24);
             bool ok = true;
             for (int kb = 0; kb < KB && ok; ++kb) {
-                const int s = kb % TC_STAGES;
-                const unsigned round = kb / TC_STAGES;
+                const int s = kb % STAGES;
+                const unsigned round = kb / STAGES;
                 ok = mbar_wait(&full[s], round & 1, abort_flag, 2);
                 if (!ok) break;
                 tc_fence_after();
@@ -171,48 +178,88 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
             tc_commit(acc_full);               // arrives when every product issued so far has retired
         }
     } else {
-        // epilogue: warp w may touch tensor-memory lanes 32 (w % 4) .. + 31; lane = row of the tile
+        // epilogue: warp w may touch tensor-memory lanes 32 (w % 4) .. + 31; a lane is a row of the tile
         const int lg = warp & 3;
         const bool ok = mbar_wait(acc_full, 0, abort_flag, 3);
         tc_fence_after();
-        const int row = m0 + lg * 32 + lane;
+        const int arow = a0row + lg * 32 + lane;
         if (ok && !*abort_flag) {
 #pragma unroll 1
             for (int c = 0; c < BN; c += 16) {
                 float v[16];
                 tc_ld16(tmem_base + ((unsigned)(lg * 32) << 16) + (unsigned)c, v);     // warp-wide
-                const int n = n0 + c;
-                if (row >= T || n >= N) continue;
-                const size_t off = (size_t)row * ldy + n;
-                const bool whole = n + 16 <= N;
-                if (MODE == 0) {
-                    __nv_bfloat16* y = (__nv_bfloat16*)Y + off;
-                    if (whole && ((uintptr_t)y & 15) == 0) {
-                        uint4 p0, p1;
-                        __nv_bfloat162 t;
+                if (!SWAP) {
+                    // this thread: token arow, outputs b0row + c .. + 15
+                    const int n = b0row + c;
+                    if (arow >= T || n >= N) continue;
+                    const bool whole = n + 16 <= N;
+                    if (MODE == 3) {
+                        __nv_bfloat16* y = (__nv_bfloat16*)Y + (size_t)arow * ldy + n / 2;
+                        if (whole && ((uintptr_t)y & 15) == 0) {
+                            uint4 p;
+                            __nv_bfloat162 t;
 #define ZLM_PK(a, b) (t = __floats2bfloat162_rn(a, b), *(unsigned*)&t)
-                        p0.x = ZLM_PK(v[0], v[1]); p0.y = ZLM_PK(v[2], v[3]); p0.z = ZLM_PK(v[4], v[5]); p0.w = ZLM_PK(v[6], v[7]);
-                        p1.x = ZLM_PK(v[8], v[9]); p1.y = ZLM_PK(v[10], v[11]); p1.z = ZLM_PK(v[12], v[13]); p1.w = ZLM_PK(v[14], v[15]);
+                            p.x = ZLM_PK(silu_mul(v[0], v[8]), silu_mul(v[1], v[9]));
+                            p.y = ZLM_PK(silu_mul(v[2], v[10]), silu_mul(v[3], v[11]));
+                            p.z = ZLM_PK(silu_mul(v[4], v[12]), silu_mul(v[5], v[13]));
+                            p.w = ZLM_PK(silu_mul(v[6], v[14]), silu_mul(v[7], v[15]));
+                            *(uint4*)y = p;
+                        } else if (whole) {
+                            for (int i = 0; i < 8; ++i) y[i] = __float2bfloat16_rn(silu_mul(v[i], v[8 + i]));
+                        }
+                    } else if (MODE == 0) {
+                        __nv_bfloat16* y = (__nv_bfloat16*)Y + (size_t)arow * ldy + n;
+                        if (whole && ((uintptr_t)y & 15) == 0) {
+                            uint4 p0, p1;
+                            __nv_bfloat162 t;
+                            p0.x = ZLM_PK(v[0], v[1]); p0.y = ZLM_PK(v[2], v[3]); p0.z = ZLM_PK(v[4], v[5]); p0.w = ZLM_PK(v[6], v[7]);
+                            p1.x = ZLM_PK(v[8], v[9]); p1.y = ZLM_PK(v[10], v[11]); p1.z = ZLM_PK(v[12], v[13]); p1.w = ZLM_PK(v[14], v[15]);
 #undef ZLM_PK
-                        *(uint4*)y = p0;
-                        *(uint4*)(y + 8) = p1;
-                    } else {
-                        for (int i = 0; i < 16 && n + i < N; ++i) y[i] = __float2bfloat16_rn(v[i]);
-                    }
-                } else {
-                    float* y = (float*)Y + off;
-                    if (whole && ((uintptr_t)y & 15) == 0) {
-#pragma unroll
-                        for (int i = 0; i < 16; i += 4) {
-                            float4 o = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
-                            if (MODE == 1) {
-                                const float4 old = *(const float4*)(y + i);
-                                o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
-                            }
-                            *(float4*)(y + i) = o;
+                            *(uint4*)y = p0;
+                            *(uint4*)(y + 8) = p1;
+                        } else {
+                            for (int i = 0; i < 16 && n + i < N; ++i) y[i] = __float2bfloat16_rn(v[i]);
                         }
                     } else {
-                        for (int i = 0; i < 16 && n + i < N; ++i) y[i] = MODE == 1 ? y[i] + v[i] : v[i];
+                        float* y = (float*)Y + (size_t)arow * ldy + n;
+                        if (whole && ((uintptr_t)y & 15) == 0) {
+#pragma unroll
+                            for (int i = 0; i < 16; i += 4) {
+                                float4 o = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+                                if (MODE == 1) {
+                                    const float4 old = *(const float4*)(y + i);
+                                    o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+                                }
+                                *(float4*)(y + i) = o;
+                            }
+                        } else {
+                            for (int i = 0; i < 16 && n + i < N; ++i) y[i] = MODE == 1 ? y[i] + v[i] : v[i];
+                        }
+                    }
+                } else {
+                    // this thread: output arow, tokens b0row + c .. + 15; a warp's lanes are 32
+                    // neighbouring outputs, so every token's store is one coalesced line
+                    const int t0 = b0row + c;
+                    if (MODE == 3) {
+                        // lanes 0-7 and 16-23 hold gate channels, lanes 8-15 and 24-31 the matching up
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            const float u = __shfl_down_sync(0xffffffffu, v[i], 8);
+                            if ((lane & 8) == 0 && arow + 8 < N + 8 && arow < N && t0 + i < T) {
+                                const int ch = (arow >> 4) * 8 + (arow & 7);
+                                ((__nv_bfloat16*)Y)[(size_t)(t0 + i) * ldy + ch] = __float2bfloat16_rn(silu_mul(v[i], u));
+                            }
+                        }
+                    } else {
+                        if (arow >= N) continue;
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            if (t0 + i >= T) break;
+                            const size_t off = (size_t)(t0 + i) * ldy + arow;
+                            if (MODE == 0) ((__nv_bfloat16*)Y)[off] = __float2bfloat16_rn(v[i]);
+                            else if (MODE == 1) ((float*)Y)[off] += v[i];
+                            else ((float*)Y)[off] = v[i];
+                        }
                     }
                 }
             }
@@ -221,6 +268,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant_
     tc_fence_before();
     __syncthreads();
     if (warp == 1) {
+        __syncwarp();
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"((unsigned)BN) : "memory");
     }
@@ -266,20 +314,20 @@ static int make_map(CUtensorMap* m, const void* ptr, int rows, int K, int ld, in
     return ZLM_OK;
 }
 
-template <int BN>
+template <int BN, int STAGES, bool SWAP>
 static int launch_tc(void* Y, const void* X, const void* W, int T, int N, int K, int ldx, int ldy, int mode,
                      cudaStream_t st) {
     CUtensorMap mx, mw;
-    int rc = make_map(&mx, X, T, K, ldx, TC_BM);
+    int rc = make_map(&mx, X, T, K, ldx, SWAP ? BN : TC_BM);
     if (rc) return rc;
-    rc = make_map(&mw, W, N, K, K, BN);
+    rc = make_map(&mw, W, N, K, K, SWAP ? TC_BM : BN);
     if (rc) return rc;
-    const size_t smem = (size_t)TC_STAGES * (TC_BM + BN) * TC_BK * 2 + 1024 + 256;
-    dim3 grid((T + TC_BM - 1) / TC_BM, (N + BN - 1) / BN);
-    ZLM_REQUIRE(grid.y <= 65535, "gemm_tc: N=%d is too large", N);
+    const size_t smem = (size_t)STAGES * (TC_BM + BN) * TC_BK * 2 + 1024 + 256;
+    dim3 grid(SWAP ? (N + TC_BM - 1) / TC_BM : (T + TC_BM - 1) / TC_BM, SWAP ? (T + BN - 1) / BN : (N + BN - 1) / BN);
+    ZLM_REQUIRE(grid.y <= 65535, "gemm_tc: the product is too large (T=%d N=%d)", T, N);
 #define ZLM_TC_LAUNCH(M)                                                                                   \
     {                                                                                                      \
-        auto kern = gemm_tc_kernel<BN, M>;                                                                 \
+        auto kern = gemm_tc_kernel<BN, STAGES, SWAP, M>;                                                   \
         static bool attr_set = false;                                                                      \
         if (!attr_set) {                                                                                   \
             cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
@@ -289,11 +337,13 @@ static int launch_tc(void* Y, const void* X, const void* W, int T, int N, int K,
             }                                                                                              \
             attr_set = true;                                                                               \
         }                                                                                                  \
-        kern<<<grid, TC_THREADS, smem, st>>>(mx, mw, Y, T, N, K, ldy);                                     \
+        if (SWAP) kern<<<grid, TC_THREADS, smem, st>>>(mw, mx, Y, T, N, K, ldy);                           \
+        else kern<<<grid, TC_THREADS, smem, st>>>(mx, mw, Y, T, N, K, ldy);                                \
     }
     if (mode == 0) ZLM_TC_LAUNCH(0)
     else if (mode == 1) ZLM_TC_LAUNCH(1)
-    else ZLM_TC_LAUNCH(2)
+    else if (mode == 2) ZLM_TC_LAUNCH(2)
+    else ZLM_TC_LAUNCH(3)
 #undef ZLM_TC_LAUNCH
     return zlm_check_launch("gemm_tc");
 }
@@ -303,14 +353,20 @@ extern "C" int zlm_gemm_tc_supported(int T, int N, int K, int ldx) {
     return (T >= 1 && N >= 8 && K >= 8 && K % 8 == 0 && ldx % 8 == 0) ? 1 : 0;
 }
 
-// mode 0: Y bf16 = X W^T; mode 1: Y fp32 += X W^T; mode 2: Y fp32 = X W^T
+// mode 0: Y bf16 = X W^T; mode 1: Y fp32 += X W^T; mode 2: Y fp32 = X W^T;
+// mode 3: Y bf16 [T, N/2] = silu(gate) * up, W's rows in groups of 8 gate + 8 up (N a multiple of 16)
 extern "C" int zlm_gemm_tc(void* Y, const void* X, const void* W, int T, int N, int K, int ldx, int ldy, int mode,
                            cudaStream_t st) {
     if (T == 0 || N == 0) return ZLM_OK;
     ZLM_REQUIRE(zlm_gemm_tc_supported(T, N, K, ldx), "gemm_tc: shape T=%d N=%d K=%d (row stride %d) is not taken", T, N, K, ldx);
     ZLM_REQUIRE(((uintptr_t)X % 16 == 0) && ((uintptr_t)W % 16 == 0), "gemm_tc: operands must be 16-byte aligned");
-    ZLM_REQUIRE(mode >= 0 && mode <= 2, "gemm_tc: mode %d", mode);
-    return launch_tc<256>(Y, X, W, T, N, K, ldx, ldy, mode, st);
+    ZLM_REQUIRE(mode >= 0 && mode <= 3, "gemm_tc: mode %d", mode);
+    ZLM_REQUIRE(mode != 3 || N % 16 == 0, "gemm_tc: the fused gate/up product needs N=%d to be a multiple of 16", N);
+    // few tokens: W is the 128-row operand so that it streams at full height
+    if (T <= 32) return launch_tc<32, 8, true>(Y, X, W, T, N, K, ldx, ldy, mode, st);
+    if (T <= 64) return launch_tc<64, 8, true>(Y, X, W, T, N, K, ldx, ldy, mode, st);
+    if (T <= 384) return launch_tc<128, 6, true>(Y, X, W, T, N, K, ldx, ldy, mode, st);
+    return launch_tc<256, 4, false>(Y, X, W, T, N, K, ldx, ldy, mode, st);
 }
 
 // 0 if no bounded wait of the kernel ever gave up; else 1 (producer), 2 (product issuer) or 3 (epilogue).

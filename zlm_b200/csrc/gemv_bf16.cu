@@ -36,7 +36,8 @@ __device__ __forceinline__ void gemv_mma(float* c, unsigned a0, unsigned a1, uns
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-// MODE 0: Y bf16 = acc; MODE 1: Y fp32 += acc; MODE 2: Y fp32 = acc.  NT: token tiles of 8.
+// MODE 0: Y bf16 = acc; MODE 1: Y fp32 += acc; MODE 2: Y fp32 = acc; MODE 3: the block's 16 rows are
+// 8 gate + 8 up channels, Y bf16 [T, N/2] = silu(gate) * up.  NT: token tiles of 8.
 template <int NT, int MODE>
 __global__ void __launch_bounds__(GEMV_THREADS)
 gemv_bf16_kernel(void* __restrict__ Y, const __nv_bfloat16* __restrict__ X,
@@ -105,6 +106,21 @@ gemv_bf16_kernel(void* __restrict__ Y, const __nv_bfloat16* __restrict__ X,
         red[warp][j][g + 8][2 * q + 1] = acc[j][3];
     }
     __syncthreads();
+    if (MODE == 3) {
+        for (int idx = tid; idx < NT * 8 * 8; idx += GEMV_THREADS) {
+            const int j = idx / 64, rem = idx % 64;
+            const int tok = j * 8 + rem / 8, row = rem % 8;
+            if (tok >= T || n0 + row + 8 >= N) continue;
+            float sg = 0.f, su = 0.f;
+#pragma unroll
+            for (int w = 0; w < GEMV_WARPS; ++w) {
+                sg += red[w][j][row][tok & 7];
+                su += red[w][j][row + 8][tok & 7];
+            }
+            ((__nv_bfloat16*)Y)[(size_t)tok * ldy + n0 / 2 + row] = __float2bfloat16_rn((sg / (1.0f + expf(-sg))) * su);
+        }
+        return;
+    }
     for (int idx = tid; idx < NT * GEMV_ROWS * 8; idx += GEMV_THREADS) {
         const int j = idx / (GEMV_ROWS * 8), rem = idx % (GEMV_ROWS * 8);
         const int tok = j * 8 + rem / GEMV_ROWS, row = rem % GEMV_ROWS;   // rows fastest: coalesced stores
@@ -126,7 +142,8 @@ static int launch_gemv(void* Y, const __nv_bfloat16* X, const __nv_bfloat16* W, 
     const int blocks = (N + GEMV_ROWS - 1) / GEMV_ROWS;
     if (mode == 0) gemv_bf16_kernel<NT, 0><<<blocks, GEMV_THREADS, 0, st>>>(Y, X, W, T, N, K, ldx, ldy);
     else if (mode == 1) gemv_bf16_kernel<NT, 1><<<blocks, GEMV_THREADS, 0, st>>>(Y, X, W, T, N, K, ldx, ldy);
-    else gemv_bf16_kernel<NT, 2><<<blocks, GEMV_THREADS, 0, st>>>(Y, X, W, T, N, K, ldx, ldy);
+    else if (mode == 2) gemv_bf16_kernel<NT, 2><<<blocks, GEMV_THREADS, 0, st>>>(Y, X, W, T, N, K, ldx, ldy);
+    else gemv_bf16_kernel<NT, 3><<<blocks, GEMV_THREADS, 0, st>>>(Y, X, W, T, N, K, ldx, ldy);
     return zlm_check_launch("gemv_bf16");
 }
 
@@ -140,7 +157,8 @@ extern "C" int zlm_gemv_bf16(void* Y, const void* X, const void* W, int T, int N
     ZLM_REQUIRE(K % 8 == 0 && ldx % 8 == 0,
                 "gemv_bf16: the inner size K=%d (row stride %d) must be a multiple of 8 for bf16 kernels", K, ldx);
     ZLM_REQUIRE(((uintptr_t)X % 16 == 0) && ((uintptr_t)W % 16 == 0), "gemv_bf16: operands must be 16-byte aligned");
-    ZLM_REQUIRE(mode >= 0 && mode <= 2, "gemv_bf16: mode %d", mode);
+    ZLM_REQUIRE(mode >= 0 && mode <= 3, "gemv_bf16: mode %d", mode);
+    ZLM_REQUIRE(mode != 3 || N % 16 == 0, "gemv_bf16: the fused gate/up product needs N=%d to be a multiple of 16", N);
     const __nv_bfloat16* x = (const __nv_bfloat16*)X;
     const __nv_bfloat16* w = (const __nv_bfloat16*)W;
     if (T <= 8) return launch_gemv<1>(Y, x, w, T, N, K, ldx, ldy, mode, st);

@@ -18,11 +18,18 @@ PAGE_TOKENS = 64
 
 _DT = {torch.float32: F32, torch.bfloat16: BF16}
 
-STORE, ACCUM, STORE_F32 = 0, 1, 2
+STORE, ACCUM, STORE_F32, SWIGLU = 0, 1, 2, 3
 
 
 class KernelError(RuntimeError):
     pass
+
+
+def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """[2I, K] with rows 8 gate, 8 up, 8 gate, ...: the layout ``linear_swiglu`` wants."""
+    I, K = gate.shape
+    assert up.shape == (I, K) and I % 8 == 0
+    return torch.stack([gate.view(I // 8, 8, K), up.view(I // 8, 8, K)], dim=1).reshape(2 * I, K).contiguous()
 
 
 def decode_splits(rows: int, nkv: int, len_bucket: int) -> int:
@@ -136,11 +143,24 @@ class CudaKernels:
         mode = ACCUM if accumulate else (STORE_F32 if out.dtype == torch.float32 else STORE)
         if mode == STORE:
             assert out.dtype == torch.bfloat16
+        self._bf16_product(out, x, w, T, N, K, ldx, ldy, mode, impl)
+
+    def _bf16_product(self, out, x, w, T, N, K, ldx, ldy, mode, impl) -> None:
         if impl is None:
-            impl = "gemv" if T <= 16 else ("tc" if T >= 128 and self.lib.zlm_gemm_tc_supported(T, N, K, ldx) else "mma")
+            impl = "gemv" if T <= 16 else ("tc" if self.lib.zlm_gemm_tc_supported(T, N, K, ldx) else "mma")
         name = {"gemv": "zlm_gemv_bf16", "mma": "zlm_gemm_bf16_mma", "tc": "zlm_gemm_tc"}[impl]
         self._call(name, c_void_p(out.data_ptr()), c_void_p(x.data_ptr()), c_void_p(w.data_ptr()),
                    c_int(T), c_int(N), c_int(K), c_int(ldx), c_int(ldy), c_int(mode), self._stream())
+
+    def linear_swiglu(self, out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, impl: Optional[str] = None) -> None:
+        """out[t, c] = silu(x[t] . gate_c) * (x[t] . up_c) in one pass over w (bf16).  w is
+        [2I, K] with the rows in groups of 16: 8 gate channels, then the 8 matching up
+        channels (``interleave_gate_up``); out is [T, I]."""
+        T, K = x.shape
+        N = w.shape[0]
+        assert x.dtype == w.dtype == out.dtype == torch.bfloat16 and w.shape[1] == K and N % 16 == 0
+        assert out.shape == (T, N // 2) and x.stride(1) == 1 and out.stride(1) == 1 and w.is_contiguous()
+        self._bf16_product(out, x, w, T, N, K, x.stride(0), out.stride(0), SWIGLU, impl)
 
     def qk_norm_rope_write(self, qkv: torch.Tensor, q_w: Optional[torch.Tensor],
                            k_w: Optional[torch.Tensor], eps: float,

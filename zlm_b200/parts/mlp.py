@@ -26,14 +26,26 @@ class SwiGLU(FeedForward):
                 "down_proj.weight": ParamSpec((self.hidden, self.inter))}
 
     def bind(self, params: Dict[str, torch.Tensor]) -> None:
-        self.w_gu = torch.cat([params.pop("gate_proj.weight"), params.pop("up_proj.weight")], dim=0).contiguous()
+        gate, up = params.pop("gate_proj.weight"), params.pop("up_proj.weight")
+        # bf16: gate and up rows interleaved in eights, so that the product's epilogue holds
+        # a channel's gate and up together and writes silu(gate) * up directly
+        self.fused = (gate.dtype == torch.bfloat16 and self.inter % 8 == 0
+                      and hasattr(self.rt.k, "linear_swiglu"))
+        if self.fused:
+            from ..kernels import interleave_gate_up
+            self.w_gu = interleave_gate_up(gate, up)
+        else:
+            self.w_gu = torch.cat([gate, up], dim=0).contiguous()
         self.w_down = params.pop("down_proj.weight")
 
     def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx: StepContext) -> None:
         rt, k = self.rt, self.rt.k
         T = x.shape[0]
-        gu = rt.ws.get("ffn.gu", (T, 2 * self.inter), rt.dtype)
-        k.linear(gu, x, self.w_gu)
         act = rt.ws.get("ffn.act", (T, self.inter), rt.dtype)
-        k.swiglu(act, gu)
+        if self.fused:
+            k.linear_swiglu(act, x, self.w_gu)
+        else:
+            gu = rt.ws.get("ffn.gu", (T, 2 * self.inter), rt.dtype)
+            k.linear(gu, x, self.w_gu)
+            k.swiglu(act, gu)
         k.linear(residual, act, self.w_down, accumulate=True)
