@@ -132,6 +132,8 @@ def run(args) -> dict:
                              max_batch=max(B, big, 1), max_seq_len=CONTEXT,
                              max_step_tokens=max(B, 8) * PROMPT_LEN)
     greedy = SamplingParams()
+    if args.pdl:
+        eng.decoder.use_pdl = True
     g = torch.Generator().manual_seed(0)
     per_layer, weight_bytes, kv_per_tok = model_numbers(cfg, args.layers)
     k = eng.rt.k
@@ -300,6 +302,7 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true")
     ap.add_argument("--profile", choices=["decode", "prefill"], help="run a small case for ncu and exit")
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN)
+    ap.add_argument("--pdl", action="store_true", help="decode kernels with programmatic dependent launch")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":

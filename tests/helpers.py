@@ -68,10 +68,10 @@ def random_prompts(vocab: int, lengths: Sequence[int], seed: int) -> List[List[i
     return [torch.randint(0, vocab, (n,), generator=g).tolist() for n in lengths]
 
 
-def assert_close(got: torch.Tensor, want: torch.Tensor, dtype: str, what: str = ""):
+def assert_close(got: torch.Tensor, want: torch.Tensor, dtype: str, what: str = "", tol=None):
     got, want = got.float().cpu(), want.float().cpu()
     assert got.shape == want.shape, f"{what}: shape {tuple(got.shape)} vs {tuple(want.shape)}"
-    tol = TOL[dtype]
+    tol = tol or TOL[dtype]
     err = (got - want).abs()
     bound = tol["atol"] + tol["rtol"] * want.abs()
     if got.dim() > 1:

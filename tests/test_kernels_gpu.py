@@ -219,7 +219,7 @@ class FakePlan:
         return self.bufs[name]
 
 
-@pytest.mark.parametrize("len_bucket", [1, 8, 64, 1024])
+@pytest.mark.parametrize("len_bucket", [16, 64, 1024])
 @pytest.mark.parametrize("nq,nkv,hd,window", [(4, 2, 16, 0), (6, 2, 48, 24), (5, 5, 80, 0), (8, 1, 128, 100),
                                               (32, 8, 128, 0), (16, 1, 64, 0), (6, 3, 32, 70)])
 def test_attention_decode_kernel(K, nq, nkv, hd, window, len_bucket):
@@ -244,7 +244,7 @@ def test_attention_decode_kernel(K, nq, nkv, hd, window, len_bucket):
     got = torch.empty(T, nq * hd, dtype=dt, device="cuda")
     plan = FakePlan(len_bucket)
     K.attention(got, q.cuda(), pool.cuda(), table.cuda(), pos.cuda(), slot.cuda(), nq, nkv, hd, scale, window, plan)
-    assert (decode_splits(T, nkv, len_bucket) > 1) == bool(plan.bufs)
+    assert (decode_splits(T, nkv, len_bucket)[0] > 1) == bool(plan.bufs)
     close(got, want, dt, atol=3e-2, rtol=3e-2)
     vfar = pool[page, 1, nkv - 1, far % PAGE, :].float()
     assert (got[0, (nq - 1) * hd:].float().cpu() - vfar).abs().max() < 0.05 * vfar.abs().max() + 0.05

@@ -1,0 +1,68 @@
+"""The engine at the layer sizes of Qwen3-8B (width 4096, 32 query heads over 8 kv
+heads of size 128, feed-forward 12288; two layers and a reduced vocabulary so that
+the plain implementation finishes in seconds): every kernel at the shapes the
+benchmark runs, in 32-bit and in bfloat16, whole prompt, chunks and decode."""
+import pytest
+import torch
+
+from helpers import assert_close, plain_logits, random_prompts, reference_tensors
+
+pytestmark = pytest.mark.gpu
+
+# Sums here run over 4096 to 12288 terms instead of the tiny models' 64 to 160, and the logits
+# are an order of magnitude larger: the rounding of a 32-bit sum grows with the square root of
+# its length, so the element-wise bound of the 32-bit comparison is ten times the tiny models'.
+# In bfloat16 the rows keep the tiny models' bound (2% of a row's norm); the element-wise bound
+# is there to catch single wild values, and among 2.4 million logits of standard deviation 1.3
+# the largest rounding error is several times the typical one: 0.15.
+TOL_8B = {"float32": dict(atol=2e-4, rtol=1e-4, row=1e-4), "bfloat16": dict(atol=0.15, rtol=2e-2, row=2e-2)}
+
+SIZES_8B = {
+    "architectures": ["Qwen3ForCausalLM"], "num_hidden_layers": 2, "hidden_size": 4096,
+    "num_attention_heads": 32, "num_key_value_heads": 8, "head_dim": 128, "intermediate_size": 12288,
+    "vocab_size": 8192, "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "tie_word_embeddings": False,
+    "max_position_embeddings": 4096, "hidden_act": "silu",
+}
+
+
+@pytest.fixture(scope="module")
+def model():
+    from zlm_b200.parts.model import DecoderModel
+    from zlm_b200.registry import config_from_dict
+    from zlm_b200.weights import random_tensors
+    cfg = config_from_dict(SIZES_8B)
+    tensors = random_tensors(DecoderModel(cfg.to_model_spec()).param_specs(), 5, "cpu", torch.float32)
+    (prompt,) = random_prompts(cfg.vocab_size, [300], seed=9)
+    want = {dt: plain_logits(reference_tensors(tensors, dt), cfg, prompt) for dt in ("float32", "bfloat16")}
+    return cfg, tensors, prompt, want
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_layer_sizes_of_the_benchmark(model, dtype):
+    from zlm_b200 import Engine, StepEntry
+    from zlm_b200.engine import parse_dtype
+    from zlm_b200.sampling import SamplingParams
+    from zlm_b200.weights.loader import target_dtype
+    from zlm_b200.parts.model import DecoderModel
+    cfg, tensors, prompt, want = model
+    dt = parse_dtype(dtype)
+    specs = DecoderModel(cfg.to_model_spec()).param_specs()
+    dev = {n: t.to("cuda").to(target_dtype(specs[n], t.dtype, dt)) for n, t in tensors.items()}
+    eng = Engine(cfg, dev, dt, "cuda:0", max_tokens=2048, max_batch=4)
+    ref = want[dtype]
+    # whole (tcgen05 products and tiled attention in bfloat16)
+    s = eng.new_sequence()
+    got = eng.step([StepEntry(s, prompt, list(range(300)))]).clone()
+    assert_close(got, ref, dtype, f"8B sizes whole {dtype}", TOL_8B[dtype])
+    eng.release(s)
+    # a long chunk, a short chunk (the few-token kernels), then single tokens through the decode path
+    s = eng.new_sequence()
+    parts = [eng.step([StepEntry(s, prompt[:200], list(range(200)))]).clone(),
+             eng.step([StepEntry(s, prompt[200:240], list(range(40)))]).clone(),
+             eng.step([StepEntry(s, prompt[240:250], list(range(10)))]).clone()]
+    assert_close(torch.cat(parts), ref[:250], dtype, f"8B sizes chunks {dtype}", TOL_8B[dtype])
+    for t in range(250, 262):
+        eng.decoder.step([s], [prompt[t]], SamplingParams())
+        assert_close(eng.decoder.last_logits.clone(), ref[t:t + 1], dtype, f"8B sizes decode {t} {dtype}", TOL_8B[dtype])
+    if dtype == "bfloat16":
+        assert eng.rt.k.gemm_tc_status() == 0

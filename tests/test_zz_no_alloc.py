@@ -49,12 +49,13 @@ def _case(seed, lens, nq, nkv, hd):
 
 def _run(lib, static, q, pool, table, pos, slot, nq, nkv, hd, splits):
     T = q.shape[0]
+    per = -(-(int(pos.max()) // PAGE + 1) // splits)          # pages per split, so that the splits cover the longest
     out = torch.zeros((T, nq * hd), dtype=torch.bfloat16, device="cuda")
     st = c_void_p(torch.cuda.current_stream().cuda_stream)
     common = (c_void_p(out.data_ptr()), c_int(out.stride(0)), c_void_p(q.data_ptr()), c_int(q.stride(0)),
               c_void_p(pool.data_ptr()), c_void_p(table.data_ptr()), c_int(table.stride(0)),
               c_void_p(pos.data_ptr()), c_void_p(slot.data_ptr()), c_int(T), c_int(nq), c_int(nkv), c_int(hd),
-              c_float(1.0 / math.sqrt(hd)), c_int(0), c_int(splits))
+              c_float(1.0 / math.sqrt(hd)), c_int(0), c_int(splits), c_int(per))
     if static:
         rc = lib.zlm_attention_decode_static(*common, st)
     else:

@@ -1,8 +1,9 @@
 // Decode attention over the paged bf16 cache: one query token per sequence, all
 // query heads of a kv group share one pass over that group's keys and values.
 //
-// grid (token, kv head, split).  A block walks its share of the sequence's pages;
-// a page (64 keys) is staged in shared memory with cp.async, double buffered; each
+// grid (token, kv head, split).  A block takes `per` consecutive pages of the
+// sequence; a page (64 keys) is staged in shared memory with cp.async, two stages,
+// the first two loads in flight together; each
 // of the 4 warps takes 16 keys of the page: S = Q K^T and O += P V on the
 // warp-level tensor cores (the group's heads are the rows of a 16-row tile), with
 // an fp32 running maximum and sum per head.  The warps' partial results are
@@ -25,7 +26,7 @@ attention_decode_kernel(__nv_bfloat16* __restrict__ out, int out_stride, const _
                         int q_stride, const __nv_bfloat16* __restrict__ pool,
                         const int* __restrict__ block_table, int table_stride,
                         const int* __restrict__ token_pos, const int* __restrict__ token_slot, int nq, int nkv,
-                        float scale_log2, int window, int splits, float* __restrict__ part_o,
+                        float scale_log2, int window, int splits, int per, float* __restrict__ part_o,
                         float* __restrict__ part_ml) {
     constexpr int KS = HD / 16;            // k-steps of Q K^T; pairs of output n-tiles of P V
     constexpr int CH = HD / 8;             // 16-byte chunks per row
@@ -38,6 +39,7 @@ attention_decode_kernel(__nv_bfloat16* __restrict__ out, int out_stride, const _
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, qd = lane & 3;
     const int G = nq / nkv;
+    pdl_launch_dependents();
     const int pos = token_pos[t];
     const int slot = token_slot[t];
     const int seq = pos + 1;
@@ -48,10 +50,11 @@ attention_decode_kernel(__nv_bfloat16* __restrict__ out, int out_stride, const _
 
     // this split's pages
     const int page_lo = t_start / ZLM_PAGE, page_hi = pos / ZLM_PAGE + 1;
-    const int per = (page_hi - page_lo + splits - 1) / splits;
     const int p_begin = page_lo + split * per;
     const int p_end = min(page_hi, p_begin + per);
+    if (p_begin >= p_end && splits > 1) return;      // the combine kernel skips this split too
 
+    pdl_wait();          // q and this step's keys and values come from the kernel before
     // Q fragments: row i of the 16-row tile is head kvh*G + i (zero beyond the group)
     unsigned qf[KS][4];
     {
@@ -87,14 +90,15 @@ attention_decode_kernel(__nv_bfloat16* __restrict__ out, int out_stride, const _
 
     if (p_begin < p_end) load_page(p_begin, 0);
     dec_commit();
+    if (p_begin + 1 < p_end) load_page(p_begin + 1, 1);
+    dec_commit();
     for (int p = p_begin; p < p_end; ++p) {
         const int stage = (p - p_begin) & 1;
-        dec_wait<0>();
+        dec_wait<1>();                       // everything but the newest group has landed: page p is there
         __syncthreads();
-        if (p + 1 < p_end) load_page(p + 1, stage ^ 1);
-        dec_commit();
         const int kbase = p * ZLM_PAGE + warp * 16;
-        if (kbase > pos || kbase + 15 < t_start) continue;       // warp-uniform: nothing to see
+        const bool busy = !(kbase > pos || kbase + 15 < t_start);       // warp-uniform
+        if (busy) {
         const __nv_bfloat16* kt = Ks + stage * TILE;
         const __nv_bfloat16* vt = Vs + stage * TILE;
 
@@ -166,6 +170,10 @@ attention_decode_kernel(__nv_bfloat16* __restrict__ out, int out_stride, const _
             dec_mma(o[2 * dn], pa, b0, b1);
             dec_mma(o[2 * dn + 1], pa, b2, b3);
         }
+        }
+        __syncthreads();                     // every warp is done with this stage
+        if (p + 2 < p_end) load_page(p + 2, stage);
+        dec_commit();
     }
     dec_wait<0>();
     __syncthreads();
@@ -215,26 +223,43 @@ attention_decode_kernel(__nv_bfloat16* __restrict__ out, int out_stride, const _
     }
 }
 
-// combines the splits of one (token, head) in the order 0 .. splits-1
-__global__ void attention_decode_combine_kernel(__nv_bfloat16* __restrict__ out, int out_stride,
-                                                const float* __restrict__ part_o,
-                                                const float* __restrict__ part_ml, int nq, int hd, int splits) {
-    const int t = blockIdx.x, head = blockIdx.y;
+// combines the splits of one (token, head) in the order 0 .. used-1: the maxima and sums
+// of the splits are read by one thread each and reduced by the block, then every thread
+// sums one output dimension over the splits (independent loads, one latency deep)
+#define COMB_THREADS 128
+#define COMB_MAX_SPLITS 1024
+__global__ void __launch_bounds__(COMB_THREADS)
+attention_decode_combine_kernel(__nv_bfloat16* __restrict__ out, int out_stride, const float* __restrict__ part_o,
+                                const float* __restrict__ part_ml, const int* __restrict__ token_pos, int nq,
+                                int hd, int splits, int per, int window) {
+    __shared__ float fs[COMB_MAX_SPLITS];
+    __shared__ float red[32];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x, head = blockIdx.y, tid = threadIdx.x;
+    const int pos = token_pos[t];
+    const int t_start = (window != 0 && pos + 1 > window) ? pos + 1 - window : 0;
+    const int pages = pos / ZLM_PAGE + 1 - t_start / ZLM_PAGE;
+    const int used = min(splits, (pages + per - 1) / per);
     const size_t base = ((size_t)t * nq + head) * splits;
-    float M = -INFINITY;
-    for (int s = 0; s < splits; ++s) M = fmaxf(M, part_ml[(base + s) * 2]);
-    float L = 0.f;
-    for (int s = 0; s < splits; ++s) {
+    float m = -INFINITY;
+    for (int s = tid; s < used; s += COMB_THREADS) m = fmaxf(m, part_ml[(base + s) * 2]);
+    const float M = block_max(m, red);
+    float l = 0.f;
+    for (int s = tid; s < used; s += COMB_THREADS) {
         const float ms = part_ml[(base + s) * 2];
-        L += ms == -INFINITY ? 0.f : part_ml[(base + s) * 2 + 1] * exp2f(ms - M);
+        const float f = ms == -INFINITY ? 0.f : exp2f(ms - M);
+        fs[s] = f;
+        l += part_ml[(base + s) * 2 + 1] * f;
     }
-    for (int d = threadIdx.x; d < hd; d += blockDim.x) {
+    const float L = block_sum(l, red);        // fixed order for a given number of splits
+    __syncthreads();
+    const float inv = 1.0f / L;
+    for (int d = tid; d < hd; d += COMB_THREADS) {
         float O = 0.f;
-        for (int s = 0; s < splits; ++s) {
-            const float ms = part_ml[(base + s) * 2];
-            if (ms != -INFINITY) O += part_o[(base + s) * hd + d] * exp2f(ms - M);
-        }
-        out[(size_t)t * out_stride + (size_t)head * hd + d] = __float2bfloat16_rn(O / L);
+#pragma unroll 8
+        for (int s = 0; s < used; ++s) O = fmaf(part_o[(base + s) * hd + d], fs[s], O);
+        out[(size_t)t * out_stride + (size_t)head * hd + d] = __float2bfloat16_rn(O * inv);
     }
 }
 
@@ -242,7 +267,7 @@ template <int HD>
 static int launch_decode(__nv_bfloat16* out, int out_stride, const __nv_bfloat16* q, int q_stride,
                          const __nv_bfloat16* pool, const int* block_table, int table_stride,
                          const int* token_pos, const int* token_slot, int T, int nq, int nkv, float scale,
-                         int window, int splits, float* part_o, float* part_ml, cudaStream_t st) {
+                         int window, int splits, int per, float* part_o, float* part_ml, cudaStream_t st) {
     const size_t stage_bytes = (size_t)4 * ZLM_PAGE * HD * sizeof(__nv_bfloat16);
     const size_t merge_bytes = (size_t)DEC_WARPS * 16 * (HD + 2) * sizeof(float);
     const size_t smem = stage_bytes > merge_bytes ? stage_bytes : merge_bytes;
@@ -258,13 +283,13 @@ static int launch_decode(__nv_bfloat16* out, int out_stride, const __nv_bfloat16
     }
     dim3 grid(T, nkv, splits);
     const float scale_log2 = scale * 1.4426950408889634f;
-    kern<<<grid, DEC_THREADS, smem, st>>>(out, out_stride, q, q_stride, pool, block_table, table_stride, token_pos,
-                                         token_slot, nq, nkv, scale_log2, window, splits, part_o, part_ml);
+    zlm_launch(kern, grid, dim3(DEC_THREADS), smem, st, out, out_stride, q, q_stride, pool, block_table, table_stride,
+               token_pos, token_slot, nq, nkv, scale_log2, window, splits, per, part_o, part_ml);
     int rc = zlm_check_launch("attention_decode");
     if (rc) return rc;
     if (splits > 1) {
-        dim3 g2(T, nq);
-        attention_decode_combine_kernel<<<g2, HD >= 128 ? 128 : 64, 0, st>>>(out, out_stride, part_o, part_ml, nq, HD, splits);
+        zlm_launch(attention_decode_combine_kernel, dim3(T, nq), dim3(COMB_THREADS), 0, st, out, out_stride,
+                   (const float*)part_o, (const float*)part_ml, token_pos, nq, HD, splits, per, window);
         rc = zlm_check_launch("attention_decode_combine");
     }
     return rc;
@@ -275,22 +300,25 @@ extern "C" int zlm_attention_decode_supported(int nq, int nkv, int hd) {
     return (nkv > 0 && nq % nkv == 0 && nq / nkv <= 16 && hd % 16 == 0 && hd >= 16 && hd <= 128) ? 1 : 0;
 }
 
+// every split takes `per` pages; splits * per pages must cover the longest sequence.
 // scratch: part_o needs T*nq*splits*hd floats, part_ml T*nq*splits*2 floats (unused if splits == 1)
 extern "C" int zlm_attention_decode(void* out, int out_stride, const void* q, int q_stride, const void* pool,
                                     const int* block_table, int table_stride, const int* token_pos,
                                     const int* token_slot, int T, int nq, int nkv, int hd, float scale,
-                                    int window, int splits, float* part_o, float* part_ml, cudaStream_t st) {
+                                    int window, int splits, int per, float* part_o, float* part_ml,
+                                    cudaStream_t st) {
     if (T == 0) return ZLM_OK;
     ZLM_REQUIRE(zlm_attention_decode_supported(nq, nkv, hd),
                 "attention_decode: %d heads over %d kv heads of size %d is not a shape this kernel takes", nq, nkv, hd);
-    ZLM_REQUIRE(splits >= 1 && splits <= 65535 && nkv <= 65535, "attention_decode: splits=%d", splits);
+    ZLM_REQUIRE(splits >= 1 && splits <= COMB_MAX_SPLITS && nkv <= 65535 && per >= 1,
+                "attention_decode: splits=%d (at most %d) of %d pages", splits, COMB_MAX_SPLITS, per);
     ZLM_REQUIRE(splits == 1 || (part_o && part_ml), "attention_decode: scratch missing for %d splits", splits);
     ZLM_REQUIRE(q_stride % 2 == 0 && ((uintptr_t)q % 4 == 0), "attention_decode: q must be 4-byte aligned");
 #define ZLM_DEC_CASE(H)                                                                                       \
     case H:                                                                                                   \
         return launch_decode<H>((__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)q, q_stride,           \
                                 (const __nv_bfloat16*)pool, block_table, table_stride, token_pos, token_slot, \
-                                T, nq, nkv, scale, window, splits, part_o, part_ml, st);
+                                T, nq, nkv, scale, window, splits, per, part_o, part_ml, st);
     switch (hd) {
         ZLM_DEC_CASE(16) ZLM_DEC_CASE(32) ZLM_DEC_CASE(48) ZLM_DEC_CASE(64) ZLM_DEC_CASE(80) ZLM_DEC_CASE(96)
         ZLM_DEC_CASE(112) ZLM_DEC_CASE(128)
@@ -315,7 +343,7 @@ static float* g_decode_scratch_ptr[ZLM_MAX_DEVICES];     // device address of th
 extern "C" int zlm_attention_decode_static(void* out, int out_stride, const void* q, int q_stride,
                                            const void* pool, const int* block_table, int table_stride,
                                            const int* token_pos, const int* token_slot, int T, int nq,
-                                           int nkv, int hd, float scale, int window, int splits,
+                                           int nkv, int hd, float scale, int window, int splits, int per,
                                            cudaStream_t st) {
     if (T == 0) return ZLM_OK;
     ZLM_REQUIRE(T > 0 && nq > 0 && hd > 0 && splits >= 1, "attention_decode_static: bad sizes T=%d nq=%d hd=%d splits=%d",
@@ -346,5 +374,5 @@ extern "C" int zlm_attention_decode_static(void* out, int out_stride, const void
     float* part_o = g_decode_scratch_ptr[dev];
     float* part_ml = part_o + (size_t)T * nq * splits * hd;
     return zlm_attention_decode(out, out_stride, q, q_stride, pool, block_table, table_stride, token_pos,
-                                token_slot, T, nq, nkv, hd, scale, window, splits, part_o, part_ml, st);
+                                token_slot, T, nq, nkv, hd, scale, window, splits, per, part_o, part_ml, st);
 }

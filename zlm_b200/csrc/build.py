@@ -22,7 +22,7 @@ LIB_NAME = "libzlm_b200.so"
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=default",
-]
+] + os.environ.get("ZLM_B200_NVCC_FLAGS", "").split()      # extra flags, e.g. -DNAME, for experiments
 
 
 def _say(msg: str) -> None:

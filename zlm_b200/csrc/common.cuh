@@ -83,3 +83,38 @@ __device__ __forceinline__ float block_max(float v, float* red) {
     t = warp_max(t);
     return t;
 }
+
+// ---------------------------------------------------------------------------
+// Programmatic dependent launch.  A decode step is a chain of short kernels; with
+// this launch attribute a kernel's blocks may be scheduled while the kernel before
+// it is still draining.  Every kernel of the chain calls pdl_launch_dependents()
+// first and pdl_wait() before it touches anything an earlier kernel of the step
+// writes (activations, cache, scratch); what it reads before the wait must be
+// constant during the step (weights, tables, the step's integer arrays, which are
+// uploaded before the step's first kernel).  Without the attribute both calls do
+// nothing.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void pdl_launch_dependents() {
+#ifndef ZLM_PDL_LATE
+    asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory");
+#endif
+}
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
+
+int zlm_pdl_enabled();
+
+template <typename... KArgs, typename... Args>
+static inline void zlm_launch(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                              Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = zlm_pdl_enabled() ? 1 : 0;
+    cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);     // errors surface in zlm_check_launch
+}

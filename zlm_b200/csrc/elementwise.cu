@@ -25,6 +25,11 @@ int zlm_check_launch(const char* what) {
     return ZLM_OK;
 }
 
+static int g_pdl = 0;
+int zlm_pdl_enabled() { return g_pdl; }
+// 1: launch the decode-path kernels with programmatic dependent launch; 0: plain stream order
+extern "C" void zlm_set_pdl(int on) { g_pdl = on ? 1 : 0; }
+
 extern "C" const char* zlm_last_error() { return g_err; }
 extern "C" int zlm_page_tokens() { return ZLM_PAGE; }
 
@@ -32,7 +37,9 @@ extern "C" int zlm_page_tokens() { return ZLM_PAGE; }
 template <typename TW>
 __global__ void embed_kernel(float* __restrict__ out, const TW* __restrict__ table,
                              const int* __restrict__ ids, int H, int V) {
+    pdl_launch_dependents();
     const int t = blockIdx.x;
+    pdl_wait();                 // the ids may be what the previous step's sampler wrote
     int id = ids[t];
     // ids are validated on the host; clamp so that a bad id can never read
     // outside the table
@@ -62,9 +69,9 @@ extern "C" int zlm_embed(float* out, const void* table, int table_dtype, const i
     ZLM_REQUIRE(T > 0 && H > 0 && V > 0, "embed: bad sizes T=%d H=%d V=%d", T, H, V);
     const int threads = H >= 4096 ? 512 : (H >= 1024 ? 256 : 128);
     if (table_dtype == ZLM_DTYPE_F32)
-        embed_kernel<float><<<T, threads, 0, st>>>(out, (const float*)table, ids, H, V);
+        zlm_launch(embed_kernel<float>, T, threads, 0, st, out, (const float*)table, ids, H, V);
     else if (table_dtype == ZLM_DTYPE_BF16)
-        embed_kernel<__nv_bfloat16><<<T, threads, 0, st>>>(out, (const __nv_bfloat16*)table, ids, H, V);
+        zlm_launch(embed_kernel<__nv_bfloat16>, T, threads, 0, st, out, (const __nv_bfloat16*)table, ids, H, V);
     else
         ZLM_REQUIRE(false, "embed: unsupported table dtype %d", table_dtype);
     return zlm_check_launch("embed");
@@ -80,9 +87,11 @@ template <typename TO>
 __global__ void rmsnorm_kernel(TO* __restrict__ out, const float* __restrict__ x, VecW w,
                                const int* __restrict__ rows, int H, float eps) {
     __shared__ float red[32];
+    pdl_launch_dependents();
     const int r = blockIdx.x;
     const int src = rows ? rows[r] : r;
     const float* xr = x + (size_t)src * H;
+    pdl_wait();
     TO* o = out + (size_t)r * H;
     const int nv = H / 4;
     if (H % 4 == 0 && nv <= NORM_MAX_V4 * (int)blockDim.x) {
@@ -133,9 +142,9 @@ extern "C" int zlm_rmsnorm(void* out, int out_dtype, const float* x, const void*
     while (threads < 1024 && threads * 4 < H) threads *= 2;
     if (out_dtype == ZLM_DTYPE_BF16 && R >= 512 && H % 4 == 0 && H <= 256 * 4 * NORM_MAX_V4 && threads > 256) threads = 256;
     if (out_dtype == ZLM_DTYPE_F32)
-        rmsnorm_kernel<float><<<R, threads, 0, st>>>((float*)out, x, vw, rows, H, eps);
+        zlm_launch(rmsnorm_kernel<float>, R, threads, 0, st, (float*)out, x, vw, rows, H, eps);
     else if (out_dtype == ZLM_DTYPE_BF16)
-        rmsnorm_kernel<__nv_bfloat16><<<R, threads, 0, st>>>((__nv_bfloat16*)out, x, vw, rows, H, eps);
+        zlm_launch(rmsnorm_kernel<__nv_bfloat16>, R, threads, 0, st, (__nv_bfloat16*)out, x, vw, rows, H, eps);
     else
         ZLM_REQUIRE(false, "rmsnorm: unsupported output dtype %d", out_dtype);
     return zlm_check_launch("rmsnorm");
@@ -145,6 +154,8 @@ extern "C" int zlm_rmsnorm(void* out, int out_dtype, const float* x, const void*
 // gu is [T, 2I]: gate in columns [0, I), up in [I, 2I)
 template <typename TA>
 __global__ void swiglu_kernel(TA* __restrict__ out, const TA* __restrict__ gu, int T, int I) {
+    pdl_launch_dependents();
+    pdl_wait();
     const size_t n = (size_t)T * I;
     for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < n;
          e += (size_t)gridDim.x * blockDim.x) {
@@ -163,10 +174,11 @@ extern "C" int zlm_swiglu(void* out, const void* gu, int dtype, int T, int I, cu
     int blocks = (int)((n + 255) / 256);
     if (blocks > 148 * 16) blocks = 148 * 16;
     if (dtype == ZLM_DTYPE_F32)
-        swiglu_kernel<float><<<blocks, 256, 0, st>>>((float*)out, (const float*)gu, T, I);
+        zlm_launch(swiglu_kernel<float>, blocks, 256, 0, st, (float*)out, (const float*)gu, T, I);
     else if (dtype == ZLM_DTYPE_BF16)
-        swiglu_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)gu, T, I);
+        zlm_launch(swiglu_kernel<__nv_bfloat16>, blocks, 256, 0, st, (__nv_bfloat16*)out, (const __nv_bfloat16*)gu, T, I);
     else
         ZLM_REQUIRE(false, "swiglu: unsupported dtype %d", dtype);
     return zlm_check_launch("swiglu");
 }
+

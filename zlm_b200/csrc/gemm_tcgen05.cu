@@ -101,7 +101,9 @@ __device__ __forceinline__ uint64_t make_desc(unsigned smem_addr) {
 __device__ __forceinline__ float silu_mul(float g, float u) { return (g / (1.0f + expf(-g))) * u; }
 
 // MODE 0: Y bf16 = acc; MODE 1: Y fp32 += acc; MODE 2: Y fp32 = acc;
-// MODE 3: the outputs come in groups of 16 = 8 gate + 8 up channels; Y bf16 [T, N/2] = silu(gate) * up.
+// MODE 3: the outputs come in groups of 16 = 8 gate + 8 up channels; Y bf16 [T, N/2] = silu(gate) * up;
+// MODE 4 (swapped form only): the block sums its share of K (blockIdx.z of gridDim.z) and stores the
+// fp32 partial product to Y [gridDim.z][T][N]; zlm_gemm_tc adds the shares up in a second kernel.
 // SWAP false: first operand = X (rows are tokens), second = W; true: first = W, second = X.
 template <int BN, int STAGES, bool SWAP, int MODE>
 __global__ void __launch_bounds__(TC_THREADS, 1)
@@ -120,7 +122,11 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int a0row = blockIdx.x * TC_BM, b0row = blockIdx.y * BN;
-    const int KB = (K + TC_BK - 1) / TC_BK;
+    const int KB_all = (K + TC_BK - 1) / TC_BK;
+    // this block's share of the k blocks (all of them unless the grid splits K)
+    const int kb_per = (KB_all + gridDim.z - 1) / gridDim.z;
+    const int kb_lo = blockIdx.z * kb_per;
+    const int KB = max(0, min(KB_all, kb_lo + kb_per) - kb_lo);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
@@ -137,6 +143,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     __syncthreads();
     tc_fence_after();
     const unsigned tmem_base = *tmem_slot;
+    pdl_launch_dependents();
+    pdl_wait();          // set-up above overlaps the kernel before; operands and Y are touched from here on
 
     if (warp == 0) {
         if (lane == 0) {
@@ -146,8 +154,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 const unsigned round = kb / STAGES;
                 if (!mbar_wait(&empty[s], (round & 1) ^ 1, abort_flag, 1)) break;
                 mbar_expect_tx(&full[s], A_BYTES + B_BYTES);
-                tma_load_2d(sA + s * A_BYTES, &map_a, kb * TC_BK, a0row, &full[s]);
-                tma_load_2d(sB + s * B_BYTES, &map_b, kb * TC_BK, b0row, &full[s]);
+                tma_load_2d(sA + s * A_BYTES, &map_a, (kb_lo + kb) * TC_BK, a0row, &full[s]);
+                tma_load_2d(sB + s * B_BYTES, &map_b, (kb_lo + kb) * TC_BK, b0row, &full[s]);
                 issued = kb + 1;
             }
             if (*abort_flag) {
@@ -188,6 +196,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             for (int c = 0; c < BN; c += 16) {
                 float v[16];
                 tc_ld16(tmem_base + ((unsigned)(lg * 32) << 16) + (unsigned)c, v);     // warp-wide
+                if (KB == 0) {
+#pragma unroll
+                    for (int i = 0; i < 16; ++i) v[i] = 0.f;     // a share of K with nothing in it
+                }
                 if (!SWAP) {
                     // this thread: token arow, outputs b0row + c .. + 15
                     const int n = b0row + c;
@@ -258,7 +270,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                             const size_t off = (size_t)(t0 + i) * ldy + arow;
                             if (MODE == 0) ((__nv_bfloat16*)Y)[off] = __float2bfloat16_rn(v[i]);
                             else if (MODE == 1) ((float*)Y)[off] += v[i];
-                            else ((float*)Y)[off] = v[i];
+                            else if (MODE == 2) ((float*)Y)[off] = v[i];
+                            else ((float*)Y)[((size_t)blockIdx.z * T + t0 + i) * N + arow] = v[i];
                         }
                     }
                 }
@@ -271,6 +284,36 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
         __syncwarp();
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"((unsigned)BN) : "memory");
+    }
+}
+
+// adds the K shares up in the order 0 .. splits-1 and finishes the product in the wanted mode
+template <int MODE>
+__global__ void gemm_tc_reduce_kernel(void* __restrict__ Y, const float* __restrict__ part, int T, int N, int ldy,
+                                      int splits) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t total = (size_t)T * N;
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < (MODE == 3 ? total / 2 : total);
+         e += (size_t)gridDim.x * blockDim.x) {
+        if (MODE == 3) {
+            // element e of [T, N/2]: channel c of token t; gate at column (c/8)*16 + c%8, up 8 further
+            const size_t t = e / (N / 2);
+            const int c = (int)(e - t * (N / 2));
+            const size_t g = t * N + (size_t)(c >> 3) * 16 + (c & 7);
+            float sg = 0.f, su = 0.f;
+            for (int s = 0; s < splits; ++s) { sg += part[s * total + g]; su += part[s * total + g + 8]; }
+            ((__nv_bfloat16*)Y)[t * ldy + c] = __float2bfloat16_rn(silu_mul(sg, su));
+        } else {
+            const size_t t = e / N;
+            const int n = (int)(e - t * N);
+            float sum = 0.f;
+            for (int s = 0; s < splits; ++s) sum += part[s * total + e];
+            const size_t off = t * ldy + n;
+            if (MODE == 0) ((__nv_bfloat16*)Y)[off] = __float2bfloat16_rn(sum);
+            else if (MODE == 1) ((float*)Y)[off] += sum;
+            else ((float*)Y)[off] = sum;
+        }
     }
 }
 
@@ -316,15 +359,18 @@ static int make_map(CUtensorMap* m, const void* ptr, int rows, int K, int ld, in
 
 template <int BN, int STAGES, bool SWAP>
 static int launch_tc(void* Y, const void* X, const void* W, int T, int N, int K, int ldx, int ldy, int mode,
-                     cudaStream_t st) {
+                     int ksplit, float* scratch, cudaStream_t st) {
     CUtensorMap mx, mw;
     int rc = make_map(&mx, X, T, K, ldx, SWAP ? BN : TC_BM);
     if (rc) return rc;
     rc = make_map(&mw, W, N, K, K, SWAP ? TC_BM : BN);
     if (rc) return rc;
     const size_t smem = (size_t)STAGES * (TC_BM + BN) * TC_BK * 2 + 1024 + 256;
-    dim3 grid(SWAP ? (N + TC_BM - 1) / TC_BM : (T + TC_BM - 1) / TC_BM, SWAP ? (T + BN - 1) / BN : (N + BN - 1) / BN);
+    dim3 grid(SWAP ? (N + TC_BM - 1) / TC_BM : (T + TC_BM - 1) / TC_BM, SWAP ? (T + BN - 1) / BN : (N + BN - 1) / BN,
+              ksplit);
     ZLM_REQUIRE(grid.y <= 65535, "gemm_tc: the product is too large (T=%d N=%d)", T, N);
+    const int kmode = ksplit > 1 ? 4 : mode;
+    void* dst = ksplit > 1 ? (void*)scratch : Y;
 #define ZLM_TC_LAUNCH(M)                                                                                   \
     {                                                                                                      \
         auto kern = gemm_tc_kernel<BN, STAGES, SWAP, M>;                                                   \
@@ -337,15 +383,38 @@ static int launch_tc(void* Y, const void* X, const void* W, int T, int N, int K,
             }                                                                                              \
             attr_set = true;                                                                               \
         }                                                                                                  \
-        if (SWAP) kern<<<grid, TC_THREADS, smem, st>>>(mw, mx, Y, T, N, K, ldy);                           \
-        else kern<<<grid, TC_THREADS, smem, st>>>(mx, mw, Y, T, N, K, ldy);                                \
+        if (SWAP) zlm_launch(kern, grid, dim3(TC_THREADS), smem, st, mw, mx, dst, T, N, K, ldy);           \
+        else zlm_launch(kern, grid, dim3(TC_THREADS), smem, st, mx, mw, dst, T, N, K, ldy);                \
     }
-    if (mode == 0) ZLM_TC_LAUNCH(0)
-    else if (mode == 1) ZLM_TC_LAUNCH(1)
-    else if (mode == 2) ZLM_TC_LAUNCH(2)
-    else ZLM_TC_LAUNCH(3)
+    if (kmode == 0) ZLM_TC_LAUNCH(0)
+    else if (kmode == 1) ZLM_TC_LAUNCH(1)
+    else if (kmode == 2) ZLM_TC_LAUNCH(2)
+    else if (kmode == 3) ZLM_TC_LAUNCH(3)
+    else if (SWAP) ZLM_TC_LAUNCH(4)
 #undef ZLM_TC_LAUNCH
-    return zlm_check_launch("gemm_tc");
+    rc = zlm_check_launch("gemm_tc");
+    if (rc || ksplit <= 1) return rc;
+    const size_t elems = (size_t)T * N / (mode == 3 ? 2 : 1);
+    int blocks = (int)((elems + 255) / 256);
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    if (mode == 0) zlm_launch(gemm_tc_reduce_kernel<0>, dim3(blocks), dim3(256), 0, st, Y, (const float*)scratch, T, N, ldy, ksplit);
+    else if (mode == 1) zlm_launch(gemm_tc_reduce_kernel<1>, dim3(blocks), dim3(256), 0, st, Y, (const float*)scratch, T, N, ldy, ksplit);
+    else if (mode == 2) zlm_launch(gemm_tc_reduce_kernel<2>, dim3(blocks), dim3(256), 0, st, Y, (const float*)scratch, T, N, ldy, ksplit);
+    else zlm_launch(gemm_tc_reduce_kernel<3>, dim3(blocks), dim3(256), 0, st, Y, (const float*)scratch, T, N, ldy, ksplit);
+    return zlm_check_launch("gemm_tc_reduce");
+}
+
+// Into how many shares the few-token form cuts K so that about one block per SM streams W:
+// 1 (no split) when the grid is large enough already; every share keeps at least 8 k blocks.
+extern "C" int zlm_gemm_tc_ksplit(int T, int N, int K) {
+    if (T > 384) return 1;
+    const int bn = T <= 32 ? 32 : (T <= 64 ? 64 : 128);
+    const int ctas = ((N + TC_BM - 1) / TC_BM) * ((T + bn - 1) / bn);
+    const int kb = (K + TC_BK - 1) / TC_BK;
+    int s = 148 / ctas;
+    if (s > 8) s = 8;
+    while (s > 1 && kb / s < 8) --s;
+    return s < 1 ? 1 : s;
 }
 
 // 1 if the tensor-memory kernel takes this product (else use zlm_gemm_bf16_mma)
@@ -354,19 +423,22 @@ extern "C" int zlm_gemm_tc_supported(int T, int N, int K, int ldx) {
 }
 
 // mode 0: Y bf16 = X W^T; mode 1: Y fp32 += X W^T; mode 2: Y fp32 = X W^T;
-// mode 3: Y bf16 [T, N/2] = silu(gate) * up, W's rows in groups of 8 gate + 8 up (N a multiple of 16)
+// mode 3: Y bf16 [T, N/2] = silu(gate) * up, W's rows in groups of 8 gate + 8 up (N a multiple of 16).
+// scratch: zlm_gemm_tc_ksplit(T, N, K) * T * N floats if that number of shares is more than 1, else unused.
 extern "C" int zlm_gemm_tc(void* Y, const void* X, const void* W, int T, int N, int K, int ldx, int ldy, int mode,
-                           cudaStream_t st) {
+                           float* scratch, cudaStream_t st) {
     if (T == 0 || N == 0) return ZLM_OK;
     ZLM_REQUIRE(zlm_gemm_tc_supported(T, N, K, ldx), "gemm_tc: shape T=%d N=%d K=%d (row stride %d) is not taken", T, N, K, ldx);
     ZLM_REQUIRE(((uintptr_t)X % 16 == 0) && ((uintptr_t)W % 16 == 0), "gemm_tc: operands must be 16-byte aligned");
     ZLM_REQUIRE(mode >= 0 && mode <= 3, "gemm_tc: mode %d", mode);
     ZLM_REQUIRE(mode != 3 || N % 16 == 0, "gemm_tc: the fused gate/up product needs N=%d to be a multiple of 16", N);
+    const int ks = zlm_gemm_tc_ksplit(T, N, K);
+    ZLM_REQUIRE(ks == 1 || scratch, "gemm_tc: scratch for %d shares of K is missing", ks);
     // few tokens: W is the 128-row operand so that it streams at full height
-    if (T <= 32) return launch_tc<32, 8, true>(Y, X, W, T, N, K, ldx, ldy, mode, st);
-    if (T <= 64) return launch_tc<64, 8, true>(Y, X, W, T, N, K, ldx, ldy, mode, st);
-    if (T <= 384) return launch_tc<128, 6, true>(Y, X, W, T, N, K, ldx, ldy, mode, st);
-    return launch_tc<256, 4, false>(Y, X, W, T, N, K, ldx, ldy, mode, st);
+    if (T <= 32) return launch_tc<32, 8, true>(Y, X, W, T, N, K, ldx, ldy, mode, ks, scratch, st);
+    if (T <= 64) return launch_tc<64, 8, true>(Y, X, W, T, N, K, ldx, ldy, mode, ks, scratch, st);
+    if (T <= 384) return launch_tc<128, 6, true>(Y, X, W, T, N, K, ldx, ldy, mode, ks, scratch, st);
+    return launch_tc<256, 4, false>(Y, X, W, T, N, K, ldx, ldy, mode, 1, scratch, st);
 }
 
 // 0 if no bounded wait of the kernel ever gave up; else 1 (producer), 2 (product issuer) or 3 (epilogue).

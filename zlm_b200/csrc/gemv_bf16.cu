@@ -61,16 +61,32 @@ gemv_bf16_kernel(void* __restrict__ Y, const __nv_bfloat16* __restrict__ X,
 #pragma unroll
         for (int r = 0; r < 4; ++r) acc[j][r] = 0.f;
 
-    // warp w takes the 32-wide k blocks w, w + 8, ...; GEMV_UNROLL of them in flight
+    // warp w takes the 32-wide k blocks w, w + 8, ...; GEMV_UNROLL of them in flight.  The
+    // weights do not depend on the kernel before this one: their first loads are issued
+    // before the wait for it, the activations after.
     const int step = GEMV_WARPS * 32;
     int kb = warp * 32;
-    for (; kb + (GEMV_UNROLL - 1) * step + 32 <= K; kb += GEMV_UNROLL * step) {
-        uint4 a[GEMV_UNROLL], b[GEMV_UNROLL], x[GEMV_UNROLL][NT];
+    pdl_launch_dependents();
+    uint4 a[GEMV_UNROLL], b[GEMV_UNROLL];
+    bool have = kb + (GEMV_UNROLL - 1) * step + 32 <= K;
+    if (have) {
 #pragma unroll
         for (int u = 0; u < GEMV_UNROLL; ++u) {
             a[u] = ld_stream16(w0 + kb + u * step);
             b[u] = ld_stream16(w1 + kb + u * step);
         }
+    }
+    pdl_wait();
+    for (; kb + (GEMV_UNROLL - 1) * step + 32 <= K; kb += GEMV_UNROLL * step) {
+        uint4 x[GEMV_UNROLL][NT];
+        if (!have) {
+#pragma unroll
+            for (int u = 0; u < GEMV_UNROLL; ++u) {
+                a[u] = ld_stream16(w0 + kb + u * step);
+                b[u] = ld_stream16(w1 + kb + u * step);
+            }
+        }
+        have = false;
 #pragma unroll
         for (int u = 0; u < GEMV_UNROLL; ++u)
 #pragma unroll
@@ -140,10 +156,10 @@ template <int NT>
 static int launch_gemv(void* Y, const __nv_bfloat16* X, const __nv_bfloat16* W, int T, int N, int K,
                        int ldx, int ldy, int mode, cudaStream_t st) {
     const int blocks = (N + GEMV_ROWS - 1) / GEMV_ROWS;
-    if (mode == 0) gemv_bf16_kernel<NT, 0><<<blocks, GEMV_THREADS, 0, st>>>(Y, X, W, T, N, K, ldx, ldy);
-    else if (mode == 1) gemv_bf16_kernel<NT, 1><<<blocks, GEMV_THREADS, 0, st>>>(Y, X, W, T, N, K, ldx, ldy);
-    else if (mode == 2) gemv_bf16_kernel<NT, 2><<<blocks, GEMV_THREADS, 0, st>>>(Y, X, W, T, N, K, ldx, ldy);
-    else gemv_bf16_kernel<NT, 3><<<blocks, GEMV_THREADS, 0, st>>>(Y, X, W, T, N, K, ldx, ldy);
+    if (mode == 0) zlm_launch(gemv_bf16_kernel<NT, 0>, blocks, GEMV_THREADS, 0, st, Y, X, W, T, N, K, ldx, ldy);
+    else if (mode == 1) zlm_launch(gemv_bf16_kernel<NT, 1>, blocks, GEMV_THREADS, 0, st, Y, X, W, T, N, K, ldx, ldy);
+    else if (mode == 2) zlm_launch(gemv_bf16_kernel<NT, 2>, blocks, GEMV_THREADS, 0, st, Y, X, W, T, N, K, ldx, ldy);
+    else zlm_launch(gemv_bf16_kernel<NT, 3>, blocks, GEMV_THREADS, 0, st, Y, X, W, T, N, K, ldx, ldy);
     return zlm_check_launch("gemv_bf16");
 }
 

@@ -27,6 +27,7 @@ qk_norm_rope_write_kernel(
     float* bufs = sm + 2 * ang;           // [ROPE_WARPS][hd]
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int t = blockIdx.x;
+    pdl_launch_dependents();
     const int pos = token_pos[t];
     for (int i = tid; i < ang; i += ROPE_WARPS * 32) {
         float s, c;
@@ -39,6 +40,7 @@ qk_norm_rope_write_kernel(
     float* buf = bufs + warp * hd;
     int page = 0;
     if (writes_kv) page = block_table[(size_t)token_slot[t] * table_stride + pos / ZLM_PAGE];
+    pdl_wait();             // the table above is the step's own; qkv comes from the kernel before
     const int j_end = min(heads, (int)(blockIdx.y + 1) * heads_per_block);
     for (int j = blockIdx.y * heads_per_block + warp; j < j_end; j += ROPE_WARPS) {
         const int kind = j < nq ? 0 : (j < nq + nkv ? 1 : 2);
@@ -112,7 +114,7 @@ static void launch_rope(void* qkv, int row_stride, VecW qw, VecW kw, int has_nor
     const int heads = nq + 2 * nkv;
     const int hpb = T >= 512 ? heads : ROPE_WARPS;
     dim3 grid(T, (heads + hpb - 1) / hpb);
-    qk_norm_rope_write_kernel<TA, NPL><<<grid, ROPE_WARPS * 32, smem, st>>>(
+    zlm_launch(qk_norm_rope_write_kernel<TA, NPL>, grid, dim3(ROPE_WARPS * 32), smem, st,
         (TA*)qkv, row_stride, qw, kw, has_norm, eps, inv_freq, n_rot, token_pos, token_slot, block_table,
         table_stride, (TA*)pool, nq, nkv, hd, writes_kv, hpb);
 }

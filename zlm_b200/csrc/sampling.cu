@@ -2,47 +2,90 @@
 // index (src/runtime/sampler.zig:14-21).
 #include "common.cuh"
 
-__global__ void __launch_bounds__(1024)
-argmax_kernel(int* __restrict__ out, const float* __restrict__ logits, int V, int ld) {
+#define ARGMAX_CHUNKS 64
+#define ARGMAX_THREADS 256
+
+__device__ __forceinline__ bool argmax_better(float va, int ia, float vb, int ib) {
+    return va > vb || (va == vb && ia < ib);     // higher value wins, equal values keep the lower index
+}
+
+// stage 1: block (row, chunk) finds the best of its chunk of the row
+__global__ void __launch_bounds__(ARGMAX_THREADS)
+argmax_partial_kernel(float* __restrict__ pv, int* __restrict__ pi, const float* __restrict__ logits, int V, int ld) {
     __shared__ float bv[32];
     __shared__ int bi[32];
+    pdl_launch_dependents();
+    pdl_wait();
     const float* row = logits + (size_t)blockIdx.x * ld;
+    const int per = (V + ARGMAX_CHUNKS - 1) / ARGMAX_CHUNKS;
+    const int lo = blockIdx.y * per, hi = min(V, lo + per);
     float best = -INFINITY;
     int idx = 0x7fffffff;
-    for (int i = threadIdx.x; i < V; i += blockDim.x) {
+    for (int i = lo + threadIdx.x; i < hi; i += ARGMAX_THREADS) {
         const float v = row[i];
         if (v > best || idx == 0x7fffffff) { best = v; idx = i; }
     }
-    // (value, index) reduction: higher value wins, equal values keep the lower index
-    auto better = [](float va, int ia, float vb, int ib) { return va > vb || (va == vb && ia < ib); };
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
         const float ov = __shfl_xor_sync(0xffffffffu, best, o);
         const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
-        if (better(ov, oi, best, idx)) { best = ov; idx = oi; }
+        if (argmax_better(ov, oi, best, idx)) { best = ov; idx = oi; }
     }
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     if (lane == 0) { bv[warp] = best; bi[warp] = idx; }
     __syncthreads();
     if (warp == 0) {
-        const int nw = blockDim.x >> 5;
-        best = lane < nw ? bv[lane] : -INFINITY;
-        idx = lane < nw ? bi[lane] : 0x7fffffff;
+        best = lane < ARGMAX_THREADS / 32 ? bv[lane] : -INFINITY;
+        idx = lane < ARGMAX_THREADS / 32 ? bi[lane] : 0x7fffffff;
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) {
             const float ov = __shfl_xor_sync(0xffffffffu, best, o);
             const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
-            if (better(ov, oi, best, idx)) { best = ov; idx = oi; }
+            if (argmax_better(ov, oi, best, idx)) { best = ov; idx = oi; }
         }
-        if (lane == 0) out[blockIdx.x] = idx == 0x7fffffff ? 0 : idx;
+        if (lane == 0) {
+            pv[blockIdx.x * ARGMAX_CHUNKS + blockIdx.y] = best;
+            pi[blockIdx.x * ARGMAX_CHUNKS + blockIdx.y] = idx;      // 0x7fffffff: the chunk is empty
+        }
     }
 }
 
-extern "C" int zlm_argmax(int* out, const float* logits, int R, int V, int ld, cudaStream_t st) {
+// stage 2: one warp per row picks among the chunks' candidates (an empty chunk's index
+// is the largest integer, so it loses every comparison against a real candidate of equal value;
+// its value is -inf, so it loses the others)
+__global__ void __launch_bounds__(32)
+argmax_final_kernel(int* __restrict__ out, const float* __restrict__ pv, const int* __restrict__ pi) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int lane = threadIdx.x;
+    float best = -INFINITY;
+    int idx = 0x7fffffff;
+    for (int c = lane; c < ARGMAX_CHUNKS; c += 32) {
+        const float v = pv[blockIdx.x * ARGMAX_CHUNKS + c];
+        const int i = pi[blockIdx.x * ARGMAX_CHUNKS + c];
+        if (argmax_better(v, i, best, idx)) { best = v; idx = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+        if (argmax_better(ov, oi, best, idx)) { best = ov; idx = oi; }
+    }
+    if (lane == 0) out[blockIdx.x] = idx == 0x7fffffff ? 0 : idx;
+}
+
+// scratch: R * 64 floats and R * 64 ints
+extern "C" int zlm_argmax(int* out, const float* logits, int R, int V, int ld, float* scratch_v, int* scratch_i,
+                          cudaStream_t st) {
     if (R == 0) return ZLM_OK;
     ZLM_REQUIRE(R > 0 && V > 0 && ld >= V, "argmax: bad sizes R=%d V=%d ld=%d", R, V, ld);
-    argmax_kernel<<<R, 1024, 0, st>>>(out, logits, V, ld);
-    return zlm_check_launch("argmax");
+    ZLM_REQUIRE(scratch_v && scratch_i, "argmax: scratch missing");
+    ZLM_REQUIRE(R <= 2147483647 / ARGMAX_CHUNKS, "argmax: too many rows");
+    zlm_launch(argmax_partial_kernel, dim3(R, ARGMAX_CHUNKS), dim3(ARGMAX_THREADS), 0, st, scratch_v, scratch_i, logits, V, ld);
+    int rc = zlm_check_launch("argmax_partial");
+    if (rc) return rc;
+    zlm_launch(argmax_final_kernel, dim3(R), dim3(32), 0, st, out, (const float*)scratch_v, (const int*)scratch_i);
+    return zlm_check_launch("argmax_final");
 }
 
 // ---------------------------------------------------------------------------
@@ -117,6 +160,8 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, int V, in
     __shared__ int sh_krem, sh_int;
     __shared__ double sh_dbl, sh_dbl2;
 
+    pdl_launch_dependents();
+    pdl_wait();
     const int row = blockIdx.x, tid = threadIdx.x;
     const float* l = logits + (size_t)row * ld;
     const int seg = (V + SAMPLE_THREADS - 1) / SAMPLE_THREADS;     // contiguous segment per thread
@@ -308,8 +353,8 @@ extern "C" int zlm_sample(int* out, const float* logits, int R, int V, int ld, f
     ZLM_REQUIRE(R > 0 && V > 0 && ld >= V, "sample: bad sizes R=%d V=%d ld=%d", R, V, ld);
     ZLM_REQUIRE(temperature > 0.f, "sample: temperature must be positive (greedy is argmax)");
     ZLM_REQUIRE(top_k >= 0 && top_p > 0.f, "sample: top_k=%d top_p=%f", top_k, top_p);
-    sample_kernel<<<R, SAMPLE_THREADS, 0, st>>>(out, logits, V, ld, temperature, top_k, top_p, seed, request,
-                                               position);
+    zlm_launch(sample_kernel, R, SAMPLE_THREADS, 0, st, out, logits, V, ld, temperature, top_k, top_p, seed, request,
+               position);
     return zlm_check_launch("sample");
 }
 

@@ -37,7 +37,9 @@
 extern "C" {
 #endif
 
-// Same arguments as zlm_attention_decode without the two scratch pointers.
+// Same arguments as zlm_attention_decode without the two scratch pointers.  Split s of a
+// sequence takes its pages [s * pages_per_split, (s + 1) * pages_per_split); splits *
+// pages_per_split pages (of 64 tokens) must cover the longest sequence.
 // out [T, nq*hd] bf16 (row stride out_stride), q [T, nq*hd] bf16 (row stride
 // q_stride), pool [pages, 2, nkv, 64, hd] bf16, block_table [slots, table_stride]
 // int32, token_pos / token_slot [T] int32.  Returns 0, or non-zero with the
@@ -45,14 +47,14 @@ extern "C" {
 int zlm_attention_decode_static(void* out, int out_stride, const void* q, int q_stride, const void* pool,
                                 const int* block_table, int table_stride, const int* token_pos,
                                 const int* token_slot, int T, int nq, int nkv, int hd, float scale, int window,
-                                int splits, cudaStream_t stream);
+                                int splits, int pages_per_split, cudaStream_t stream);
 
 // The existing entry point, for comparison: the caller passes scratch of
 // T*nq*splits*hd floats (part_o) and T*nq*splits*2 floats (part_ml).
 int zlm_attention_decode(void* out, int out_stride, const void* q, int q_stride, const void* pool,
                          const int* block_table, int table_stride, const int* token_pos, const int* token_slot,
-                         int T, int nq, int nkv, int hd, float scale, int window, int splits, float* part_o,
-                         float* part_ml, cudaStream_t stream);
+                         int T, int nq, int nkv, int hd, float scale, int window, int splits, int pages_per_split,
+                         float* part_o, float* part_ml, cudaStream_t stream);
 
 const char* zlm_last_error(void);
 

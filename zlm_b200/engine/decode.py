@@ -27,6 +27,10 @@ class DecodeRunner:
         self.e = engine
         cuda = engine.device.type == "cuda"
         self.use_graphs = (cuda and engine.model.graph_safe) if use_graphs is None else use_graphs
+        # programmatic dependent launch between the step's kernels: off.  Measured at batch 8,
+        # Qwen3-8B sizes: 5.32 ms a step with early triggers and weight prefetch before the
+        # wait, 4.46 ms with late triggers, 4.49 ms in plain stream order.
+        self.use_pdl = False
         self.graphs: Dict[Tuple, torch.cuda.CUDAGraph] = {}
         self.graph_generation = -1
         self.out = torch.zeros(engine.max_batch, dtype=torch.int32, device=engine.device)
@@ -85,6 +89,16 @@ class DecodeRunner:
 
     # ------------------------------------------------------------------ device work
     def _device_work(self, ctx, R: int, params: SamplingParams) -> None:
+        if self.use_pdl:
+            self.e.rt.k.set_pdl(True)
+            try:
+                self._device_work_inner(ctx, R, params)
+            finally:
+                self.e.rt.k.set_pdl(False)
+        else:
+            self._device_work_inner(ctx, R, params)
+
+    def _device_work_inner(self, ctx, R: int, params: SamplingParams) -> None:
         e = self.e
         logits = e.run_model(ctx, R)
         self.last_logits = logits
@@ -95,17 +109,21 @@ class DecodeRunner:
             e.rt.k.sample(self.out[:R], logits, params.temperature, params.top_k, params.top_p, params.seed,
                           meta[0], meta[1])
 
+    def _generation(self):
+        """Changes whenever a scratch buffer that a captured graph may point at has moved."""
+        return (self.e.rt.ws.generation, getattr(self.e.rt.k, "scratch_generation", 0))
+
     def _replay(self, ctx, R: int, params: SamplingParams) -> None:
         e = self.e
         key = (R, ctx.len_bucket, params)
-        if self.graph_generation != e.rt.ws.generation:
+        if self.graph_generation != self._generation():
             self.graphs.clear()
         g = self.graphs.get(key)
         if g is None:
             # a first eager run creates every scratch buffer the step needs; it also is
             # this step's result, so nothing is computed twice on replayed steps
             self._device_work(ctx, R, params)
-            gen = e.rt.ws.generation
+            gen = self._generation()
             torch.cuda.synchronize()
             g = torch.cuda.CUDAGraph()
             counter = getattr(e.rt.k, "launches", None)
@@ -114,7 +132,7 @@ class DecodeRunner:
                 self._device_work(ctx, R, params)
             if counter:
                 self.launches_per_step = counter() - before
-            if gen != e.rt.ws.generation:
+            if gen != self._generation():
                 raise RuntimeError("scratch buffers moved during graph capture")
             self.graph_generation = gen
             self.graphs[key] = g

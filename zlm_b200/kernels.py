@@ -32,13 +32,19 @@ def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     return torch.stack([gate.view(I // 8, 8, K), up.view(I // 8, 8, K)], dim=1).reshape(2 * I, K).contiguous()
 
 
-def decode_splits(rows: int, nkv: int, len_bucket: int) -> int:
-    """Into how many parts the decode attention cuts a sequence's keys: enough blocks
-    for a few waves over the GPU's 148 SMs (3 blocks each), but at least 4 pages a
-    part.  ``len_bucket`` is the longest sequence of the step in pages, rounded up to
-    a power of two, so that the choice (and a captured graph) holds for many steps."""
-    want = -(-1776 // max(1, rows * nkv))
-    return max(1, min(want, len_bucket // 4))
+def decode_splits(rows: int, nkv: int, len_bucket: int):
+    """How the decode attention cuts a sequence's pages: (splits, pages per split).  The
+    parts are sized so that the grid is about two waves of the GPU (148 SMs x 3 blocks),
+    and are at least two pages long.  ``len_bucket`` is the longest sequence of the step
+    in pages, rounded up to a power of two, so that the choice (and a captured graph)
+    holds for many steps."""
+    per = max(2, -(-len_bucket * rows * nkv // 888))
+    per = min(per, max(1, len_bucket))
+    splits = -(-len_bucket // per)
+    while splits > 1024:
+        per *= 2
+        splits = -(-len_bucket // per)
+    return splits, per
 
 
 def _dt(t: torch.Tensor) -> int:
@@ -68,7 +74,19 @@ class CudaKernels:
         if not torch.cuda.is_available():
             raise KernelError("zlm_b200 needs a CUDA GPU (sm_100a); none is visible and there is no CPU path")
         self._fn = {}
+        self._scratch = {}
+        self.scratch_generation = 0
         self._launches = 0
+
+    def scratch(self, name: str, n: int, dtype: torch.dtype, device) -> torch.Tensor:
+        """Scratch memory that a kernel needs beyond its operands.  It grows when asked for
+        more and keeps its address otherwise; ``scratch_generation`` counts the moves, so
+        that a captured graph that holds an old address is not replayed."""
+        buf = self._scratch.get(name)
+        if buf is None or buf.numel() < n or buf.dtype != dtype or buf.device != device:
+            self._scratch[name] = buf = torch.empty(max(n, 1 << 16), dtype=dtype, device=device)
+            self.scratch_generation += 1
+        return buf
 
     def launches(self) -> int:
         """Kernel launches issued through this object so far."""
@@ -148,7 +166,14 @@ class CudaKernels:
     def _bf16_product(self, out, x, w, T, N, K, ldx, ldy, mode, impl) -> None:
         if impl is None:
             impl = "gemv" if T <= 16 else ("tc" if self.lib.zlm_gemm_tc_supported(T, N, K, ldx) else "mma")
-        name = {"gemv": "zlm_gemv_bf16", "mma": "zlm_gemm_bf16_mma", "tc": "zlm_gemm_tc"}[impl]
+        if impl == "tc":
+            ks = self.lib.zlm_gemm_tc_ksplit(T, N, K)
+            scratch = self.scratch("gemm_tc.partials", ks * T * N, torch.float32, out.device) if ks > 1 else None
+            self._call("zlm_gemm_tc", c_void_p(out.data_ptr()), c_void_p(x.data_ptr()), c_void_p(w.data_ptr()),
+                       c_int(T), c_int(N), c_int(K), c_int(ldx), c_int(ldy), c_int(mode), c_void_p(_ptr(scratch)),
+                       self._stream())
+            return
+        name = {"gemv": "zlm_gemv_bf16", "mma": "zlm_gemm_bf16_mma"}[impl]
         self._call(name, c_void_p(out.data_ptr()), c_void_p(x.data_ptr()), c_void_p(w.data_ptr()),
                    c_int(T), c_int(N), c_int(K), c_int(ldx), c_int(ldy), c_int(mode), self._stream())
 
@@ -206,7 +231,7 @@ class CudaKernels:
         assert tuple(pool.shape[1:]) == (2, nkv, PAGE_TOKENS, hd)
         if (plan is not None and plan.is_decode and q.dtype == torch.bfloat16
                 and self.lib.zlm_attention_decode_supported(nq, nkv, hd)):
-            splits = decode_splits(T, nkv, plan.len_bucket)
+            splits, per = decode_splits(T, nkv, plan.len_bucket)
             part_o = part_ml = None
             if splits > 1:
                 part_o = plan.scratch("attn.part_o", (T * nq * splits * hd,), torch.float32)
@@ -215,7 +240,7 @@ class CudaKernels:
                        c_void_p(q.data_ptr()), c_int(q.stride(0)), c_void_p(pool.data_ptr()),
                        c_void_p(block_table.data_ptr()), c_int(block_table.stride(0)),
                        c_void_p(token_pos.data_ptr()), c_void_p(token_slot.data_ptr()), c_int(T), c_int(nq),
-                       c_int(nkv), c_int(hd), c_float(scale), c_int(window), c_int(splits),
+                       c_int(nkv), c_int(hd), c_float(scale), c_int(window), c_int(splits), c_int(per),
                        c_void_p(_ptr(part_o)), c_void_p(_ptr(part_ml)), self._stream())
             return
         if (plan is not None and not plan.is_decode and q.dtype == torch.bfloat16
@@ -238,8 +263,16 @@ class CudaKernels:
         """out[r] = index of the highest logit of row r, ties to the lowest index."""
         R, V = logits.shape
         assert logits.dtype == torch.float32 and logits.stride(1) == 1 and out.dtype == torch.int32
+        sv = self.scratch("argmax.values", R * 64, torch.float32, logits.device)
+        si = self.scratch("argmax.indices", R * 64, torch.int32, logits.device)
         self._call("zlm_argmax", c_void_p(out.data_ptr()), c_void_p(logits.data_ptr()), c_int(R), c_int(V),
-                   c_int(logits.stride(0)), self._stream())
+                   c_int(logits.stride(0)), c_void_p(sv.data_ptr()), c_void_p(si.data_ptr()), self._stream())
+
+    def set_pdl(self, on: bool) -> None:
+        """Launch the decode-path kernels with programmatic dependent launch (a kernel's
+        blocks are scheduled, and its weights start streaming, while the kernel before it
+        drains) or in plain stream order."""
+        self.lib.zlm_set_pdl(c_int(1 if on else 0))
 
     def gemm_tc_status(self) -> int:
         """0 unless a bounded wait inside the tcgen05 GEMM ever gave up (synchronises)."""
