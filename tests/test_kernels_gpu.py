@@ -266,9 +266,11 @@ class PrefillPlan:
         self.len_bucket = 1
 
 
+@pytest.mark.parametrize("impl", ["mma", None])
 @pytest.mark.parametrize("nq,nkv,hd,window", [(4, 2, 16, 0), (6, 2, 48, 24), (5, 5, 80, 0), (8, 1, 128, 100),
-                                              (32, 8, 128, 0), (6, 3, 32, 70), (4, 1, 64, 64)])
-def test_attention_prefill_kernel(K, nq, nkv, hd, window):
+                                              (32, 8, 128, 0), (6, 3, 32, 70), (4, 1, 64, 64), (3, 3, 128, 0),
+                                              (4, 2, 128, 17)])
+def test_attention_prefill_kernel(K, nq, nkv, hd, window, impl):
     """Tiles of query tokens over the paged cache: whole prompts, a chunk that
     continues a cached prefix, a single token, tile and page edges; a far key
     dominates one head of the last query of the first sequence."""
@@ -289,8 +291,10 @@ def test_attention_prefill_kernel(K, nq, nkv, hd, window):
     want = torch.empty(T, nq * hd, dtype=dt)
     PlainKernels().attention(want, q, pool, table, pos, slot, nq, nkv, hd, scale, window)
     got = torch.empty(T, nq * hd, dtype=dt, device="cuda")
-    K.attention(got, q.cuda(), pool.cuda(), table.cuda(), pos.cuda(), slot.cuda(), nq, nkv, hd, scale, window,
-                PrefillPlan(slots, starts, news))
+    plan = PrefillPlan(slots, starts, news)
+    plan.attention_impl = impl          # None: the tcgen05 kernel where it takes the shape (head size 128)
+    K.attention(got, q.cuda(), pool.cuda(), table.cuda(), pos.cuda(), slot.cuda(), nq, nkv, hd, scale, window, plan)
+    assert K.gemm_tc_status() == 0
     close(got, want, dt, atol=3e-2, rtol=3e-2)
     vfar = pool[page, 1, nkv - 1, far % PAGE, :].float()
     assert (got[299, (nq - 1) * hd:].float().cpu() - vfar).abs().max() < 0.05 * vfar.abs().max() + 0.05

@@ -22,83 +22,58 @@
 // out_i = sum_j W[i,j] x_j with bf16 operands and fp32 accumulation
 // (src/kernels/linear/matvec/kernels/bfloat.zig:43-67; the reference's batched
 // product: src/kernels/linear/matmul/root.zig:62-81).
-#include "common.cuh"
-#include <cuda.h>
-
-#define TC_BM 128
-#define TC_BK 64
-#define TC_THREADS 192
-#define TC_WAIT_LIMIT (1u << 24)
-
-__device__ int g_gemm_tc_error = 0;
-
-// ---------------------------------------------------------------- PTX wrappers
-__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, unsigned count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, unsigned bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try(uint64_t* bar, unsigned parity) {
-    unsigned ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
-        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
-    return ok != 0;
-}
-// bounded wait; false if it gave up (or another role already did)
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity, volatile int* abort_flag, int where) {
-    for (unsigned it = 0; it < TC_WAIT_LIMIT; ++it) {
-        if (mbar_try(bar, parity)) return true;
-        if (*abort_flag) return false;
-    }
-    *abort_flag = where;
-    atomicCAS(&g_gemm_tc_error, 0, where);
-    return false;
-}
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n"
-        ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void tc_mma(unsigned tmem_d, uint64_t desc_a, uint64_t desc_b, unsigned idesc, unsigned accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
-        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void tc_ld16(unsigned taddr, float* v) {
-    unsigned r[16];
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];\n"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-        : "r"(taddr) : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
-}
-
-// shared-memory operand descriptor: K-major tile whose rows are 128 bytes, 128-byte
-// swizzle; 8-row groups are 1024 bytes apart.  Fields in units of 16 bytes.
-__device__ __forceinline__ uint64_t make_desc(unsigned smem_addr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);     // start address
-    d |= (uint64_t)1 << 16;                          // leading byte offset (unused for this layout)
-    d |= (uint64_t)(1024 >> 4) << 32;                // stride byte offset: 8 rows x 128 bytes
-    d |= (uint64_t)1 << 46;                          // descriptor version of this architecture
-    d |= (uint64_t)2 << 61;                          // 128-byte swizzle
-    return d;
-}
+#include "tc_common.cuh"
 
 __device__ __forceinline__ float silu_mul(float g, float u) { return (g / (1.0f + expf(-g))) * u; }
+
+// a thread's 16 consecutive outputs (columns n .. n+15) of token `row` in the wanted mode
+template <int MODE>
+__device__ __forceinline__ void store_row16(const float* v, void* Y, int row, int n, int T, int N, int ldy) {
+    if (row >= T || n >= N) return;
+    const bool whole = n + 16 <= N;
+    __nv_bfloat162 t;
+#define ZLM_PK(a, b) (t = __floats2bfloat162_rn(a, b), *(unsigned*)&t)
+    if (MODE == 3) {
+        __nv_bfloat16* y = (__nv_bfloat16*)Y + (size_t)row * ldy + n / 2;
+        if (whole && ((uintptr_t)y & 15) == 0) {
+            uint4 p;
+            p.x = ZLM_PK(silu_mul(v[0], v[8]), silu_mul(v[1], v[9]));
+            p.y = ZLM_PK(silu_mul(v[2], v[10]), silu_mul(v[3], v[11]));
+            p.z = ZLM_PK(silu_mul(v[4], v[12]), silu_mul(v[5], v[13]));
+            p.w = ZLM_PK(silu_mul(v[6], v[14]), silu_mul(v[7], v[15]));
+            *(uint4*)y = p;
+        } else if (whole) {
+            for (int i = 0; i < 8; ++i) y[i] = __float2bfloat16_rn(silu_mul(v[i], v[8 + i]));
+        }
+    } else if (MODE == 0) {
+        __nv_bfloat16* y = (__nv_bfloat16*)Y + (size_t)row * ldy + n;
+        if (whole && ((uintptr_t)y & 15) == 0) {
+            uint4 p0, p1;
+            p0.x = ZLM_PK(v[0], v[1]); p0.y = ZLM_PK(v[2], v[3]); p0.z = ZLM_PK(v[4], v[5]); p0.w = ZLM_PK(v[6], v[7]);
+            p1.x = ZLM_PK(v[8], v[9]); p1.y = ZLM_PK(v[10], v[11]); p1.z = ZLM_PK(v[12], v[13]); p1.w = ZLM_PK(v[14], v[15]);
+            *(uint4*)y = p0;
+            *(uint4*)(y + 8) = p1;
+        } else {
+            for (int i = 0; i < 16 && n + i < N; ++i) y[i] = __float2bfloat16_rn(v[i]);
+        }
+    } else {
+        float* y = (float*)Y + (size_t)row * ldy + n;
+        if (whole && ((uintptr_t)y & 15) == 0) {
+#pragma unroll
+            for (int i = 0; i < 16; i += 4) {
+                float4 o = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
+                if (MODE == 1) {
+                    const float4 old = *(const float4*)(y + i);
+                    o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+                }
+                *(float4*)(y + i) = o;
+            }
+        } else {
+            for (int i = 0; i < 16 && n + i < N; ++i) y[i] = MODE == 1 ? y[i] + v[i] : v[i];
+        }
+    }
+#undef ZLM_PK
+}
 
 // MODE 0: Y bf16 = acc; MODE 1: Y fp32 += acc; MODE 2: Y fp32 = acc;
 // MODE 3: the outputs come in groups of 16 = 8 gate + 8 up channels; Y bf16 [T, N/2] = silu(gate) * up;
@@ -201,53 +176,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     for (int i = 0; i < 16; ++i) v[i] = 0.f;     // a share of K with nothing in it
                 }
                 if (!SWAP) {
-                    // this thread: token arow, outputs b0row + c .. + 15
-                    const int n = b0row + c;
-                    if (arow >= T || n >= N) continue;
-                    const bool whole = n + 16 <= N;
-                    if (MODE == 3) {
-                        __nv_bfloat16* y = (__nv_bfloat16*)Y + (size_t)arow * ldy + n / 2;
-                        if (whole && ((uintptr_t)y & 15) == 0) {
-                            uint4 p;
-                            __nv_bfloat162 t;
-#define ZLM_PK(a, b) (t = __floats2bfloat162_rn(a, b), *(unsigned*)&t)
-                            p.x = ZLM_PK(silu_mul(v[0], v[8]), silu_mul(v[1], v[9]));
-                            p.y = ZLM_PK(silu_mul(v[2], v[10]), silu_mul(v[3], v[11]));
-                            p.z = ZLM_PK(silu_mul(v[4], v[12]), silu_mul(v[5], v[13]));
-                            p.w = ZLM_PK(silu_mul(v[6], v[14]), silu_mul(v[7], v[15]));
-                            *(uint4*)y = p;
-                        } else if (whole) {
-                            for (int i = 0; i < 8; ++i) y[i] = __float2bfloat16_rn(silu_mul(v[i], v[8 + i]));
-                        }
-                    } else if (MODE == 0) {
-                        __nv_bfloat16* y = (__nv_bfloat16*)Y + (size_t)arow * ldy + n;
-                        if (whole && ((uintptr_t)y & 15) == 0) {
-                            uint4 p0, p1;
-                            __nv_bfloat162 t;
-                            p0.x = ZLM_PK(v[0], v[1]); p0.y = ZLM_PK(v[2], v[3]); p0.z = ZLM_PK(v[4], v[5]); p0.w = ZLM_PK(v[6], v[7]);
-                            p1.x = ZLM_PK(v[8], v[9]); p1.y = ZLM_PK(v[10], v[11]); p1.z = ZLM_PK(v[12], v[13]); p1.w = ZLM_PK(v[14], v[15]);
-#undef ZLM_PK
-                            *(uint4*)y = p0;
-                            *(uint4*)(y + 8) = p1;
-                        } else {
-                            for (int i = 0; i < 16 && n + i < N; ++i) y[i] = __float2bfloat16_rn(v[i]);
-                        }
-                    } else {
-                        float* y = (float*)Y + (size_t)arow * ldy + n;
-                        if (whole && ((uintptr_t)y & 15) == 0) {
-#pragma unroll
-                            for (int i = 0; i < 16; i += 4) {
-                                float4 o = make_float4(v[i], v[i + 1], v[i + 2], v[i + 3]);
-                                if (MODE == 1) {
-                                    const float4 old = *(const float4*)(y + i);
-                                    o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
-                                }
-                                *(float4*)(y + i) = o;
-                            }
-                        } else {
-                            for (int i = 0; i < 16 && n + i < N; ++i) y[i] = MODE == 1 ? y[i] + v[i] : v[i];
-                        }
-                    }
+                    store_row16<MODE>(v, Y, arow, b0row + c, T, N, ldy);
                 } else {
                     // this thread: output arow, tokens b0row + c .. + 15; a warp's lanes are 32
                     // neighbouring outputs, so every token's store is one coalesced line
@@ -287,6 +216,130 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     }
 }
 
+// ---------------------------------------------------------------------------
+// The many-token form as a persistent kernel: one block per SM walks the 128 x 256
+// tiles of Y (token tiles fastest, so that blocks that run together share a tile of
+// W).  Tensor memory holds two accumulators; while the epilogue warps drain one,
+// the product warp already fills the other, and the TMA ring never stops between
+// tiles.  acc_full[b] / acc_empty[b] hand accumulator b back and forth.
+// ---------------------------------------------------------------------------
+template <int BN, int STAGES, int MODE>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                          void* __restrict__ Y, int T, int N, int K, int ldy) {
+    constexpr unsigned A_BYTES = TC_BM * TC_BK * 2, B_BYTES = BN * TC_BK * 2;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    unsigned char* sA = smem;
+    unsigned char* sB = smem + STAGES * A_BYTES;
+    uint64_t* full = (uint64_t*)(sB + STAGES * B_BYTES);
+    uint64_t* empty = full + STAGES;
+    uint64_t* acc_full = empty + STAGES;       // [2]
+    uint64_t* acc_empty = acc_full + 2;        // [2]
+    unsigned* tmem_slot = (unsigned*)(acc_empty + 2);
+    volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int KB = (K + TC_BK - 1) / TC_BK;
+    const int m_tiles = (T + TC_BM - 1) / TC_BM, n_tiles = (N + BN - 1) / BN;
+    const int tiles = m_tiles * n_tiles;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n"
+                     ::"r"(smem_u32(tmem_slot)), "r"((unsigned)(2 * BN)) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const unsigned tmem_base = *tmem_slot;
+    pdl_launch_dependents();
+    pdl_wait();
+
+    if (warp == 0) {
+        if (lane == 0) {
+            unsigned it = 0;            // k blocks issued so far, over all tiles
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
+                const int a0row = (tile % m_tiles) * TC_BM, b0row = (tile / m_tiles) * BN;
+                for (int kb = 0; kb < KB; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    if (!mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1, abort_flag, 1)) { ok = false; break; }
+                    mbar_expect_tx(&full[s], A_BYTES + B_BYTES);
+                    tma_load_2d(sA + s * A_BYTES, &map_a, kb * TC_BK, a0row, &full[s]);
+                    tma_load_2d(sB + s * B_BYTES, &map_b, kb * TC_BK, b0row, &full[s]);
+                }
+            }
+            if (*abort_flag) {
+                // copies may still be landing in this block's shared memory: wait for them (bounded)
+                for (unsigned j = it > (unsigned)STAGES ? it - STAGES : 0; j < it; ++j)
+                    for (unsigned w = 0; w < TC_WAIT_LIMIT; ++w)
+                        if (mbar_try(&full[j % STAGES], (j / STAGES) & 1)) break;
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(BN >> 3) << 17) |
+                                   ((unsigned)(TC_BM >> 4) << 24);
+            unsigned it = 0, local = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x, ++local) {
+                const unsigned buf = local & 1;
+                // the epilogue must have drained this accumulator (two tiles ago)
+                ok = mbar_wait(&acc_empty[buf], ((local >> 1) & 1) ^ 1, abort_flag, 4);
+                if (!ok) break;
+                tc_fence_after();
+                for (int kb = 0; kb < KB; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    ok = mbar_wait(&full[s], (it / STAGES) & 1, abort_flag, 2);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const unsigned a0 = smem_u32(sA + s * A_BYTES), b0 = smem_u32(sB + s * B_BYTES);
+#pragma unroll
+                    for (int k = 0; k < TC_BK / 16; ++k)
+                        tc_mma(tmem_base + buf * BN, make_desc(a0 + k * 32), make_desc(b0 + k * 32), idesc, (kb | k) != 0);
+                    tc_commit(&empty[s]);
+                }
+                tc_commit(&acc_full[buf]);
+            }
+            if (!ok) { tc_commit(&acc_full[0]); tc_commit(&acc_full[1]); }     // let the epilogue out
+        }
+    } else {
+        const int lg = warp & 3;
+        unsigned local = 0;
+        for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++local) {
+            const unsigned buf = local & 1;
+            const int a0row = (tile % m_tiles) * TC_BM, b0row = (tile / m_tiles) * BN;
+            const bool ok = mbar_wait(&acc_full[buf], (local >> 1) & 1, abort_flag, 3);
+            tc_fence_after();
+            if (!ok || *abort_flag) break;
+            const int arow = a0row + lg * 32 + lane;
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 16) {
+                float v[16];
+                tc_ld16(tmem_base + ((unsigned)(lg * 32) << 16) + buf * BN + (unsigned)c, v);
+                store_row16<MODE>(v, Y, arow, b0row + c, T, N, ldy);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[buf]);      // one arrival per epilogue warp
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"((unsigned)(2 * BN)) : "memory");
+    }
+}
+
 // adds the K shares up in the order 0 .. splits-1 and finishes the product in the wanted mode
 template <int MODE>
 __global__ void gemm_tc_reduce_kernel(void* __restrict__ Y, const float* __restrict__ part, int T, int N, int ldy,
@@ -318,12 +371,8 @@ __global__ void gemm_tc_reduce_kernel(void* __restrict__ Y, const float* __restr
 }
 
 // ---------------------------------------------------------------- host side
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn get_encode() {
-    static EncodeTiledFn fn = nullptr;
+ZlmEncodeTiledFn zlm_tensor_map_encoder() {
+    static ZlmEncodeTiledFn fn = nullptr;
     static bool tried = false;
     if (!tried) {
         tried = true;
@@ -331,30 +380,34 @@ static EncodeTiledFn get_encode() {
         cudaDriverEntryPointQueryResult q;
         if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
             q == cudaDriverEntryPointSuccess)
-            fn = (EncodeTiledFn)p;
+            fn = (ZlmEncodeTiledFn)p;
     }
     return fn;
 }
 
-// rows x K bf16 matrix, row stride ld elements; box = box_rows x 64 elements, 128-byte swizzle, zero fill
-static int make_map(CUtensorMap* m, const void* ptr, int rows, int K, int ld, int box_rows) {
-    EncodeTiledFn enc = get_encode();
+int zlm_make_map_2d(CUtensorMap* m, const void* ptr, long long rows, int cols, long long ld, int box_rows, int box_cols) {
+    ZlmEncodeTiledFn enc = zlm_tensor_map_encoder();
     if (!enc) {
-        zlm_set_error("gemm_tc: the driver does not provide cuTensorMapEncodeTiled");
+        zlm_set_error("tensor map: the driver does not provide cuTensorMapEncodeTiled");
         return ZLM_ERR_CUDA;
     }
-    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
     cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-    cuuint32_t box[2] = {TC_BK, (cuuint32_t)box_rows};
+    cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
     cuuint32_t estr[2] = {1, 1};
     CUresult r = enc(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (void*)ptr, dims, strides, box, estr,
                      CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) {
-        zlm_set_error("gemm_tc: cuTensorMapEncodeTiled failed with %d (rows=%d K=%d ld=%d)", (int)r, rows, K, ld);
+        zlm_set_error("tensor map: cuTensorMapEncodeTiled failed with %d (rows=%lld cols=%d ld=%lld)", (int)r, rows, cols, ld);
         return ZLM_ERR_CUDA;
     }
     return ZLM_OK;
+}
+
+// rows x K bf16 matrix, row stride ld elements; box = box_rows x 64 elements
+static int make_map(CUtensorMap* m, const void* ptr, int rows, int K, int ld, int box_rows) {
+    return zlm_make_map_2d(m, ptr, rows, K, ld, box_rows, TC_BK);
 }
 
 template <int BN, int STAGES, bool SWAP>
@@ -404,6 +457,49 @@ static int launch_tc(void* Y, const void* X, const void* W, int T, int N, int K,
     return zlm_check_launch("gemm_tc_reduce");
 }
 
+static int sm_count() {
+    static int n = 0;
+    if (!n) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+            n = 148;
+    }
+    return n;
+}
+
+template <int BN, int STAGES>
+static int launch_tc_persistent(void* Y, const void* X, const void* W, int T, int N, int K, int ldx, int ldy, int mode,
+                                cudaStream_t st) {
+    CUtensorMap mx, mw;
+    int rc = make_map(&mx, X, T, K, ldx, TC_BM);
+    if (rc) return rc;
+    rc = make_map(&mw, W, N, K, K, BN);
+    if (rc) return rc;
+    const size_t smem = (size_t)STAGES * (TC_BM + BN) * TC_BK * 2 + 1024 + 256;
+    const long long tiles = (long long)((T + TC_BM - 1) / TC_BM) * ((N + BN - 1) / BN);
+    const int blocks = (int)(tiles < sm_count() ? tiles : sm_count());
+#define ZLM_TCP_LAUNCH(M)                                                                                  \
+    {                                                                                                      \
+        auto kern = gemm_tc_persistent_kernel<BN, STAGES, M>;                                              \
+        static bool attr_set = false;                                                                      \
+        if (!attr_set) {                                                                                   \
+            cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            if (e != cudaSuccess) {                                                                        \
+                zlm_set_error("gemm_tc: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e)); \
+                return ZLM_ERR_CUDA;                                                                       \
+            }                                                                                              \
+            attr_set = true;                                                                               \
+        }                                                                                                  \
+        zlm_launch(kern, dim3(blocks), dim3(TC_THREADS), smem, st, mx, mw, Y, T, N, K, ldy);               \
+    }
+    if (mode == 0) ZLM_TCP_LAUNCH(0)
+    else if (mode == 1) ZLM_TCP_LAUNCH(1)
+    else if (mode == 2) ZLM_TCP_LAUNCH(2)
+    else ZLM_TCP_LAUNCH(3)
+#undef ZLM_TCP_LAUNCH
+    return zlm_check_launch("gemm_tc_persistent");
+}
+
 // Into how many shares the few-token form cuts K so that about one block per SM streams W:
 // 1 (no split) when the grid is large enough already; every share keeps at least 8 k blocks.
 extern "C" int zlm_gemm_tc_ksplit(int T, int N, int K) {
@@ -438,13 +534,13 @@ extern "C" int zlm_gemm_tc(void* Y, const void* X, const void* W, int T, int N, 
     if (T <= 32) return launch_tc<32, 8, true>(Y, X, W, T, N, K, ldx, ldy, mode, ks, scratch, st);
     if (T <= 64) return launch_tc<64, 8, true>(Y, X, W, T, N, K, ldx, ldy, mode, ks, scratch, st);
     if (T <= 384) return launch_tc<128, 6, true>(Y, X, W, T, N, K, ldx, ldy, mode, ks, scratch, st);
-    return launch_tc<256, 4, false>(Y, X, W, T, N, K, ldx, ldy, mode, 1, scratch, st);
+    return launch_tc_persistent<256, 4>(Y, X, W, T, N, K, ldx, ldy, mode, st);
 }
 
 // 0 if no bounded wait of the kernel ever gave up; else 1 (producer), 2 (product issuer) or 3 (epilogue).
 // Synchronises the device.
 extern "C" int zlm_gemm_tc_status() {
     int v = 0;
-    if (cudaMemcpyFromSymbol(&v, g_gemm_tc_error, sizeof(int)) != cudaSuccess) return -1;
+    if (cudaMemcpyFromSymbol(&v, g_tc_error, sizeof(int)) != cudaSuccess) return -1;
     return v;
 }

@@ -246,6 +246,16 @@ class CudaKernels:
         if (plan is not None and not plan.is_decode and q.dtype == torch.bfloat16
                 and getattr(plan, "cu_seqlens", None) is not None
                 and self.lib.zlm_attention_prefill_supported(nq, nkv, hd)):
+            impl = getattr(plan, "attention_impl", None)
+            if impl != "mma" and self.lib.zlm_attention_prefill_tc_supported(nq, nkv, hd, q.stride(0), out.stride(0)):
+                self._call("zlm_attention_prefill_tc", c_void_p(out.data_ptr()), c_int(out.stride(0)),
+                           c_void_p(q.data_ptr()), c_int(q.stride(0)), c_int(T), c_void_p(pool.data_ptr()),
+                           ctypes.c_longlong(pool.shape[0]), c_void_p(block_table.data_ptr()),
+                           c_int(block_table.stride(0)), c_void_p(plan.cu_seqlens.data_ptr()),
+                           c_void_p(plan.seq_slot.data_ptr()), c_void_p(plan.seq_start.data_ptr()), c_int(plan.R),
+                           c_int(plan.max_new), c_int(nq), c_int(nkv), c_int(hd), c_float(scale), c_int(window),
+                           self._stream())
+                return
             self._call("zlm_attention_prefill", c_void_p(out.data_ptr()), c_int(out.stride(0)),
                        c_void_p(q.data_ptr()), c_int(q.stride(0)), c_void_p(pool.data_ptr()),
                        c_void_p(block_table.data_ptr()), c_int(block_table.stride(0)),
@@ -275,8 +285,9 @@ class CudaKernels:
         self.lib.zlm_set_pdl(c_int(1 if on else 0))
 
     def gemm_tc_status(self) -> int:
-        """0 unless a bounded wait inside the tcgen05 GEMM ever gave up (synchronises)."""
-        return int(self.lib.zlm_gemm_tc_status())
+        """0 unless a bounded wait inside a tcgen05 kernel (product or attention) ever gave up
+        (synchronises)."""
+        return int(self.lib.zlm_gemm_tc_status()) or int(self.lib.zlm_attention_tc_status())
 
     def sample(self, out: torch.Tensor, logits: torch.Tensor, temperature: float, top_k: int, top_p: float,
                seed: int, request: torch.Tensor, position: torch.Tensor) -> None:
