@@ -1,11 +1,15 @@
 // Prefill attention on the 5th-generation tensor cores, head size 128, bf16 paged cache.
 //
-// A block owns 128 query tokens of one sequence and one query head and walks the
-// sequence's pages (64 keys each) that these tokens may see.
-//   warp 0      TMA producer: the Q tile once, then a ring of (K page, V page) tiles
-//   warp 1      issues S = Q K^T (128 x 64, fp32 in tensor memory, two S buffers) and
-//               O += P V (128 x 128 in tensor memory) with tcgen05.mma
-//   warps 2..5  softmax: thread = query row.  They read S from tensor memory, mask by the
+// A block owns 128 query tokens of one sequence and HPC (1 or 2) query heads of one kv
+// group, and walks the sequence's pages (64 keys each) that these tokens may see; the
+// heads of a block share the K and V tiles in shared memory, and while the softmax
+// warps of one head work, the tensor cores serve the other.
+//   warp 0      TMA producer: the Q tiles once, then a ring of (K page, V page) tiles
+//   1 warp per head: one thread of it issues that head's S = Q K^T (128 x 64, fp32 in
+//               tensor memory, two S buffers) and O += P V (128 x 128 in tensor memory)
+//               with tcgen05.mma (issuing a product costs one thread about 70 cycles, so
+//               the heads do not share an issuer)
+//   4 warps per head: softmax, thread = query row.  They read S from tensor memory, mask by the
 //               row's own position and window, keep a running maximum and sum in fp32,
 //               write P as bf16 into shared memory in the layout the second product
 //               wants, and at the end scale O by 1/sum and store it.
@@ -24,47 +28,58 @@
 #define FA_BM 128          // query rows per block
 #define FA_HD 128          // head size this kernel is built for
 #define FA_STAGES 3
-#define FA_THREADS 192
 #define FA_RESCALE 8.0f    // log2 units
 
+
+// 2^x on the special-function unit; the arguments here are at most 2^8 after the lazy rescale
+__device__ __forceinline__ float fa_ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;\n" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ unsigned fa_pack(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *(unsigned*)&v;
 }
 
-__global__ void __launch_bounds__(FA_THREADS, 1)
+template <int HPC>
+__global__ void __launch_bounds__(32 + 160 * HPC, 1)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
                             __nv_bfloat16* __restrict__ out, int out_stride, const int* __restrict__ block_table,
                             int table_stride, const int* __restrict__ cu_seqlens, const int* __restrict__ seq_slot,
-                            const int* __restrict__ seq_start, int tiles_per_seq, int nq, int nkv, float scale_log2,
-                            int window) {
+                            const int* __restrict__ seq_start, int R, int tiles_per_seq, int nq, int nkv,
+                            float scale_log2, int window) {
     constexpr unsigned Q_BYTES = FA_BM * FA_HD * 2;                 // two halves of [128][64]
     constexpr unsigned KV_BYTES = ZLM_PAGE * FA_HD * 2;             // K or V: two halves of [64][64]
     constexpr unsigned P_BYTES = FA_BM * ZLM_PAGE * 2;              // [128][64]
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-    unsigned char* sQ = smem;
-    unsigned char* sK = sQ + Q_BYTES;
+    unsigned char* sQ = smem;                                       // [HPC] Q tiles
+    unsigned char* sK = sQ + HPC * Q_BYTES;
     unsigned char* sV = sK + FA_STAGES * KV_BYTES;
-    unsigned char* sP = sV + FA_STAGES * KV_BYTES;                  // two P buffers
-    uint64_t* q_full = (uint64_t*)(sP + 2 * P_BYTES);
-    uint64_t* kv_full = q_full + 1;            // [STAGES]  TMA bytes landed
-    uint64_t* kv_empty = kv_full + FA_STAGES;  // [STAGES]  O += P V of that page retired
-    uint64_t* s_full = kv_empty + FA_STAGES;   // [2]       S = Q K^T retired
-    uint64_t* s_empty = s_full + 2;            // [2]       softmax has read S
-    uint64_t* p_full = s_empty + 2;            // [2]       P written (and O rescaled if needed)
-    uint64_t* pv_done = p_full + 2;            // [1]       an O += P V retired
-    unsigned* tmem_slot = (unsigned*)(pv_done + 1);
+    unsigned char* sP = sV + FA_STAGES * KV_BYTES;                  // [HPC][2] P buffers
+    uint64_t* q_full = (uint64_t*)(sP + HPC * 2 * P_BYTES);
+    uint64_t* kv_full = q_full + 1;            // [STAGES]   TMA bytes landed
+    uint64_t* kv_empty = kv_full + FA_STAGES;  // [STAGES]   every head's O += P V of that page retired
+    uint64_t* s_full = kv_empty + FA_STAGES;   // [HPC][2]   S = Q K^T retired
+    uint64_t* s_empty = s_full + 2 * HPC;      // [HPC][2]   softmax has read S
+    uint64_t* p_full = s_empty + 2 * HPC;      // [HPC][2]   P written (and O rescaled if needed)
+    uint64_t* pv_done = p_full + 2 * HPC;      // [HPC]      an O += P V of that head retired
+    unsigned* tmem_slot = (unsigned*)(pv_done + HPC);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int r = blockIdx.x / tiles_per_seq, b = blockIdx.x % tiles_per_seq;
-    const int head = blockIdx.y;
+    // blocks are numbered so that the tiles with the most pages (the last rows of the longest
+    // prompts) start first and the short ones fill the gaps at the end
+    const int n_hb = nq / HPC;                 // head groups
+    const int rank = blockIdx.x / n_hb;        // 0 = the last tile of a sequence
+    const int b = tiles_per_seq - 1 - rank / R, r = rank % R;
+    const int head0 = (blockIdx.x % n_hb) * HPC;   // the block's first query head; its heads share a kv head
     const int tok0 = cu_seqlens[r], n_new = cu_seqlens[r + 1] - tok0;
     const int row0 = b * FA_BM;
     if (row0 >= n_new) return;
     const int rows = min(FA_BM, n_new - row0);
-    const int kvh = head / (nq / nkv);
+    const int kvh = head0 / (nq / nkv);
     const int start = seq_start[r];
     const int* pages = block_table + (size_t)seq_slot[r] * table_stride;
     const int first_pos = start + row0, last_pos = start + row0 + rows - 1;
@@ -74,30 +89,31 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 
     if (threadIdx.x == 0) {
         mbar_init(q_full, 1);
-        for (int s = 0; s < FA_STAGES; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
-        for (int i = 0; i < 2; ++i) { mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 4); mbar_init(&p_full[i], 4); }
-        mbar_init(pv_done, 1);
+        for (int s = 0; s < FA_STAGES; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], HPC); }
+        for (int i = 0; i < 2 * HPC; ++i) { mbar_init(&s_full[i], 1); mbar_init(&s_empty[i], 4); mbar_init(&p_full[i], 4); }
+        for (int i = 0; i < HPC; ++i) mbar_init(&pv_done[i], 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
     if (warp == 1) {
-        // columns: S0 [0,64), S1 [64,128), O [128,256)
+        // columns per head: S0 [0,64), S1 [64,128), O [128,256)
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n"
-                     ::"r"(smem_u32(tmem_slot)), "r"(256u) : "memory");
+                     ::"r"(smem_u32(tmem_slot)), "r"(256u * HPC) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
     }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const unsigned tmem_base = *tmem_slot;
-    const unsigned tmem_o = tmem_base + 128;
 
     if (warp == 0) {
         if (lane == 0) {
-            // Q: two 64-column halves of this head, 128 token rows
-            mbar_expect_tx(q_full, Q_BYTES);
-            tma_load_2d(sQ, &map_q, head * FA_HD, tok0 + row0, q_full);
-            tma_load_2d(sQ + Q_BYTES / 2, &map_q, head * FA_HD + 64, tok0 + row0, q_full);
+            // Q: two 64-column halves per head, 128 token rows
+            mbar_expect_tx(q_full, HPC * Q_BYTES);
+            for (int h = 0; h < HPC; ++h) {
+                tma_load_2d(sQ + h * Q_BYTES, &map_q, (head0 + h) * FA_HD, tok0 + row0, q_full);
+                tma_load_2d(sQ + h * Q_BYTES + Q_BYTES / 2, &map_q, (head0 + h) * FA_HD + 64, tok0 + row0, q_full);
+            }
             int issued = 0;
             for (int j = 0; j < NP; ++j) {
                 const int s = j % FA_STAGES;
@@ -120,49 +136,64 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                         if (mbar_try(&kv_full[j % FA_STAGES], (j / FA_STAGES) & 1)) break;
             }
         }
-    } else if (warp == 1) {
+    } else if (warp <= HPC) {
         if (lane == 0) {
+            const int h = warp - 1;             // the head this thread issues products for
             // S: M 128, N 64, both operands K-major.  O: M 128, N 128, A (P) K-major, B (V) MN-major.
             const unsigned idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(ZLM_PAGE >> 3) << 17) | (8u << 24);
             const unsigned idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | ((unsigned)(FA_HD >> 3) << 17) | (8u << 24);
-            const unsigned q0 = smem_u32(sQ);
             bool ok = mbar_wait(q_full, 0, abort_flag, 2);
+            // Descriptors differ only in their start address (in units of 16 bytes, a 14-bit field
+            // that never carries here), so they are built once and advanced by constants.
+            const uint64_t qd = make_desc(smem_u32(sQ + h * Q_BYTES));
+            const unsigned tmem_h = tmem_base + h * 256;
             auto issue_s = [&](int j) -> bool {
                 const int s = j % FA_STAGES, sb = j & 1;
                 if (!mbar_wait(&kv_full[s], (j / FA_STAGES) & 1, abort_flag, 2)) return false;
-                if (!mbar_wait(&s_empty[sb], ((j >> 1) & 1) ^ 1, abort_flag, 5)) return false;
+                if (!mbar_wait(&s_empty[h * 2 + sb], ((j >> 1) & 1) ^ 1, abort_flag, 5)) return false;
                 tc_fence_after();
-                const unsigned k0 = smem_u32(sK + s * KV_BYTES);
+                const uint64_t kd = make_desc(smem_u32(sK + s * KV_BYTES));
 #pragma unroll
                 for (int ks = 0; ks < FA_HD / 16; ++ks) {
-                    const unsigned qa = q0 + (ks >> 2) * (Q_BYTES / 2) + (ks & 3) * 32;
-                    const unsigned kb = k0 + (ks >> 2) * (KV_BYTES / 2) + (ks & 3) * 32;
-                    tc_mma(tmem_base + sb * ZLM_PAGE, make_desc(qa), make_desc(kb), idesc_s, ks != 0);
+                    const unsigned qoff = ((ks >> 2) * (Q_BYTES / 2) + (ks & 3) * 32) >> 4;
+                    const unsigned koff = ((ks >> 2) * (KV_BYTES / 2) + (ks & 3) * 32) >> 4;
+                    tc_mma(tmem_h + sb * ZLM_PAGE, qd + qoff, kd + koff, idesc_s, ks != 0);
                 }
-                tc_commit(&s_full[sb]);
+                tc_commit(&s_full[h * 2 + sb]);
                 return true;
             };
             if (ok && NP > 0) ok = issue_s(0);
             for (int j = 0; j < NP && ok; ++j) {
                 if (j + 1 < NP) { ok = issue_s(j + 1); if (!ok) break; }
                 const int s = j % FA_STAGES, sb = j & 1;
-                ok = mbar_wait(&p_full[sb], (j >> 1) & 1, abort_flag, 6);
+                ok = mbar_wait(&p_full[h * 2 + sb], (j >> 1) & 1, abort_flag, 6);
                 if (!ok) break;
                 tc_fence_after();
-                const unsigned p0 = smem_u32(sP + sb * P_BYTES), v0 = smem_u32(sV + s * KV_BYTES);
+                // V tile: [64 keys][128 bytes] for dims 0..63, then the same for dims 64..127:
+                // 16 keys a step = 2048 bytes; next 64 dims 8192 bytes on; 8-key groups 1024 bytes apart
+                const uint64_t vd = make_desc_ex(smem_u32(sV + s * KV_BYTES), KV_BYTES / 2, 1024);
+                const uint64_t pd = make_desc(smem_u32(sP + (h * 2 + sb) * P_BYTES));
 #pragma unroll
-                for (int kk = 0; kk < ZLM_PAGE / 16; ++kk) {
-                    // V tile: [64 keys][128 bytes] for dims 0..63, then the same for dims 64..127:
-                    // 16 keys a step = 2048 bytes; next 64 dims 8192 bytes on; 8-key groups 1024 bytes apart
-                    tc_mma(tmem_o, make_desc(p0 + kk * 32), make_desc_ex(v0 + kk * 2048, KV_BYTES / 2, 1024), idesc_o,
-                           (j | kk) != 0);
-                }
-                tc_commit(&kv_empty[s]);
-                tc_commit(pv_done);
+                for (int kk = 0; kk < ZLM_PAGE / 16; ++kk)
+                    tc_mma(tmem_h + 128, pd + ((kk * 32) >> 4), vd + ((kk * 2048) >> 4), idesc_o, (j | kk) != 0);
+                tc_commit(&pv_done[h]);
+                tc_commit(&kv_empty[s]);           // one arrival per head: the page is free when all have retired
             }
-            if (!ok) { tc_commit(&s_full[0]); tc_commit(&s_full[1]); tc_commit(pv_done); }
+            if (!ok) {
+                tc_commit(&s_full[h * 2]);
+                tc_commit(&s_full[h * 2 + 1]);
+                tc_commit(&pv_done[h]);
+            }
         }
     } else {
+        const int hh = (warp - 1 - HPC) >> 2;           // which of the block's heads this warp serves
+        const int head = head0 + hh;
+        uint64_t* const s_full_h = s_full + hh * 2;
+        uint64_t* const s_empty_h = s_empty + hh * 2;
+        uint64_t* const p_full_h = p_full + hh * 2;
+        uint64_t* const pv_done_h = pv_done + hh;
+        const unsigned tmem_s = tmem_base + hh * 256, tmem_o = tmem_base + hh * 256 + 128;
+        unsigned char* const sP_h = sP + hh * 2 * P_BYTES;
         const int lg = warp & 3;
         const int i = lg * 32 + lane;                   // row of the tile = lane of tensor memory
         const bool row_ok = i < rows;
@@ -173,32 +204,48 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         bool ok = true;
         for (int j = 0; j < NP; ++j) {
             const int sb = j & 1;
-            ok = mbar_wait(&s_full[sb], (j >> 1) & 1, abort_flag, 3);
+            ok = mbar_wait(&s_full_h[sb], (j >> 1) & 1, abort_flag, 3);
             tc_fence_after();
             if (!ok || *abort_flag) { ok = false; break; }
             float sv[ZLM_PAGE];
 #pragma unroll
-            for (int c = 0; c < ZLM_PAGE; c += 16) tc_ld16(tmem_base + lane_addr + sb * ZLM_PAGE + c, sv + c);
+            for (int c = 0; c < ZLM_PAGE; c += 16) tc_ld16_nowait(tmem_s + lane_addr + sb * ZLM_PAGE + c, sv + c);
+            tc_wait_ld();
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&s_empty[sb]);            // S may be overwritten by page j + 2
+            if (lane == 0) mbar_arrive(&s_empty_h[sb]);          // S may be overwritten by page j + 2
             const int kbase = (page_lo + j) * ZLM_PAGE;
             float mx = -INFINITY;
+            // a page that every row of the tile sees whole needs no mask (block-uniform test)
+            const bool inner = rows == FA_BM && kbase + ZLM_PAGE - 1 <= first_pos &&
+                               (window == 0 || kbase >= last_pos + 1 - window);
+            // four independent chains: one warp per scheduler has no other warp to hide a chain's latency
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+            if (inner) {
 #pragma unroll
-            for (int c = 0; c < ZLM_PAGE; ++c) {
-                const int key = kbase + c;
-                const bool vis = row_ok && key <= pos && key >= lo;
-                sv[c] = vis ? sv[c] * scale_log2 : -INFINITY;
-                mx = fmaxf(mx, sv[c]);
+                for (int c = 0; c < ZLM_PAGE; ++c) {
+                    sv[c] *= scale_log2;
+                    mx4[c & 3] = fmaxf(mx4[c & 3], sv[c]);
+                }
+            } else {
+#pragma unroll
+                for (int c = 0; c < ZLM_PAGE; ++c) {
+                    const int key = kbase + c;
+                    const bool vis = row_ok && key <= pos && key >= lo;
+                    sv[c] = vis ? sv[c] * scale_log2 : -INFINITY;
+                    mx4[c & 3] = fmaxf(mx4[c & 3], sv[c]);
+                }
             }
+            mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
             // lazy reference: move it only when the maximum grew by more than 2^8
             const bool grow = mx > m_ref + FA_RESCALE;              // also true for the first real maximum
             const float m_new = grow ? mx : m_ref;
             const float alpha = (grow && m_ref != -INFINITY) ? exp2f(m_ref - m_new) : 1.0f;
             const bool need_rescale = grow && m_ref != -INFINITY && j > 0;
             if (__any_sync(0xffffffffu, need_rescale)) {
-                // O must be at rest: the product of page j-1 has retired (page j's has not been issued)
-                ok = mbar_wait(pv_done, (j - 1) & 1, abort_flag, 7);
+                // O must be at rest: the product of page j-1 has retired (page j's cannot have been
+                // issued, it waits for this warp)
+                ok = mbar_wait(pv_done_h, (j - 1) & 1, abort_flag, 7);
                 tc_fence_after();
                 if (!ok) break;
 #pragma unroll 1
@@ -215,31 +262,31 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             l *= alpha;
             m_ref = m_new;
             const float ref = m_ref == -INFINITY ? 0.f : m_ref;
-            float ps = 0.f;
+            float ps4[4] = {0.f, 0.f, 0.f, 0.f};
             // P row -> shared memory, 128 bytes a row, 16-byte chunks swizzled by (row % 8)
-            unsigned char* prow = sP + sb * P_BYTES + i * 128;
+            unsigned char* prow = sP_h + sb * P_BYTES + i * 128;
 #pragma unroll
             for (int ch = 0; ch < 8; ++ch) {
                 float p[8];
 #pragma unroll
                 for (int e = 0; e < 8; ++e) {
-                    p[e] = exp2f(sv[ch * 8 + e] - ref);           // exp2(-inf) = 0 for masked keys
-                    ps += p[e];
+                    p[e] = fa_ex2(sv[ch * 8 + e] - ref);          // 2^-inf = 0 for masked keys
+                    ps4[e & 3] += p[e];
                 }
                 uint4 pk;
                 pk.x = fa_pack(p[0], p[1]); pk.y = fa_pack(p[2], p[3]);
                 pk.z = fa_pack(p[4], p[5]); pk.w = fa_pack(p[6], p[7]);
                 *(uint4*)(prow + ((ch ^ (i & 7)) << 4)) = pk;
             }
-            l += ps;
+            l += (ps4[0] + ps4[1]) + (ps4[2] + ps4[3]);
             fence_async_smem();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&p_full[sb]);
+            if (lane == 0) mbar_arrive(&p_full_h[sb]);
         }
         // the last two products: this warp only knows that the third last has retired, and a
         // parity can tell two phases apart, not three; so wait for them one after the other
-        if (ok && NP > 1) ok = mbar_wait(pv_done, (NP - 2) & 1, abort_flag, 8);
-        if (ok && NP > 0) ok = mbar_wait(pv_done, (NP - 1) & 1, abort_flag, 8);
+        if (ok && NP > 1) ok = mbar_wait(pv_done_h, (NP - 2) & 1, abort_flag, 8);
+        if (ok && NP > 0) ok = mbar_wait(pv_done_h, (NP - 1) & 1, abort_flag, 8);
         tc_fence_after();
         if (ok && !*abort_flag) {
             const float inv = row_ok ? 1.0f / l : 0.f;
@@ -265,7 +312,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     if (warp == 1) {
         __syncwarp();
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(256u) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(256u * HPC) : "memory");
     }
 }
 
@@ -291,21 +338,31 @@ extern "C" int zlm_attention_prefill_tc(void* out, int out_stride, const void* q
     if (rc) return rc;
     rc = zlm_make_map_2d(&mkv, pool, pool_pages * 2 * nkv * ZLM_PAGE, hd, hd, ZLM_PAGE, 64);
     if (rc) return rc;
-    const size_t smem = (size_t)FA_BM * FA_HD * 2 + 2 * FA_STAGES * ZLM_PAGE * FA_HD * 2 + 2 * FA_BM * ZLM_PAGE * 2 + 1024 + 256;
-    static bool attr_set = false;
-    if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        if (e != cudaSuccess) {
-            zlm_set_error("attention_prefill_tc: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
-            return ZLM_ERR_CUDA;
-        }
-        attr_set = true;
-    }
     const int tiles = (max_new + FA_BM - 1) / FA_BM;
-    ZLM_REQUIRE((long long)R * tiles < 2147483647LL && nq <= 65535, "attention_prefill_tc: too many tiles");
-    zlm_launch(attention_prefill_tc_kernel, dim3(R * tiles, nq), dim3(FA_THREADS), smem, st, mq, mkv,
-               (__nv_bfloat16*)out, out_stride, block_table, table_stride, cu_seqlens, seq_slot, seq_start, tiles, nq,
-               nkv, scale * 1.4426950408889634f, window);
+    const int hpc = ((nq / nkv) % 2 == 0) ? 2 : 1;       // two heads of a kv group share a block if the group is even
+    ZLM_REQUIRE((long long)R * tiles * nq < 2147483647LL, "attention_prefill_tc: too many tiles");
+    const size_t smem = (size_t)hpc * FA_BM * FA_HD * 2 + 2 * FA_STAGES * ZLM_PAGE * FA_HD * 2 +
+                        (size_t)hpc * 2 * FA_BM * ZLM_PAGE * 2 + 1024 + 256;
+#define ZLM_FA_LAUNCH(H)                                                                                          \
+    {                                                                                                             \
+        static bool attr_set = false;                                                                             \
+        if (!attr_set) {                                                                                          \
+            cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<H>,                                  \
+                                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);         \
+            if (e != cudaSuccess) {                                                                               \
+                zlm_set_error("attention_prefill_tc: cannot reserve %zu bytes of shared memory: %s", smem,        \
+                              cudaGetErrorString(e));                                                             \
+                return ZLM_ERR_CUDA;                                                                              \
+            }                                                                                                     \
+            attr_set = true;                                                                                      \
+        }                                                                                                         \
+        zlm_launch(attention_prefill_tc_kernel<H>, dim3(R * tiles * (nq / H)), dim3(32 + 160 * H), smem, st, mq, mkv,    \
+                   (__nv_bfloat16*)out, out_stride, block_table, table_stride, cu_seqlens, seq_slot, seq_start,   \
+                   R, tiles, nq, nkv, scale * 1.4426950408889634f, window);                                       \
+    }
+    if (hpc == 2) ZLM_FA_LAUNCH(2)
+    else ZLM_FA_LAUNCH(1)
+#undef ZLM_FA_LAUNCH
     return zlm_check_launch("attention_prefill_tc");
 }
 

@@ -152,10 +152,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                 ok = mbar_wait(&full[s], round & 1, abort_flag, 2);
                 if (!ok) break;
                 tc_fence_after();
-                const unsigned a0 = smem_u32(sA + s * A_BYTES), b0 = smem_u32(sB + s * B_BYTES);
+                // one descriptor per stage, advanced by constants (the start address field counts
+                // 16-byte units and does not carry): the issuing thread has no instruction to spare
+                const uint64_t ad = make_desc(smem_u32(sA + s * A_BYTES)), bd = make_desc(smem_u32(sB + s * B_BYTES));
 #pragma unroll
                 for (int k = 0; k < TC_BK / 16; ++k)
-                    tc_mma(tmem_base, make_desc(a0 + k * 32), make_desc(b0 + k * 32), idesc, (kb | k) != 0);
+                    tc_mma(tmem_base, ad + ((k * 32) >> 4), bd + ((k * 32) >> 4), idesc, (kb | k) != 0);
                 tc_commit(&empty[s]);          // the stage is free once these products have read it
             }
             tc_commit(acc_full);               // arrives when every product issued so far has retired
@@ -300,10 +302,10 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
                     ok = mbar_wait(&full[s], (it / STAGES) & 1, abort_flag, 2);
                     if (!ok) break;
                     tc_fence_after();
-                    const unsigned a0 = smem_u32(sA + s * A_BYTES), b0 = smem_u32(sB + s * B_BYTES);
+                    const uint64_t ad = make_desc(smem_u32(sA + s * A_BYTES)), bd = make_desc(smem_u32(sB + s * B_BYTES));
 #pragma unroll
                     for (int k = 0; k < TC_BK / 16; ++k)
-                        tc_mma(tmem_base + buf * BN, make_desc(a0 + k * 32), make_desc(b0 + k * 32), idesc, (kb | k) != 0);
+                        tc_mma(tmem_base + buf * BN, ad + ((k * 32) >> 4), bd + ((k * 32) >> 4), idesc, (kb | k) != 0);
                     tc_commit(&empty[s]);
                 }
                 tc_commit(&acc_full[buf]);
