@@ -55,6 +55,23 @@ attention_decode_kernel(__nv_bfloat16* __restrict__ out, int out_stride, const _
     if (p_begin >= p_end && splits > 1) return;      // the combine kernel skips this split too
 
     pdl_wait();          // q and this step's keys and values come from the kernel before
+    // the pages do not depend on q: start them now, they land while q is fetched
+    auto load_page = [&](int p, int stage) {
+        const __nv_bfloat16* kb = pool + (size_t)pages[p] * page_stride + (size_t)kvh * TILE;
+        const __nv_bfloat16* vb = kb + v_off;
+        __nv_bfloat16* ks_ = Ks + stage * TILE;
+        __nv_bfloat16* vs_ = Vs + stage * TILE;
+        for (int id = tid; id < ZLM_PAGE * CH; id += DEC_THREADS) {
+            const int r = id / CH, c = id % CH;
+            dec_cp_async16(ks_ + tile_off<HD>(r, c), kb + r * HD + c * 8);
+            dec_cp_async16(vs_ + tile_off<HD>(r, c), vb + r * HD + c * 8);
+        }
+    };
+
+    if (p_begin < p_end) load_page(p_begin, 0);
+    dec_commit();
+    if (p_begin + 1 < p_end) load_page(p_begin + 1, 1);
+    dec_commit();
     // Q fragments: row i of the 16-row tile is head kvh*G + i (zero beyond the group)
     unsigned qf[KS][4];
     {
@@ -76,22 +93,6 @@ attention_decode_kernel(__nv_bfloat16* __restrict__ out, int out_stride, const _
         for (int r = 0; r < 4; ++r) o[i][r] = 0.f;
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;   // rows g and g+8
 
-    auto load_page = [&](int p, int stage) {
-        const __nv_bfloat16* kb = pool + (size_t)pages[p] * page_stride + (size_t)kvh * TILE;
-        const __nv_bfloat16* vb = kb + v_off;
-        __nv_bfloat16* ks_ = Ks + stage * TILE;
-        __nv_bfloat16* vs_ = Vs + stage * TILE;
-        for (int id = tid; id < ZLM_PAGE * CH; id += DEC_THREADS) {
-            const int r = id / CH, c = id % CH;
-            dec_cp_async16(ks_ + tile_off<HD>(r, c), kb + r * HD + c * 8);
-            dec_cp_async16(vs_ + tile_off<HD>(r, c), vb + r * HD + c * 8);
-        }
-    };
-
-    if (p_begin < p_end) load_page(p_begin, 0);
-    dec_commit();
-    if (p_begin + 1 < p_end) load_page(p_begin + 1, 1);
-    dec_commit();
     for (int p = p_begin; p < p_end; ++p) {
         const int stage = (p - p_begin) & 1;
         dec_wait<1>();                       // everything but the newest group has landed: page p is there
