@@ -141,7 +141,7 @@ class CudaKernels:
         """out = x @ w.T (out in x's dtype, or fp32), or out += x @ w.T into the fp32
         residual stream when ``accumulate``.  w is [N, K] row-major.  bf16 products pick
         their kernel by the number of tokens: "gemv" (register-fragment streaming, up to
-        16), "tc" (TMA + tcgen05, 128 and more), "mma" (mma.sync, everything else);
+        8), "tc" (TMA + tcgen05, from 9 on), "mma" (mma.sync, what the others do not take);
         ``impl`` forces one (tests)."""
         T, K = x.shape
         N = w.shape[0]
@@ -165,7 +165,10 @@ class CudaKernels:
 
     def _bf16_product(self, out, x, w, T, N, K, ldx, ldy, mode, impl) -> None:
         if impl is None:
-            impl = "gemv" if T <= 16 else ("tc" if self.lib.zlm_gemm_tc_supported(T, N, K, ldx) else "mma")
+            # measured at Qwen3-8B sizes: the register-fragment GEMV wins up to 8 tokens, the
+            # swapped tcgen05 form from 9 on
+            tc_ok = self.lib.zlm_gemm_tc_supported(T, N, K, ldx)
+            impl = "gemv" if (T <= 8 or (T <= 16 and not tc_ok)) else ("tc" if tc_ok else "mma")
         if impl == "tc":
             ks = self.lib.zlm_gemm_tc_ksplit(T, N, K)
             scratch = self.scratch("gemm_tc.partials", ks * T * N, torch.float32, out.device) if ks > 1 else None
