@@ -140,6 +140,37 @@ __device__ double block_excl_scan(double v, double* warp_tot, double* total) {
     return base + inc - v;
 }
 
+// Walks a row with 8 loads in flight per thread: a loop whose body branches on the value it
+// has just loaded would otherwise wait a whole memory latency per element.
+template <typename F>
+__device__ __forceinline__ void for_each_strided(const float* __restrict__ l, int V, F f) {
+    for (int base = threadIdx.x; base < V; base += 8 * SAMPLE_THREADS) {
+        float v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int i = base + u * SAMPLE_THREADS;
+            v[u] = i < V ? l[i] : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            const int i = base + u * SAMPLE_THREADS;
+            if (i < V) f(i, v[u]);
+        }
+    }
+}
+// the same over a thread's own contiguous segment [i0, i1), in index order; f returns false to stop
+template <typename F>
+__device__ __forceinline__ void for_each_segment(const float* __restrict__ l, int i0, int i1, F f) {
+    for (int base = i0; base < i1; base += 8) {
+        float v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) v[u] = base + u < i1 ? l[base + u] : 0.f;
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+            if (base + u < i1 && !f(base + u, v[u])) return;
+    }
+}
+
 struct Thresh {
     unsigned key;   // keep keys above this
     int cut;        // and keys equal to it at indices <= cut
@@ -154,11 +185,16 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, int V, in
               const int* __restrict__ position) {
     __shared__ float redf[32];
     __shared__ double redd[32];
-    __shared__ double hist_w[256];
+    __shared__ unsigned long long hist_w[256];     // weights of a pass's bins in 2^-40 units (exact, order-free sums)
     __shared__ int hist_c[256];
     __shared__ unsigned sh_prefix;
     __shared__ int sh_krem, sh_int;
-    __shared__ double sh_dbl, sh_dbl2;
+    __shared__ unsigned long long sh_u64, sh_u64b;
+    // one histogram per warp, so that only the 32 lanes of a warp ever meet on an address
+    extern __shared__ __align__(16) unsigned char sample_smem[];
+    unsigned long long* warp_w = (unsigned long long*)sample_smem;                // [32][256]
+    int* warp_c = (int*)(warp_w + 32 * 256);                                      // [32][256]
+    const int my_warp = threadIdx.x >> 5;
 
     pdl_launch_dependents();
     pdl_wait();
@@ -166,17 +202,16 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, int V, in
     const float* l = logits + (size_t)row * ld;
     const int seg = (V + SAMPLE_THREADS - 1) / SAMPLE_THREADS;     // contiguous segment per thread
     const int i0 = min(V, tid * seg), i1 = min(V, i0 + seg);
-    const double invT = 1.0 / (double)temperature;
+    const float invT = 1.0f / temperature;
 
     float mx = -INFINITY;
-    for (int i = tid; i < V; i += SAMPLE_THREADS) mx = fmaxf(mx, l[i]);
+    for_each_strided(l, V, [&](int, float v) { mx = fmaxf(mx, v); });
     mx = block_max(mx, redf);
-    const double dmx = (double)mx;
 
     // index of the n-th (1-based) element with key == key0 among those kept by `lim`
     auto nth_equal = [&](unsigned key0, int n, const Thresh& lim) -> int {
         int c = 0;
-        for (int i = i0; i < i1; ++i) c += (order_key(l[i]) == key0 && kept(key0, i, lim)) ? 1 : 0;
+        for_each_segment(l, i0, i1, [&](int i, float v) { c += (order_key(v) == key0 && kept(key0, i, lim)) ? 1 : 0; return true; });
         double tot;
         const int before = (int)block_excl_scan((double)c, redd, &tot);
         __syncthreads();
@@ -184,8 +219,10 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, int V, in
         __syncthreads();
         if (before < n && n <= before + c) {
             int seen = before;
-            for (int i = i0; i < i1; ++i)
-                if (order_key(l[i]) == key0 && kept(key0, i, lim) && ++seen == n) { sh_int = i; break; }
+            for_each_segment(l, i0, i1, [&](int i, float v) {
+                if (order_key(v) == key0 && kept(key0, i, lim) && ++seen == n) { sh_int = i; return false; }
+                return true;
+            });
         }
         __syncthreads();
         return sh_int;
@@ -197,24 +234,21 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, int V, in
         if (tid == 0) { sh_prefix = 0u; sh_krem = top_k; }
         __syncthreads();
         for (int shift = 24; shift >= 0; shift -= 8) {
-            if (tid < 256) hist_c[tid] = 0;
+            for (int i = tid; i < 32 * 256; i += SAMPLE_THREADS) warp_c[i] = 0;
             __syncthreads();
             const unsigned prefix = sh_prefix;
             const unsigned mask = shift == 24 ? 0u : (0xffffffffu << (shift + 8));
-            // neighbours mostly fall into the same bin: add a run at a time
-            int cb = -1, cc = 0;
-            for (int i = tid; i < V; i += SAMPLE_THREADS) {
-                const unsigned k = order_key(l[i]);
-                if ((k & mask) != prefix) continue;
-                const int b = (k >> shift) & 255;
-                if (b != cb) {
-                    if (cc) atomicAdd(&hist_c[cb], cc);
-                    cb = b;
-                    cc = 0;
-                }
-                ++cc;
+            for_each_strided(l, V, [&](int, float v) {
+                const unsigned k = order_key(v);
+                if ((k & mask) == prefix) atomicAdd(&warp_c[my_warp * 256 + ((k >> shift) & 255)], 1);
+            });
+            __syncthreads();
+            if (tid < 256) {
+                int c = 0;
+#pragma unroll 8
+                for (int w = 0; w < 32; ++w) c += warp_c[w * 256 + tid];
+                hist_c[tid] = c;
             }
-            if (cc) atomicAdd(&hist_c[cb], cc);
             __syncthreads();
             if (tid == 0) {
                 int rem = sh_krem, b = 255;
@@ -234,48 +268,53 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, int V, in
         tk.cut = nth_equal(tk.key, ties_kept, all);
     }
 
-    // total weight of what top-k keeps
-    double part = 0.0;
-    for (int i = tid; i < V; i += SAMPLE_THREADS) {
-        const float v = l[i];
-        if (kept(order_key(v), i, tk)) part += exp(((double)v - dmx) * invT);
-    }
-    double total;
-    block_excl_scan(part, redd, &total);
-    __syncthreads();
-
+    // total weight of what top-k keeps, in 2^-40 units
+    const double FX = 1099511627776.0;
+    // a token's weight exp((l - max) / T): 32-bit arithmetic, as the softmax of the model's other
+    // kernels; sums of weights are exact (fixed point, or 64-bit floating point for the draw)
+    auto weight = [&](float v) -> float { return expf((v - mx) * invT); };
+    auto weight_fx = [&](float v) -> unsigned long long { return (unsigned long long)((double)weight(v) * FX + 0.5); };
     Thresh tp = tk;
     if (top_p < 1.0f) {
-        const double target = (double)top_p * total;
-        if (tid == 0) { sh_prefix = 0u; sh_dbl = 0.0; }      // sh_dbl: weight strictly above the prefix
+        unsigned long long part = 0;
+        for_each_strided(l, V, [&](int i, float v) {
+            if (kept(order_key(v), i, tk)) part += weight_fx(v);
+        });
+        if (tid == 0) sh_u64 = 0;
+        __syncthreads();
+        atomicAdd(&sh_u64, part);
+        __syncthreads();
+        const unsigned long long total = sh_u64;
+        const unsigned long long target = (unsigned long long)((double)top_p * (double)total);
+        __syncthreads();
+        if (tid == 0) { sh_prefix = 0u; sh_u64 = 0; }         // sh_u64: weight strictly above the prefix
         __syncthreads();
         for (int shift = 24; shift >= 0; shift -= 8) {
-            if (tid < 256) { hist_w[tid] = 0.0; hist_c[tid] = 0; }
+            for (int i = tid; i < 32 * 256; i += SAMPLE_THREADS) { warp_w[i] = 0; warp_c[i] = 0; }
             __syncthreads();
             const unsigned prefix = sh_prefix;
             const unsigned mask = shift == 24 ? 0u : (0xffffffffu << (shift + 8));
-            int cb = -1, cc = 0;
-            double cw = 0.0;
-            for (int i = tid; i < V; i += SAMPLE_THREADS) {
-                const float v = l[i];
+            for_each_strided(l, V, [&](int i, float v) {
                 const unsigned k = order_key(v);
-                if ((k & mask) != prefix || !kept(k, i, tk)) continue;
-                const int b = (k >> shift) & 255;
-                if (b != cb) {
-                    if (cc) { atomicAdd(&hist_w[cb], cw); atomicAdd(&hist_c[cb], cc); }
-                    cb = b;
-                    cc = 0;
-                    cw = 0.0;
-                }
-                cw += exp(((double)v - dmx) * invT);
-                ++cc;
+                if ((k & mask) != prefix || !kept(k, i, tk)) return;
+                const int b = my_warp * 256 + ((k >> shift) & 255);
+                atomicAdd(&warp_w[b], weight_fx(v));
+                atomicAdd(&warp_c[b], 1);
+            });
+            __syncthreads();
+            if (tid < 256) {
+                unsigned long long w = 0;
+                int c = 0;
+#pragma unroll 8
+                for (int wi = 0; wi < 32; ++wi) { w += warp_w[wi * 256 + tid]; c += warp_c[wi * 256 + tid]; }
+                hist_w[tid] = w;
+                hist_c[tid] = c;
             }
-            if (cc) { atomicAdd(&hist_w[cb], cw); atomicAdd(&hist_c[cb], cc); }
             __syncthreads();
             if (tid == 0) {
                 // from the top bin down: the first non-empty bin at which the running weight
-                // reaches the target; if rounding lets none reach it, the lowest non-empty bin
-                double above = sh_dbl;
+                // reaches the target; if none reaches it, the lowest non-empty bin
+                unsigned long long above = sh_u64;
                 int b = -1, lowest = -1;
                 for (int c = 255; c >= 0; --c) {
                     if (hist_c[c] == 0) continue;
@@ -284,33 +323,37 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, int V, in
                     above += hist_w[c];
                 }
                 if (b < 0) { b = lowest; above -= hist_w[lowest]; }
-                sh_dbl = above;
-                sh_dbl2 = hist_w[b];
+                sh_u64 = above;
+                sh_u64b = hist_w[b];
                 sh_int = hist_c[b];
                 sh_prefix = prefix | ((unsigned)b << shift);
             }
             __syncthreads();
         }
         tp.key = sh_prefix;
-        const double above = sh_dbl, tie_w = sh_dbl2;
+        const unsigned long long above = sh_u64, tie_w = sh_u64b;
         const int ties = sh_int;
         __syncthreads();
         // ties at the threshold weigh the same; keep as many as reach the target
         int need = ties;
-        if (ties > 1 && tie_w > 0.0) {
-            const double each = tie_w / (double)ties;
-            need = (int)ceil((target - above) / each);
-            need = need < 1 ? 1 : (need > ties ? ties : need);
+        if (ties > 1 && tie_w > 0) {
+            const unsigned long long each = tie_w / (unsigned long long)ties;
+            if (each > 0 && target > above) {
+                const unsigned long long n = (target - above + each - 1) / each;
+                need = n < 1 ? 1 : (n > (unsigned long long)ties ? ties : (int)n);
+            } else {
+                need = 1;
+            }
         }
         tp.cut = nth_equal(tp.key, need, tk);
     }
 
     // the draw: r = u * kept weight; walk the kept set in index order
     double mine = 0.0;
-    for (int i = i0; i < i1; ++i) {
-        const float v = l[i];
-        if (kept(order_key(v), i, tp)) mine += exp(((double)v - dmx) * invT);
-    }
+    for_each_segment(l, i0, i1, [&](int i, float v) {
+        if (kept(order_key(v), i, tp)) mine += (double)weight(v);
+        return true;
+    });
     double kept_sum;
     const double before = block_excl_scan(mine, redd, &kept_sum);
     __syncthreads();
@@ -327,7 +370,7 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, int V, in
             const float v = l[i];
             if (!kept(order_key(v), i, tp)) continue;
             last = i;
-            cum += exp(((double)v - dmx) * invT);
+            cum += (double)weight(v);
             if (r < cum) { pick = i; break; }
         }
         atomicMax(&sh_int, pick >= 0 ? pick : last);
@@ -353,7 +396,17 @@ extern "C" int zlm_sample(int* out, const float* logits, int R, int V, int ld, f
     ZLM_REQUIRE(R > 0 && V > 0 && ld >= V, "sample: bad sizes R=%d V=%d ld=%d", R, V, ld);
     ZLM_REQUIRE(temperature > 0.f, "sample: temperature must be positive (greedy is argmax)");
     ZLM_REQUIRE(top_k >= 0 && top_p > 0.f, "sample: top_k=%d top_p=%f", top_k, top_p);
-    zlm_launch(sample_kernel, R, SAMPLE_THREADS, 0, st, out, logits, V, ld, temperature, top_k, top_p, seed, request,
+    const size_t smem = (size_t)32 * 256 * (sizeof(unsigned long long) + sizeof(int));
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(sample_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) {
+            zlm_set_error("sample: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+            return ZLM_ERR_CUDA;
+        }
+        attr_set = true;
+    }
+    zlm_launch(sample_kernel, R, SAMPLE_THREADS, smem, st, out, logits, V, ld, temperature, top_k, top_p, seed, request,
                position);
     return zlm_check_launch("sample");
 }
