@@ -502,22 +502,33 @@ static int launch_tc_persistent(void* Y, const void* X, const void* W, int T, in
     return zlm_check_launch("gemm_tc_persistent");
 }
 
-// Into how many shares the few-token form cuts K so that about one block per SM streams W:
-// 1 (no split) when the grid is large enough already; every share keeps at least 8 k blocks.
+// 1 if the tensor-memory kernel takes this product (else use zlm_gemm_bf16_mma)
+extern "C" int zlm_gemm_tc_supported(int T, int N, int K, int ldx) {
+    return (T >= 1 && N >= 8 && K >= 8 && K % 8 == 0 && ldx % 8 == 0) ? 1 : 0;
+}
+
+// Into how many shares the few-token form cuts K.  The product streams W once; with `ctas`
+// output tiles on 148 SMs the time is the number of rounds the busiest SM runs, each round a
+// tile's share of W, plus writing and re-reading the fp32 partial products (mostly in L2,
+// counted at half weight).  The number of shares (at most 8, each at least 8 k blocks) that
+// makes this smallest is taken.
 extern "C" int zlm_gemm_tc_ksplit(int T, int N, int K) {
     if (T > 384) return 1;
     const int bn = T <= 32 ? 32 : (T <= 64 ? 64 : 128);
     const int ctas = ((N + TC_BM - 1) / TC_BM) * ((T + bn - 1) / bn);
     const int kb = (K + TC_BK - 1) / TC_BK;
-    int s = 148 / ctas;
-    if (s > 8) s = 8;
-    while (s > 1 && kb / s < 8) --s;
-    return s < 1 ? 1 : s;
-}
-
-// 1 if the tensor-memory kernel takes this product (else use zlm_gemm_bf16_mma)
-extern "C" int zlm_gemm_tc_supported(int T, int N, int K, int ldx) {
-    return (T >= 1 && N >= 8 && K >= 8 && K % 8 == 0 && ldx % 8 == 0) ? 1 : 0;
+    const int sms = 148;
+    const double w_bytes = 2.0 * N * K;
+    int best = 1;
+    double best_cost = 1e300;
+    for (int s = 1; s <= 8; ++s) {
+        if (s > 1 && kb / s < 8) break;
+        const int rounds = (ctas * s + sms - 1) / sms;
+        double cost = rounds * (w_bytes / ctas / s);
+        if (s > 1) cost += 0.5 * (2.0 * s * T * (double)N * 4.0) / sms;
+        if (cost < best_cost * 0.97) { best_cost = cost; best = s; }      // a new split must pay for its reduce launch
+    }
+    return best;
 }
 
 // mode 0: Y bf16 = X W^T; mode 1: Y fp32 += X W^T; mode 2: Y fp32 = X W^T;

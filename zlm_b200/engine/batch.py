@@ -158,9 +158,13 @@ def make_context(stager: MetaStager, arrays, T: int, R: int, workspace=None) -> 
     s_start = arrays["seq_start"]
     max_len = int((s_start + s_new).max())
     pages = (max_len + 63) // 64
+    # the longest sequence in pages, rounded up: powers of two up to 8, then multiples of 8
+    # (what the decode attention sizes its grid by, and a captured graph is keyed by)
     bucket = 1
-    while bucket < pages:
+    while bucket < pages and bucket < 8:
         bucket *= 2
+    if bucket < pages:
+        bucket = (pages + 7) // 8 * 8
     return StepContext(
         len_bucket=bucket, workspace=workspace,
         T=T, R=R,

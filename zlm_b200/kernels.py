@@ -34,11 +34,15 @@ def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
 
 def decode_splits(rows: int, nkv: int, len_bucket: int):
     """How the decode attention cuts a sequence's pages: (splits, pages per split).  The
-    parts are sized so that the grid is about two waves of the GPU (148 SMs x 3 blocks),
-    and are at least two pages long.  ``len_bucket`` is the longest sequence of the step
-    in pages, rounded up to a power of two, so that the choice (and a captured graph)
-    holds for many steps."""
-    per = max(2, -(-len_bucket * rows * nkv // 888))
+    parts are sized so that the grid is one wave of the GPU (148 SMs x 3 blocks) for small
+    batches (measured best at batch 8: a block's fixed cost is paid once) and four for large
+    ones (whose blocks are long, so that an unfinished last wave costs more), and are at
+    least two pages long.  ``len_bucket`` is the longest sequence of
+    the step in pages, rounded up, so that the choice (and a captured graph) holds for many
+    steps."""
+    work = len_bucket * rows * nkv
+    waves = 4 if work >= 8 * 444 else 1
+    per = max(2, -(-work // (444 * waves)))
     per = min(per, max(1, len_bucket))
     splits = -(-len_bucket // per)
     while splits > 1024:

@@ -130,7 +130,7 @@ class StepContext:
     is_decode: bool = False
     max_new: int = 0
     max_len: int = 0          # longest sequence after this step
-    len_bucket: int = 1       # max_len in pages, rounded up to a power of two
+    len_bucket: int = 1       # max_len in pages, rounded up (powers of two to 8, then multiples of 8)
     workspace: Any = None     # the runtime's Workspace
     extras: Dict[str, Any] = field(default_factory=dict)
 
