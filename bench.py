@@ -134,6 +134,8 @@ def run(args) -> dict:
     greedy = SamplingParams()
     if args.pdl:
         eng.decoder.use_pdl = True
+    if args.decode == "stream":
+        eng.decoder.use_stream = eng.decoder.can_stream
     g = torch.Generator().manual_seed(0)
     per_layer, weight_bytes, kv_per_tok = model_numbers(cfg, args.layers)
     k = eng.rt.k
@@ -165,7 +167,7 @@ def run(args) -> dict:
         ev1.record()
         torch.cuda.synchronize()
         ms = ev0.elapsed_time(ev1)
-        launches = dec.launches_per_step * n_steps if dec.use_graphs else k.launches() - l0
+        launches = dec.launches_per_step * n_steps if (dec.use_graphs or dec.use_stream) else k.launches() - l0
         return ms, ctx0, launches
 
     # ---- prefill of 2,048 tokens at batch 1 ------------------------------------------
@@ -260,6 +262,8 @@ def profile(args) -> int:
     eng = Engine.from_random(cfg, seed=0, dtype="bfloat16", device="cuda:0", max_tokens=B * (L + 256),
                              max_batch=B, max_seq_len=L + 256, max_step_tokens=min(B, 8) * L)
     eng.decoder.use_graphs = False
+    if args.decode == "stream":
+        eng.decoder.use_stream = eng.decoder.can_stream
     g = torch.Generator().manual_seed(0)
     ps = [torch.randint(0, cfg.vocab_size, (L,), generator=g).tolist() for _ in range(B)]
     slots = [eng.new_sequence() for _ in ps]
@@ -303,6 +307,8 @@ def main() -> int:
     ap.add_argument("--profile", choices=["decode", "prefill"], help="run a small case for ncu and exit")
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN)
     ap.add_argument("--pdl", action="store_true", help="decode kernels with programmatic dependent launch")
+    ap.add_argument("--decode", choices=["graph", "stream"], default="graph",
+                    help="graph: a CUDA graph of one kernel per operation; stream: the persistent decode kernel where it applies")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":

@@ -129,11 +129,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                 issued = j + 1;
             }
             if (*abort_flag) {
-                for (unsigned w = 0; w < TC_WAIT_LIMIT; ++w)
-                    if (mbar_try(q_full, 0)) break;
+                mbar_drain(q_full, 0);
                 for (int j = max(0, issued - FA_STAGES); j < issued; ++j)
-                    for (unsigned w = 0; w < TC_WAIT_LIMIT; ++w)
-                        if (mbar_try(&kv_full[j % FA_STAGES], (j / FA_STAGES) & 1)) break;
+                    mbar_drain(&kv_full[j % FA_STAGES], (j / FA_STAGES) & 1);
             }
         }
     } else if (warp <= HPC) {

@@ -46,6 +46,13 @@ struct VecW {
         return dtype == ZLM_DTYPE_F32 ? ((const float*)p)[i]
                                       : __bfloat162float(((const __nv_bfloat16*)p)[i]);
     }
+    // elements i .. i + 3, i a multiple of 4 (the vector starts 16-byte aligned)
+    __device__ __forceinline__ float4 load4(int i) const {
+        if (dtype == ZLM_DTYPE_F32) return *(const float4*)((const float*)p + i);
+        const uint2 u = *(const uint2*)((const __nv_bfloat16*)p + i);
+        return make_float4(__uint_as_float(u.x << 16), __uint_as_float(u.x & 0xffff0000u),
+                           __uint_as_float(u.y << 16), __uint_as_float(u.y & 0xffff0000u));
+    }
 };
 
 __device__ __forceinline__ float warp_sum(float v) {
@@ -79,6 +86,43 @@ __device__ __forceinline__ float block_max(float v, float* red) {
     __syncthreads();
     if (lane == 0) red[warp] = v;
     __syncthreads();
+    float t = (lane < nw) ? red[lane] : -INFINITY;
+    t = warp_max(t);
+    return t;
+}
+
+// ---------------------------------------------------------------------------
+// A group of warps that works like a thread block of its own: the whole block of a
+// stand-alone kernel (barrier 0), or some warps of a larger persistent block (a named
+// barrier).  Code written against it runs unchanged in both places.
+// ---------------------------------------------------------------------------
+struct GroupSync {
+    int id;         // hardware barrier
+    int threads;    // threads that take part, a multiple of 32
+    __device__ __forceinline__ void sync() const {
+        asm volatile("bar.sync %0, %1;\n" ::"r"(id), "r"(threads) : "memory");
+    }
+};
+
+// the sums and maxima above for a group: `tid` counts inside the group
+__device__ __forceinline__ float group_sum(float v, float* red, int tid, const GroupSync& gs) {
+    const int lane = tid & 31, warp = tid >> 5;
+    const int nw = gs.threads >> 5;
+    v = warp_sum(v);
+    gs.sync();
+    if (lane == 0) red[warp] = v;
+    gs.sync();
+    float t = (lane < nw) ? red[lane] : 0.f;
+    t = warp_sum(t);
+    return t;
+}
+__device__ __forceinline__ float group_max(float v, float* red, int tid, const GroupSync& gs) {
+    const int lane = tid & 31, warp = tid >> 5;
+    const int nw = gs.threads >> 5;
+    v = warp_max(v);
+    gs.sync();
+    if (lane == 0) red[warp] = v;
+    gs.sync();
     float t = (lane < nw) ? red[lane] : -INFINITY;
     t = warp_max(t);
     return t;

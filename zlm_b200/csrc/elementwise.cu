@@ -3,6 +3,7 @@
 // src/kernels/transformer/norm.zig:4-37 (eps inside the root, x*inv then *w),
 // src/kernels/transformer/activation.zig:8-13 (g / (1 + e^-g) * u).
 #include "common.cuh"
+#include "elementwise.cuh"
 #include <stdarg.h>
 #include <stdio.h>
 
@@ -40,27 +41,7 @@ __global__ void embed_kernel(float* __restrict__ out, const TW* __restrict__ tab
     pdl_launch_dependents();
     const int t = blockIdx.x;
     pdl_wait();                 // the ids may be what the previous step's sampler wrote
-    int id = ids[t];
-    // ids are validated on the host; clamp so that a bad id can never read
-    // outside the table
-    id = id < 0 ? 0 : (id >= V ? V - 1 : id);
-    const TW* row = table + (size_t)id * H;
-    float* o = out + (size_t)t * H;
-    if (sizeof(TW) == 2 && H % 8 == 0) {
-        // 16-byte loads, two 16-byte stores
-        for (int c = threadIdx.x; c < H / 8; c += blockDim.x) {
-            const uint4 v = *(const uint4*)((const __nv_bfloat16*)row + c * 8);
-            float4 lo, hi;
-            lo.x = __uint_as_float(v.x << 16); lo.y = __uint_as_float(v.x & 0xffff0000u);
-            lo.z = __uint_as_float(v.y << 16); lo.w = __uint_as_float(v.y & 0xffff0000u);
-            hi.x = __uint_as_float(v.z << 16); hi.y = __uint_as_float(v.z & 0xffff0000u);
-            hi.z = __uint_as_float(v.w << 16); hi.w = __uint_as_float(v.w & 0xffff0000u);
-            *(float4*)(o + c * 8) = lo;
-            *(float4*)(o + c * 8 + 4) = hi;
-        }
-        return;
-    }
-    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = to_f32(row[i]);
+    embed_row(out + (size_t)t * H, table, ids[t], H, V, threadIdx.x, blockDim.x);
 }
 
 extern "C" int zlm_embed(float* out, const void* table, int table_dtype, const int* ids, int T,
@@ -82,7 +63,6 @@ extern "C" int zlm_embed(float* out, const void* table, int table_dtype, const i
 // size is a function of H alone, so the order of the sum never depends on the batch.
 // With H a multiple of 4 every thread keeps its float4s in registers between the
 // sum and the scaling, so the row is read once and the latency is one load deep.
-#define NORM_MAX_V4 4
 template <typename TO>
 __global__ void rmsnorm_kernel(TO* __restrict__ out, const float* __restrict__ x, VecW w,
                                const int* __restrict__ rows, int H, float eps) {
@@ -90,43 +70,19 @@ __global__ void rmsnorm_kernel(TO* __restrict__ out, const float* __restrict__ x
     pdl_launch_dependents();
     const int r = blockIdx.x;
     const int src = rows ? rows[r] : r;
-    const float* xr = x + (size_t)src * H;
     pdl_wait();
-    TO* o = out + (size_t)r * H;
-    const int nv = H / 4;
-    if (H % 4 == 0 && nv <= NORM_MAX_V4 * (int)blockDim.x) {
-        float4 v[NORM_MAX_V4];
-        float s = 0.f;
-#pragma unroll
-        for (int j = 0; j < NORM_MAX_V4; ++j) {
-            const int c = threadIdx.x + j * blockDim.x;
-            v[j] = c < nv ? *(const float4*)(xr + c * 4) : make_float4(0.f, 0.f, 0.f, 0.f);
-            s = fmaf(v[j].x, v[j].x, s); s = fmaf(v[j].y, v[j].y, s);
-            s = fmaf(v[j].z, v[j].z, s); s = fmaf(v[j].w, v[j].w, s);
-        }
-        s = block_sum(s, red);
-        const float inv = 1.0f / sqrtf(s / (float)H + eps);
-#pragma unroll
-        for (int j = 0; j < NORM_MAX_V4; ++j) {
-            const int c = threadIdx.x + j * blockDim.x;
-            if (c < nv) {
-                const int i = c * 4;
-                o[i] = from_f32<TO>((v[j].x * inv) * w[i]);
-                o[i + 1] = from_f32<TO>((v[j].y * inv) * w[i + 1]);
-                o[i + 2] = from_f32<TO>((v[j].z * inv) * w[i + 2]);
-                o[i + 3] = from_f32<TO>((v[j].w * inv) * w[i + 3]);
-            }
-        }
-        return;
-    }
-    float s = 0.f;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) {
-        const float v = xr[i];
-        s = fmaf(v, v, s);
-    }
-    s = block_sum(s, red);
-    const float inv = 1.0f / sqrtf(s / (float)H + eps);
-    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = from_f32<TO>((xr[i] * inv) * w[i]);
+    rmsnorm_row<TO, 1>(out + (size_t)r * H, x + (size_t)src * H, w, H, eps, red, threadIdx.x,
+                       GroupSync{0, (int)blockDim.x}, blockDim.x);
+}
+
+// threads of the block that norms one row.  32-bit output (the 32-bit path): a function of H
+// only, so that the order of the sum never depends on the batch.  bf16 output: rows of a long
+// step share an SM better with 256 threads each; the difference is in the last bit of the sum.
+extern "C" int zlm_rmsnorm_threads(int out_dtype, int R, int H) {
+    int threads = 128;
+    while (threads < 1024 && threads * 4 < H) threads *= 2;
+    if (out_dtype == ZLM_DTYPE_BF16 && R >= 512 && H % 4 == 0 && H <= 256 * 4 * NORM_MAX_V4 && threads > 256) threads = 256;
+    return threads;
 }
 
 extern "C" int zlm_rmsnorm(void* out, int out_dtype, const float* x, const void* w, int w_dtype,
@@ -134,13 +90,10 @@ extern "C" int zlm_rmsnorm(void* out, int out_dtype, const float* x, const void*
     if (R == 0) return ZLM_OK;
     ZLM_REQUIRE(R > 0 && H > 0, "rmsnorm: bad sizes R=%d H=%d", R, H);
     ZLM_REQUIRE(w_dtype == ZLM_DTYPE_F32 || w_dtype == ZLM_DTYPE_BF16, "rmsnorm: weight dtype %d", w_dtype);
+    ZLM_REQUIRE(H % 4 != 0 || ((uintptr_t)x % 16 == 0 && (uintptr_t)w % 16 == 0 && (uintptr_t)out % 16 == 0),
+                "rmsnorm: input, weight and output must be 16-byte aligned");
     VecW vw{w, w_dtype};
-    // 32-bit output (the 32-bit path): a function of H only, so that the order of the sum
-    // never depends on the batch.  bf16 output: rows of a long step share an SM better
-    // with 256 threads each; the difference is in the last bit of the sum.
-    int threads = 128;
-    while (threads < 1024 && threads * 4 < H) threads *= 2;
-    if (out_dtype == ZLM_DTYPE_BF16 && R >= 512 && H % 4 == 0 && H <= 256 * 4 * NORM_MAX_V4 && threads > 256) threads = 256;
+    const int threads = zlm_rmsnorm_threads(out_dtype, R, H);
     if (out_dtype == ZLM_DTYPE_F32)
         zlm_launch(rmsnorm_kernel<float>, R, threads, 0, st, (float*)out, x, vw, rows, H, eps);
     else if (out_dtype == ZLM_DTYPE_BF16)

@@ -136,8 +136,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
             if (*abort_flag) {
                 // copies may still be landing in this block's shared memory: wait for them (bounded)
                 for (int kb = max(0, issued - STAGES); kb < issued; ++kb)
-                    for (unsigned it = 0; it < TC_WAIT_LIMIT; ++it)
-                        if (mbar_try(&full[kb % STAGES], (kb / STAGES) & 1)) break;
+                    mbar_drain(&full[kb % STAGES], (kb / STAGES) & 1);
             }
         }
     } else if (warp == 1) {
@@ -281,8 +280,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
             if (*abort_flag) {
                 // copies may still be landing in this block's shared memory: wait for them (bounded)
                 for (unsigned j = it > (unsigned)STAGES ? it - STAGES : 0; j < it; ++j)
-                    for (unsigned w = 0; w < TC_WAIT_LIMIT; ++w)
-                        if (mbar_try(&full[j % STAGES], (j / STAGES) & 1)) break;
+                    mbar_drain(&full[j % STAGES], (j / STAGES) & 1);
             }
         }
     } else if (warp == 1) {

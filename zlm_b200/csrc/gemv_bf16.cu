@@ -2,7 +2,7 @@
 // Y[t, n] = sum_k X[t, k] W[n, k], fp32 accumulation.
 //
 // The step is bound by reading W once.  A block owns 16 rows of W; its 8 warps
-// split K between them.  Every thread loads 16 bytes (8 consecutive k) of row g
+// split K between them (512 columns each of every 4096).  Every thread loads 16 bytes (8 consecutive k) of row g
 // and of row g+8 straight from global memory into registers, and the 8 matching
 // k of token g of X; these registers are, as they are, the A and B fragments of
 // two m16n8k16 tensor-core products: a sum over k does not care in which order
@@ -55,64 +55,84 @@ gemv_bf16_kernel(void* __restrict__ Y, const __nv_bfloat16* __restrict__ X,
         xok[j] = j * 8 + g < T;
         xr[j] = X + (size_t)(xok[j] ? j * 8 + g : 0) * ldx + q * 8;
     }
+    // Four chains of sums per thread, so that four tensor-core products can be in flight
+    // (one chain would run at the latency of the instruction).  K is cut into chunks of
+    // 8 x 512 columns; warp w takes the w-th 512 columns of every chunk, as 16 blocks of 32
+    // in ascending k; chain 2 * (i & 1) + h takes the h-th 16 k of block i.  The chains are
+    // added at the end, (0 + 1) + (2 + 3).  The persistent decode kernel (decode_stream.cu)
+    // adds in the same order.
+    float ch[NT][4][4];
+#pragma unroll
+    for (int j = 0; j < NT; ++j)
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+#pragma unroll
+            for (int r = 0; r < 4; ++r) ch[j][c][r] = 0.f;
+
+    // GEMV_UNROLL blocks in flight.  The weights do not depend on the kernel before this one:
+    // their first loads are issued before the wait for it, the activations after.
+    constexpr int SEG = 512, CHUNK = GEMV_WARPS * SEG;
+    pdl_launch_dependents();
+    uint4 a[GEMV_UNROLL], b[GEMV_UNROLL];
+    bool have = warp * SEG + GEMV_UNROLL * 32 <= K;
+    if (have) {
+#pragma unroll
+        for (int u = 0; u < GEMV_UNROLL; ++u) {
+            a[u] = ld_stream16(w0 + warp * SEG + u * 32);
+            b[u] = ld_stream16(w1 + warp * SEG + u * 32);
+        }
+    }
+    pdl_wait();
+    for (int kc = warp * SEG; kc < K; kc += CHUNK) {
+        const int kend = min(K, kc + SEG);
+        int kb = kc;
+        for (; kb + GEMV_UNROLL * 32 <= kend; kb += GEMV_UNROLL * 32) {
+            uint4 x[GEMV_UNROLL][NT];
+            if (!have) {
+#pragma unroll
+                for (int u = 0; u < GEMV_UNROLL; ++u) {
+                    a[u] = ld_stream16(w0 + kb + u * 32);
+                    b[u] = ld_stream16(w1 + kb + u * 32);
+                }
+            }
+            have = false;
+#pragma unroll
+            for (int u = 0; u < GEMV_UNROLL; ++u)
+#pragma unroll
+                for (int j = 0; j < NT; ++j)
+                    x[u][j] = xok[j] ? __ldg((const uint4*)(xr[j] + kb + u * 32)) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+            for (int u = 0; u < GEMV_UNROLL; ++u)      // kb - kc is a multiple of 128: block u has parity u & 1
+#pragma unroll
+                for (int j = 0; j < NT; ++j) {
+                    gemv_mma(ch[j][2 * (u & 1)], a[u].x, b[u].x, a[u].y, b[u].y, x[u][j].x, x[u][j].y);
+                    gemv_mma(ch[j][2 * (u & 1) + 1], a[u].z, b[u].z, a[u].w, b[u].w, x[u][j].z, x[u][j].w);
+                }
+        }
+        for (int par = 0; kb < kend; kb += 32, par ^= 1) {
+            // K is a multiple of 8, so a thread's 8 k are all inside or all outside
+            const bool in = kb + q * 8 < K;
+            const uint4 z = make_uint4(0, 0, 0, 0);
+            const uint4 a = in ? ld_stream16(w0 + kb) : z;
+            const uint4 b = in ? ld_stream16(w1 + kb) : z;
+#pragma unroll
+            for (int j = 0; j < NT; ++j) {
+                const uint4 x = (in && xok[j]) ? __ldg((const uint4*)(xr[j] + kb)) : z;
+                if (par == 0) {
+                    gemv_mma(ch[j][0], a.x, b.x, a.y, b.y, x.x, x.y);
+                    gemv_mma(ch[j][1], a.z, b.z, a.w, b.w, x.z, x.w);
+                } else {
+                    gemv_mma(ch[j][2], a.x, b.x, a.y, b.y, x.x, x.y);
+                    gemv_mma(ch[j][3], a.z, b.z, a.w, b.w, x.z, x.w);
+                }
+            }
+        }
+    }
     float acc[NT][4];
 #pragma unroll
     for (int j = 0; j < NT; ++j)
 #pragma unroll
-        for (int r = 0; r < 4; ++r) acc[j][r] = 0.f;
-
-    // warp w takes the 32-wide k blocks w, w + 8, ...; GEMV_UNROLL of them in flight.  The
-    // weights do not depend on the kernel before this one: their first loads are issued
-    // before the wait for it, the activations after.
-    const int step = GEMV_WARPS * 32;
-    int kb = warp * 32;
-    pdl_launch_dependents();
-    uint4 a[GEMV_UNROLL], b[GEMV_UNROLL];
-    bool have = kb + (GEMV_UNROLL - 1) * step + 32 <= K;
-    if (have) {
-#pragma unroll
-        for (int u = 0; u < GEMV_UNROLL; ++u) {
-            a[u] = ld_stream16(w0 + kb + u * step);
-            b[u] = ld_stream16(w1 + kb + u * step);
-        }
-    }
-    pdl_wait();
-    for (; kb + (GEMV_UNROLL - 1) * step + 32 <= K; kb += GEMV_UNROLL * step) {
-        uint4 x[GEMV_UNROLL][NT];
-        if (!have) {
-#pragma unroll
-            for (int u = 0; u < GEMV_UNROLL; ++u) {
-                a[u] = ld_stream16(w0 + kb + u * step);
-                b[u] = ld_stream16(w1 + kb + u * step);
-            }
-        }
-        have = false;
-#pragma unroll
-        for (int u = 0; u < GEMV_UNROLL; ++u)
-#pragma unroll
-            for (int j = 0; j < NT; ++j)
-                x[u][j] = xok[j] ? __ldg((const uint4*)(xr[j] + kb + u * step)) : make_uint4(0, 0, 0, 0);
-#pragma unroll
-        for (int u = 0; u < GEMV_UNROLL; ++u)
-#pragma unroll
-            for (int j = 0; j < NT; ++j) {
-                gemv_mma(acc[j], a[u].x, b[u].x, a[u].y, b[u].y, x[u][j].x, x[u][j].y);
-                gemv_mma(acc[j], a[u].z, b[u].z, a[u].w, b[u].w, x[u][j].z, x[u][j].w);
-            }
-    }
-    for (; kb < K; kb += step) {
-        // K is a multiple of 8, so a thread's 8 k are all inside or all outside
-        const bool in = kb + q * 8 < K;
-        const uint4 z = make_uint4(0, 0, 0, 0);
-        const uint4 a = in ? ld_stream16(w0 + kb) : z;
-        const uint4 b = in ? ld_stream16(w1 + kb) : z;
-#pragma unroll
-        for (int j = 0; j < NT; ++j) {
-            const uint4 x = (in && xok[j]) ? __ldg((const uint4*)(xr[j] + kb)) : z;
-            gemv_mma(acc[j], a.x, b.x, a.y, b.y, x.x, x.y);
-            gemv_mma(acc[j], a.z, b.z, a.w, b.w, x.z, x.w);
-        }
-    }
+        for (int r = 0; r < 4; ++r) acc[j][r] = (ch[j][0][r] + ch[j][1][r]) + (ch[j][2][r] + ch[j][3][r]);
     // acc[j][0..1]: row g, tokens 8j + 2q, 2q+1; acc[j][2..3]: row g + 8
 #pragma unroll
     for (int j = 0; j < NT; ++j) {

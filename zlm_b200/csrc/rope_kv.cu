@@ -5,14 +5,8 @@
 // src/kernels/transformer/norm.zig:128-166, src/kernels/transformer/rope.zig:161-206,
 // src/kernels/transformer/attention.zig:6-28).  All arithmetic in fp32.
 #include "common.cuh"
+#include "rope_kv.cuh"
 
-#define ROPE_MAX_PER_LANE 16   // head_dim <= 512
-#define ROPE_WARPS 4
-
-// One block per token.  The token's rotation table (cos and sin of pos * inv_freq[i]) is
-// computed once into shared memory and shared by all heads; then the warps take the
-// heads in turn: heads 0..nq-1 are q, then nkv k heads, then nkv v heads.  NPL is the
-// number of elements a lane holds (head_dim <= 32 * NPL).
 template <typename TA, int NPL>
 __global__ void __launch_bounds__(ROPE_WARPS * 32)
 qk_norm_rope_write_kernel(
@@ -21,86 +15,10 @@ qk_norm_rope_write_kernel(
     const int* __restrict__ token_slot, const int* __restrict__ block_table, int table_stride,
     TA* __restrict__ pool, int nq, int nkv, int hd, int writes_kv, int heads_per_block) {
     extern __shared__ float sm[];
-    const int ang = n_rot / 2, half = hd / 2;
-    float* cs = sm;                       // [ang]
-    float* sn = sm + ang;                 // [ang]
-    float* bufs = sm + 2 * ang;           // [ROPE_WARPS][hd]
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-    const int t = blockIdx.x;
-    pdl_launch_dependents();
-    const int pos = token_pos[t];
-    for (int i = tid; i < ang; i += ROPE_WARPS * 32) {
-        float s, c;
-        sincosf((float)pos * inv_freq[i], &s, &c);
-        cs[i] = c;
-        sn[i] = s;
-    }
-    __syncthreads();
-    const int heads = nq + 2 * nkv;
-    float* buf = bufs + warp * hd;
-    int page = 0;
-    if (writes_kv) page = block_table[(size_t)token_slot[t] * table_stride + pos / ZLM_PAGE];
-    pdl_wait();             // the table above is the step's own; qkv comes from the kernel before
-    const int j_end = min(heads, (int)(blockIdx.y + 1) * heads_per_block);
-    for (int j = blockIdx.y * heads_per_block + warp; j < j_end; j += ROPE_WARPS) {
-        const int kind = j < nq ? 0 : (j < nq + nkv ? 1 : 2);
-        if (kind == 2 && !writes_kv) break;     // v is only ever copied to the cache (warp-uniform)
-        TA* src = qkv + (size_t)t * row_stride + (size_t)j * hd;
-        float v[NPL];
-        float ss = 0.f;
-#pragma unroll
-        for (int r = 0; r < NPL; ++r) {
-            const int e = lane + 32 * r;
-            v[r] = e < hd ? to_f32(src[e]) : 0.f;
-            ss = fmaf(v[r], v[r], ss);
-        }
-        if (kind != 2) {
-            if (has_norm) {
-                ss = warp_sum(ss);
-                const float inv = 1.0f / sqrtf(ss / (float)hd + eps);
-                const VecW& w = kind == 0 ? qw : kw;
-#pragma unroll
-                for (int r = 0; r < NPL; ++r) {
-                    const int e = lane + 32 * r;
-                    if (e < hd) v[r] = (v[r] * inv) * w[e];
-                }
-            }
-            if (ang > 0) {
-                __syncwarp();
-#pragma unroll
-                for (int r = 0; r < NPL; ++r) {
-                    const int e = lane + 32 * r;
-                    if (e < hd) buf[e] = v[r];
-                }
-                __syncwarp();
-#pragma unroll
-                for (int r = 0; r < NPL; ++r) {
-                    const int e = lane + 32 * r;
-                    if (e < hd) {
-                        const int i = e < half ? e : e - half;
-                        if (i < ang) {
-                            const float x0 = buf[i], x1 = buf[i + half];
-                            v[r] = e < half ? (x0 * cs[i] - x1 * sn[i]) : (x0 * sn[i] + x1 * cs[i]);
-                        }
-                    }
-                }
-            }
-        }
-        TA* dst;
-        if (kind == 0 || !writes_kv) {
-            dst = src;                               // q (and k when nothing is written) in place
-        } else {
-            const int kvh = kind == 1 ? j - nq : j - nq - nkv;
-            const size_t page_stride = (size_t)2 * nkv * ZLM_PAGE * hd;
-            dst = pool + (size_t)page * page_stride + (size_t)(kind - 1) * nkv * ZLM_PAGE * hd +
-                  ((size_t)kvh * ZLM_PAGE + (pos % ZLM_PAGE)) * hd;
-        }
-#pragma unroll
-        for (int r = 0; r < NPL; ++r) {
-            const int e = lane + 32 * r;
-            if (e < hd) dst[e] = from_f32<TA>(v[r]);
-        }
-    }
+    qk_norm_rope_write_item<TA, NPL, true>(sm, threadIdx.x, GroupSync{0, ROPE_WARPS * 32}, blockIdx.x, blockIdx.y,
+                                           qkv, row_stride, qw, kw, has_norm, eps, inv_freq, n_rot, token_pos,
+                                           token_slot, block_table, table_stride, pool, nq, nkv, hd, writes_kv,
+                                           heads_per_block);
 }
 
 template <typename TA, int NPL>

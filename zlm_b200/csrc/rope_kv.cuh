@@ -1,0 +1,103 @@
+// The body of the q/k norm + rotation + cache write kernel as a function of a group of
+// warps (see rope_kv.cu for what it computes), shared by the stand-alone kernel and the
+// persistent decode kernel.
+#pragma once
+#include "common.cuh"
+
+#define ROPE_MAX_PER_LANE 16   // head_dim <= 512
+#define ROPE_WARPS 4
+
+// One block per token.  The token's rotation table (cos and sin of pos * inv_freq[i]) is
+// computed once into shared memory and shared by all heads; then the warps take the
+// heads in turn: heads 0..nq-1 are q, then nkv k heads, then nkv v heads.  NPL is the
+// number of elements a lane holds (head_dim <= 32 * NPL).
+// The work of one block of the kernel below, token t and head chunk `chunk`, by a group of
+// ROPE_WARPS warps; `sm` holds n_rot + ROPE_WARPS * hd floats.
+template <typename TA, int NPL, bool PDL>
+__device__ __forceinline__ void qk_norm_rope_write_item(
+    float* sm, const int tid, const GroupSync gs, const int t, const int chunk,
+    TA* qkv, int row_stride, VecW qw, VecW kw, int has_norm, float eps,
+    const float* inv_freq, int n_rot, const int* token_pos,
+    const int* token_slot, const int* block_table, int table_stride,
+    TA* pool, int nq, int nkv, int hd, int writes_kv, int heads_per_block) {
+    const int ang = n_rot / 2, half = hd / 2;
+    float* cs = sm;                       // [ang]
+    float* sn = sm + ang;                 // [ang]
+    float* bufs = sm + 2 * ang;           // [ROPE_WARPS][hd]
+    const int lane = tid & 31, warp = tid >> 5;
+    if (PDL) pdl_launch_dependents();
+    const int pos = token_pos[t];
+    for (int i = tid; i < ang; i += ROPE_WARPS * 32) {
+        float s, c;
+        sincosf((float)pos * inv_freq[i], &s, &c);
+        cs[i] = c;
+        sn[i] = s;
+    }
+    gs.sync();
+    const int heads = nq + 2 * nkv;
+    float* buf = bufs + warp * hd;
+    int page = 0;
+    if (writes_kv) page = block_table[(size_t)token_slot[t] * table_stride + pos / ZLM_PAGE];
+    if (PDL) pdl_wait();    // the table above is the step's own; qkv comes from the kernel before
+    const int j_end = min(heads, (chunk + 1) * heads_per_block);
+    for (int j = chunk * heads_per_block + warp; j < j_end; j += ROPE_WARPS) {
+        const int kind = j < nq ? 0 : (j < nq + nkv ? 1 : 2);
+        if (kind == 2 && !writes_kv) break;     // v is only ever copied to the cache (warp-uniform)
+        TA* src = qkv + (size_t)t * row_stride + (size_t)j * hd;
+        float v[NPL];
+        float ss = 0.f;
+#pragma unroll
+        for (int r = 0; r < NPL; ++r) {
+            const int e = lane + 32 * r;
+            v[r] = e < hd ? to_f32(src[e]) : 0.f;
+            ss = fmaf(v[r], v[r], ss);
+        }
+        if (kind != 2) {
+            if (has_norm) {
+                ss = warp_sum(ss);
+                const float inv = 1.0f / sqrtf(ss / (float)hd + eps);
+                const VecW& w = kind == 0 ? qw : kw;
+#pragma unroll
+                for (int r = 0; r < NPL; ++r) {
+                    const int e = lane + 32 * r;
+                    if (e < hd) v[r] = (v[r] * inv) * w[e];
+                }
+            }
+            if (ang > 0) {
+                __syncwarp();
+#pragma unroll
+                for (int r = 0; r < NPL; ++r) {
+                    const int e = lane + 32 * r;
+                    if (e < hd) buf[e] = v[r];
+                }
+                __syncwarp();
+#pragma unroll
+                for (int r = 0; r < NPL; ++r) {
+                    const int e = lane + 32 * r;
+                    if (e < hd) {
+                        const int i = e < half ? e : e - half;
+                        if (i < ang) {
+                            const float x0 = buf[i], x1 = buf[i + half];
+                            v[r] = e < half ? (x0 * cs[i] - x1 * sn[i]) : (x0 * sn[i] + x1 * cs[i]);
+                        }
+                    }
+                }
+            }
+        }
+        TA* dst;
+        if (kind == 0 || !writes_kv) {
+            dst = src;                               // q (and k when nothing is written) in place
+        } else {
+            const int kvh = kind == 1 ? j - nq : j - nq - nkv;
+            const size_t page_stride = (size_t)2 * nkv * ZLM_PAGE * hd;
+            dst = pool + (size_t)page * page_stride + (size_t)(kind - 1) * nkv * ZLM_PAGE * hd +
+                  ((size_t)kvh * ZLM_PAGE + (pos % ZLM_PAGE)) * hd;
+        }
+#pragma unroll
+        for (int r = 0; r < NPL; ++r) {
+            const int e = lane + 32 * r;
+            if (e < hd) dst[e] = from_f32<TA>(v[r]);
+        }
+    }
+}
+

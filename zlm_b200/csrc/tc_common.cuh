@@ -8,7 +8,7 @@
 #define TC_BM 128
 #define TC_BK 64
 #define TC_THREADS 192
-#define TC_WAIT_LIMIT (1u << 24)
+#define TC_WAIT_NS 2000000000ull        // a wait gives up after two seconds
 
 // set when a bounded wait gives up; one copy per translation unit (each has its own status call)
 static __device__ int g_tc_error = 0;
@@ -29,15 +29,29 @@ __device__ __forceinline__ bool mbar_try(uint64_t* bar, unsigned parity) {
         : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
     return ok != 0;
 }
-// bounded wait; false if it gave up (or another role already did)
+// bounded wait; false if it gave up (or another role already did).  The bound is in time: a
+// try_wait may itself block for a while, so counting polls would bound nothing.
+__device__ __forceinline__ unsigned long long tc_now_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(t));
+    return t;
+}
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity, volatile int* abort_flag, int where) {
-    for (unsigned it = 0; it < TC_WAIT_LIMIT; ++it) {
+    if (mbar_try(bar, parity)) return true;
+    const unsigned long long t0 = tc_now_ns();
+    for (unsigned it = 1;; ++it) {
         if (mbar_try(bar, parity)) return true;
         if (*abort_flag) return false;
+        if ((it & 63) == 0 && tc_now_ns() - t0 > TC_WAIT_NS) break;
     }
     *abort_flag = where;
     atomicCAS(&g_tc_error, 0, where);
     return false;
+}
+// after a wait gave up: lets copies that are still in flight land (at most 10 ms each)
+__device__ __forceinline__ void mbar_drain(uint64_t* bar, unsigned parity) {
+    const unsigned long long t0 = tc_now_ns();
+    while (!mbar_try(bar, parity) && tc_now_ns() - t0 < 10000000ull) {}
 }
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
     asm volatile(

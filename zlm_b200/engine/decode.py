@@ -1,12 +1,21 @@
-"""Decode steps as replayed CUDA graphs.
+"""Decode steps as replayed CUDA graphs, or as one persistent kernel.
 
 A decode step (one token for each of R live sequences, logits at every row, one
-sampled token per row) launches a few hundred small kernels; at small batches the
-GPU finishes them faster than the host can launch them.  The step's device work
-is therefore captured once per (R, sampling parameters) and replayed.  All its
-inputs live at fixed device addresses: the per-step integer arrays in the
-engine's staging buffer, the block tables, the scratch buffers; what changes
-from step to step is their content, which is uploaded before the replay.
+sampled token per row) is a chain of a few hundred small operations; launched one
+by one the GPU finishes them faster than the host can launch them.  Both remedies
+rest on the fact that all inputs of a step live at fixed device addresses (the
+per-step integer arrays in the engine's staging buffer, the block tables, the
+scratch buffers) and only their content changes from step to step:
+
+* the step's device work is captured once per (R, length bucket, sampling
+  parameters) as a CUDA graph and replayed: the default;
+* ``use_stream``: bf16 steps of up to 8 rows whose parts launch nothing but the
+  library's kernels are recorded once per (R, length bucket) as a program of the
+  persistent decode kernel (``stream.py``) and run as one cooperative launch.  It
+  gives the same bits as the graph; measured at Qwen3-8B sizes it is slower than
+  the graph (its products stream the weights at 4.4 TB/s against 4.7 TB/s for the
+  stand-alone kernels, and its attention runs on one warp group per SM), so it is
+  off unless asked for.
 
 Sampled tokens stay on the device and can be fed to the next step from there, so
 a run of steps needs no host round trip unless the caller wants the tokens.
@@ -20,19 +29,30 @@ import torch
 
 from ..sampling import SamplingParams
 from .batch import StepError, make_context
+from .stream import MAX_TOKENS as STREAM_MAX_ROWS
+from .stream import NotStreamable, StepRecorder, StreamProgram, stream_blocks
 
 
 class DecodeRunner:
-    def __init__(self, engine, use_graphs: Optional[bool] = None):
+    def __init__(self, engine, use_graphs: Optional[bool] = None, use_stream: Optional[bool] = None):
         self.e = engine
         cuda = engine.device.type == "cuda"
         self.use_graphs = (cuda and engine.model.graph_safe) if use_graphs is None else use_graphs
+        self.stream_blocks = stream_blocks(engine.rt.k) if cuda else 0
+        self.can_stream = bool(cuda and engine.dtype == torch.bfloat16 and engine.model.kernels_only
+                               and self.stream_blocks > 0)
+        self.use_stream = bool(use_stream) and self.can_stream
         # programmatic dependent launch between the step's kernels: off.  Measured at batch 8,
         # Qwen3-8B sizes: 5.32 ms a step with early triggers and weight prefetch before the
         # wait, 4.46 ms with late triggers, 4.49 ms in plain stream order.
         self.use_pdl = False
+        # blocks the decode attention cuts its work for: None lets each path take its own
+        # (what runs at a time: 3 per SM stand-alone, 1 per SM in the persistent kernel)
+        self.attention_blocks: Optional[int] = None
         self.graphs: Dict[Tuple, torch.cuda.CUDAGraph] = {}
         self.graph_generation = -1
+        self.programs: Dict[Tuple, Optional[StreamProgram]] = {}
+        self.program_generation = None
         self.out = torch.zeros(engine.max_batch, dtype=torch.int32, device=engine.device)
         self.last_logits: Optional[torch.Tensor] = None
         self.launches_per_step = 0
@@ -79,10 +99,12 @@ class DecodeRunner:
             e._sample_meta[:, :R].copy_(meta)
         arrays.setdefault("token_ids", ar)   # make_context only needs the shapes
         ctx = make_context(e.stager, arrays, R, R, e.rt.ws)
-        if self.use_graphs:
-            self._replay(ctx, R, params)
-        else:
-            self._device_work(ctx, R, params)
+        ctx.attention_blocks = self.attention_blocks
+        if not (self.use_stream and R <= STREAM_MAX_ROWS and self._run_program(ctx, R, params)):
+            if self.use_graphs:
+                self._replay(ctx, R, params)
+            else:
+                self._device_work(ctx, R, params)
         e.cache.commit(growth)
         e.steps_run += 1
         return self.out[:R]
@@ -99,15 +121,69 @@ class DecodeRunner:
             self._device_work_inner(ctx, R, params)
 
     def _device_work_inner(self, ctx, R: int, params: SamplingParams) -> None:
-        e = self.e
-        logits = e.run_model(ctx, R)
+        logits = self.e.run_model(ctx, R)
         self.last_logits = logits
+        self._choose(logits, R, params)
+
+    def _choose(self, logits: torch.Tensor, R: int, params: SamplingParams) -> None:
+        e = self.e
         meta = e._sample_meta[:, :R]
         if params.greedy:
             e.rt.k.argmax(self.out[:R], logits)
         else:
             e.rt.k.sample(self.out[:R], logits, params.temperature, params.top_k, params.top_p, params.seed,
                           meta[0], meta[1])
+
+    # ------------------------------------------------------------------ the persistent kernel
+    def _run_program(self, ctx, R: int, params: SamplingParams) -> bool:
+        """Runs the step as one launch of the persistent kernel and chooses the tokens; False
+        if this step cannot be a program (the caller then launches the kernels one by one)."""
+        before = self.e.rt.k.launches()
+        ok, logits = self.run_program(ctx, R, R)
+        if not ok:
+            return False
+        self.last_logits = logits
+        self._choose(logits, R, params)
+        self.launches_per_step = self.e.rt.k.launches() - before
+        return True
+
+    def run_program(self, ctx, R: int, wanted: int):
+        """The device work of a step of one token per row (``Engine.run_model``) as one launch
+        of the persistent kernel: (True, logits at the first ``wanted`` of the uploaded rows,
+        or None) or (False, None) if this step cannot be a program."""
+        if not (self.use_stream and ctx.is_decode and ctx.T == R and R <= STREAM_MAX_ROWS):
+            return False, None
+        if self.program_generation != self._generation():
+            self.programs.clear()
+        key = (R, wanted, ctx.len_bucket, ctx.attention_blocks)
+        if key not in self.programs:
+            self.programs[key] = self._record(ctx, wanted)
+            self.program_generation = self._generation()
+        entry = self.programs[key]
+        if entry is None:
+            return False, None
+        prog, logits = entry
+        prog.run()
+        return True, logits
+
+    def _record(self, ctx, wanted: int):
+        """One walk over the model with a recorder in the kernels' place.  Scratch buffers
+        that the walk itself creates or grows move; it is repeated until none did."""
+        e = self.e
+        k = e.rt.k
+        for _ in range(3):
+            gen = self._generation()
+            rec = StepRecorder(k, self.stream_blocks)
+            e.rt.k = rec
+            try:
+                logits = e.run_model(ctx, wanted)
+            except NotStreamable:
+                return None
+            finally:
+                e.rt.k = k
+            if gen == self._generation():
+                return StreamProgram(k, rec, e.device), logits
+        raise RuntimeError("scratch buffers kept moving while the decode program was recorded")
 
     def _generation(self):
         """Changes whenever a scratch buffer that a captured graph may point at has moved."""

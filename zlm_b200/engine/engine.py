@@ -117,7 +117,11 @@ class Engine:
         self.cache.reserve(growth)            # raises before anything is launched
         self.stager.upload(arrays, T, R)
         ctx = make_context(self.stager, arrays, T, R, self.rt.ws)
-        logits = self.run_model(ctx, W)
+        ctx.attention_blocks = self.decoder.attention_blocks
+        # one token per row: the persistent decode kernel, if the step can be its program
+        done, logits = self.decoder.run_program(ctx, R, W)
+        if not done:
+            logits = self.run_model(ctx, W)
         self.cache.commit(growth)
         self.steps_run += 1
         return logits

@@ -32,17 +32,18 @@ def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     return torch.stack([gate.view(I // 8, 8, K), up.view(I // 8, 8, K)], dim=1).reshape(2 * I, K).contiguous()
 
 
-def decode_splits(rows: int, nkv: int, len_bucket: int):
+def decode_splits(rows: int, nkv: int, len_bucket: int, blocks: Optional[int] = None):
     """How the decode attention cuts a sequence's pages: (splits, pages per split).  The
-    parts are sized so that the grid is one wave of the GPU (148 SMs x 3 blocks) for small
-    batches (measured best at batch 8: a block's fixed cost is paid once) and four for large
-    ones (whose blocks are long, so that an unfinished last wave costs more), and are at
-    least two pages long.  ``len_bucket`` is the longest sequence of
-    the step in pages, rounded up, so that the choice (and a captured graph) holds for many
-    steps."""
+    parts are sized so that the work is one wave of the blocks that run at a time (148 SMs
+    x 3 blocks for the stand-alone kernel) for small batches (measured best at batch 8: a
+    block's fixed cost is paid once) and four for large ones (whose blocks are long, so
+    that an unfinished last wave costs more), and are at least two pages long.
+    ``len_bucket`` is the longest sequence of the step in pages, rounded up, so that the
+    choice (and a captured graph) holds for many steps."""
+    blocks = blocks or 444
     work = len_bucket * rows * nkv
-    waves = 4 if work >= 8 * 444 else 1
-    per = max(2, -(-work // (444 * waves)))
+    waves = 4 if work >= 8 * blocks else 1
+    per = max(2, -(-work // (blocks * waves)))
     per = min(per, max(1, len_bucket))
     splits = -(-len_bucket // per)
     while splits > 1024:
@@ -238,7 +239,7 @@ class CudaKernels:
         assert tuple(pool.shape[1:]) == (2, nkv, PAGE_TOKENS, hd)
         if (plan is not None and plan.is_decode and q.dtype == torch.bfloat16
                 and self.lib.zlm_attention_decode_supported(nq, nkv, hd)):
-            splits, per = decode_splits(T, nkv, plan.len_bucket)
+            splits, per = decode_splits(T, nkv, plan.len_bucket, getattr(plan, "attention_blocks", None))
             part_o = part_ml = None
             if splits > 1:
                 part_o = plan.scratch("attn.part_o", (T * nq * splits * hd,), torch.float32)
@@ -295,6 +296,11 @@ class CudaKernels:
         """0 unless a bounded wait inside a tcgen05 kernel (product or attention) ever gave up
         (synchronises)."""
         return int(self.lib.zlm_gemm_tc_status()) or int(self.lib.zlm_attention_tc_status())
+
+    def stream_status(self) -> int:
+        """0 unless a bounded wait inside the persistent decode kernel ever gave up
+        (synchronises)."""
+        return int(self.lib.zlm_stream_status())
 
     def sample(self, out: torch.Tensor, logits: torch.Tensor, temperature: float, top_k: int, top_p: float,
                seed: int, request: torch.Tensor, position: torch.Tensor) -> None:

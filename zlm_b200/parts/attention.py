@@ -53,6 +53,10 @@ class GQAAttention(Mixer):
     def cache_request(self) -> Optional[CacheRequest]:
         return CacheRequest(self.nkv, self.hd, self.window)
 
+    @property
+    def kernels_only(self) -> bool:      # type: ignore[override]
+        return bool(getattr(self.position, "kernels_only", False))
+
     def attach(self, rt) -> None:
         super().attach(rt)
         self.position.attach(rt)

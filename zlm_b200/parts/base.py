@@ -132,6 +132,7 @@ class StepContext:
     max_len: int = 0          # longest sequence after this step
     len_bucket: int = 1       # max_len in pages, rounded up (powers of two to 8, then multiples of 8)
     workspace: Any = None     # the runtime's Workspace
+    attention_blocks: Optional[int] = None    # blocks the decode attention sizes its splits for (None: its default)
     extras: Dict[str, Any] = field(default_factory=dict)
 
     def scratch(self, name: str, shape, dtype) -> torch.Tensor:
@@ -155,6 +156,10 @@ class Part:
     # a part whose forward launches only kernels (no host-side branching on
     # device data, no allocation) may be captured in a CUDA graph
     graph_safe = True
+    # a part whose forward does its device work through the methods of ``rt.k`` alone (no
+    # torch operation, no kernel of its own) can also be recorded as part of a program of
+    # the persistent decode kernel; a part has to say so itself
+    kernels_only = False
 
 
 class Norm(Part):

@@ -30,6 +30,10 @@ class PreNormBlock(Part):
     def graph_safe(self) -> bool:      # type: ignore[override]
         return all(c.graph_safe for c in self.children().values())
 
+    @property
+    def kernels_only(self) -> bool:      # type: ignore[override]
+        return all(getattr(c, "kernels_only", False) for c in self.children().values())
+
     def forward(self, hidden: torch.Tensor, ctx: StepContext, io: LayerIO) -> None:
         rt = self.rt
         x = rt.ws.get("block.normed", hidden.shape, rt.dtype)

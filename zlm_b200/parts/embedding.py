@@ -16,6 +16,8 @@ from .base import ParamSpec, Part
 
 @register_embedding("token_embedding")
 class TokenEmbedding(Part):
+    kernels_only = True
+
     def __init__(self, vocab_size: int, hidden_size: int):
         self.vocab, self.hidden = int(vocab_size), int(hidden_size)
         self.weight: Optional[torch.Tensor] = None
@@ -32,6 +34,8 @@ class TokenEmbedding(Part):
 
 @register_head("lm_head")
 class LMHead(Part):
+    kernels_only = True
+
     def __init__(self, vocab_size: int, hidden_size: int, tied: bool):
         self.vocab, self.hidden, self.tied = int(vocab_size), int(hidden_size), bool(tied)
         self.weight: Optional[torch.Tensor] = None

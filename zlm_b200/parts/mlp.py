@@ -16,6 +16,8 @@ from .base import FeedForward, ParamSpec, StepContext
 
 @register_feed_forward("swiglu")
 class SwiGLU(FeedForward):
+    kernels_only = True
+
     def __init__(self, hidden_size: int, intermediate_size: int):
         self.hidden = int(hidden_size)
         self.inter = int(intermediate_size)

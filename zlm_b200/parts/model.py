@@ -84,6 +84,12 @@ class DecoderModel:
     def graph_safe(self) -> bool:
         return all(b.graph_safe for b in self.blocks)
 
+    @property
+    def kernels_only(self) -> bool:
+        """Every part does its device work through the kernel object alone."""
+        parts = list(self.blocks) + [self.embedding, self.final_norm, self.head]
+        return all(getattr(p, "kernels_only", False) for p in parts)
+
     # ---- the step -------------------------------------------------------------
     def forward(self, ctx: StepContext, ios: List[LayerIO]) -> torch.Tensor:
         """Runs the step's tokens through every schedule entry; returns the fp32
