@@ -135,3 +135,81 @@ def test_sampling_params_and_uniforms():
     assert all(0.0 <= u < 1.0 for u in us) and len(set(us)) > 990
     assert abs(sum(us) / len(us) - 0.5) < 0.03
     assert uniform_for(3, 1, 2) == uniform_for(3, 1, 2) != uniform_for(4, 1, 2)
+
+
+class QueueingEngine(ScriptedEngine):
+    """The scripted engine with steps that can be queued one ahead, as the GPU engine has
+    them: a step fed ``None`` takes, for the same rows, the tokens that the step queued
+    before it sampled.  A row of such a step that had already met its stop token computes
+    something nobody looks at; every row that goes on must have been fed its own token."""
+
+    def __init__(self, *a, **kw):
+        super().__init__(*a, **kw)
+        self.unfetched = 0
+        self.last = None                      # (requests, sampled) of the newest queued step
+        self.wasted = 0
+
+    def decode_launch(self, slots, tokens, params, requests):
+        assert self.unfetched < 2, "more than two steps in flight"
+        if tokens is None:
+            assert self.last is not None and list(requests) == self.last[0], "a step fed from the device must keep its rows"
+            tokens = self.last[1]
+        sampled = []
+        for s, r, tok in zip(slots, requests, tokens):
+            assert s in self.held, "a freed slot was stepped"
+            self.held[s] += 1
+            assert self.held[s] <= self.max_seq_len
+            i = self.cursor.get(r, 0)
+            if i > 0 and self.script[r][i - 1] == 99 and 99 in self.stop_ids:
+                self.wasted += 1                                   # the row met its stop token one step ago
+                sampled.append(-1)
+                continue
+            assert tok == self.script[r][i - 1], f"request {r} was fed {tok}, its last token is {self.script[r][i - 1]}"
+            sampled.append(self._next(r))
+        self.log.append(("decode", list(requests), list(tokens)))
+        self.last = (list(requests), sampled)
+        self.unfetched += 1
+        return sampled
+
+    def decode_fetch(self, handle):
+        self.unfetched -= 1
+        return handle
+
+    def decode_sample(self, *a):
+        raise AssertionError("the loop should queue its steps")
+
+    stop_ids = (99,)
+
+
+@pytest.mark.parametrize("max_tokens", [1, 2, 4, 7])
+def test_steps_queued_one_ahead_give_the_same_tokens(max_tokens):
+    script = {0: [1, 2, 99, 50, 51, 52, 53, 54], 1: [3, 99, 60, 61, 62, 63, 64, 65], 2: [4, 5, 6, 7, 8, 9, 10, 11],
+              3: [99, 70, 71, 72, 73, 74, 75, 76], 4: [10, 11, 12, 13, 14, 15, 16, 17], 5: [20, 21, 22, 23, 24, 99, 25, 26]}
+    prompts = [[1] * 5, [2] * 3, [3] * 9, [4] * 2, [5] * 7, [6] * 4]
+    plain = ScriptedEngine(script)
+    want = generate(plain, prompts, max_tokens=max_tokens)
+    seen = []
+    eng = QueueingEngine(script)
+    got = generate(eng, prompts, max_tokens=max_tokens, on_token=lambda r, t: seen.append((r, t)))
+    assert got.tokens == want.tokens and got.finish_reasons == want.finish_reasons
+    assert eng.held == {} and eng.unfetched == 0 and eng.max_live == 3
+    for r, toks in enumerate(got.tokens):
+        assert [t for q, t in seen if q == r] == toks          # every token reported once, in order
+    # a row is computed for nothing at most once: in the step queued before its stop token was read
+    assert eng.wasted <= sum(reason == "stop" for reason in got.finish_reasons)
+
+
+def test_queued_steps_respect_the_context_limit_and_failures():
+    eng = QueueingEngine({0: list(range(1, 50))}, max_seq_len=12)
+    res = generate(eng, [[7] * 10], max_tokens=40)
+    assert res.tokens == [[1, 2, 3]] and res.finish_reasons == ["context"] and eng.held == {}
+
+    class Failing(QueueingEngine):
+        def decode_launch(self, *a):
+            if len(self.log) >= 2:
+                raise RuntimeError("boom")
+            return super().decode_launch(*a)
+    eng = Failing({0: [1, 2, 3, 4], 1: [3, 4, 5, 6]})
+    with pytest.raises(RuntimeError, match="boom"):
+        generate(eng, [[1], [2]], max_tokens=4)
+    assert eng.held == {}

@@ -253,3 +253,110 @@ def test_attention_part_alone_with_another_position_encoding():
     f = (1.0 + 0.01 * pos.float())[:, None, None]
     want = P.linear(P.causal_attention(q * f, k / f, v).reshape(T, nq * hd), w["o_proj.weight"])
     torch.testing.assert_close(res.cpu(), want, atol=2e-5, rtol=1e-4)
+
+
+def test_toy_routed_feed_forward_in_one_layer_of_two():
+    """A feed-forward with routing of its own (two experts, the router's argmax picks one
+    per token), defined here, sits in the first layer of a two-layer model whose second
+    layer keeps the dense SwiGLU: feed-forwards are chosen layer by layer, and the
+    framework's files do not change.  (A toy: it is no model of anyone's.)"""
+    from zlm_b200 import Engine, StepEntry
+    from zlm_b200.config import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
+    from zlm_b200.parts.base import FeedForward, ParamSpec
+    from zlm_b200.parts.model import DecoderModel
+    from zlm_b200.registry import ARCHITECTURES, FEED_FORWARDS, register_architecture, register_feed_forward
+    from zlm_b200.weights import random_tensors
+
+    if "toy_two_experts" not in FEED_FORWARDS:
+        @register_feed_forward("toy_two_experts")
+        class TwoExperts(FeedForward):
+            graph_safe = False
+
+            def __init__(self, hidden_size, width):
+                self.h, self.w = hidden_size, width
+
+            def param_specs(self):
+                return {"router.weight": ParamSpec((2, self.h)), "up.weight": ParamSpec((2 * self.w, self.h)),
+                        "down.weight": ParamSpec((2 * self.h, self.w))}
+
+            def bind(self, params):
+                self.router = params["router.weight"].float()
+                self.up = params["up.weight"].float().view(2, self.w, self.h)
+                self.down = params["down.weight"].float().view(2, self.h, self.w)
+
+            def forward(self, x, residual, ctx):
+                xf = x.float()
+                pick = (xf @ self.router.t()).argmax(-1)                       # router logits in fp32
+                for e in range(2):
+                    rows = (pick == e).nonzero()[:, 0]
+                    if rows.numel():
+                        residual[rows] += torch.relu(xf[rows] @ self.up[e].t()) @ self.down[e].t()
+
+    if "ToyRoutedForCausalLM" not in ARCHITECTURES:
+        @register_architecture("ToyRoutedForCausalLM")
+        @dataclass(frozen=True)
+        class ToyRoutedConfig:
+            eos_token_ids: tuple = ()
+
+            @classmethod
+            def from_dict(cls, d):
+                return cls()
+
+            def to_dict(self):
+                return {"architectures": ["ToyRoutedForCausalLM"]}
+
+            def to_model_spec(self):
+                norm = lambda p: PartSpec("rms_norm", {"eps": 1e-5}, prefix=p)
+                att = lambda p: PartSpec("gqa_attention", {
+                    "num_heads": 2, "num_kv_heads": 1, "head_dim": 16, "qk_norm": True,
+                    "position": {"kind": "rope_half_split", "theta": 1000.0, "head_dim": 16, "n_rot": 16}}, prefix=p)
+                l0 = LayerSpec("pre_norm", att("l0.att."), PartSpec("toy_two_experts", {"width": 24}, prefix="l0.moe."),
+                               norm("l0.n1."), norm("l0.n2."))
+                l1 = LayerSpec("pre_norm", att("l1.att."), PartSpec("swiglu", {"intermediate_size": 40}, prefix="l1.ffn."),
+                               norm("l1.n1."), norm("l1.n2."))
+                return ModelSpec("ToyRoutedForCausalLM", 32, 70, 256, (l0, l1), (ScheduleEntry(0), ScheduleEntry(1)),
+                                 PartSpec("token_embedding", {}, prefix="emb."), norm("out_norm."),
+                                 PartSpec("lm_head", {"tied": False}, prefix="head."))
+
+    cfg = ARCHITECTURES["ToyRoutedForCausalLM"]()
+    t = random_tensors(DecoderModel(cfg.to_model_spec()).param_specs(), 7)
+    for n in t:
+        if "router" in n:
+            t[n] = t[n] * 50            # clear decisions: no token sits on the fence
+    eng = Engine(cfg, {n: v.cuda() for n, v in t.items()}, torch.float32, "cuda:0", max_tokens=512, max_batch=4)
+
+    def reference(ids):
+        T = len(ids)
+        h = P.embed(t["emb.weight"], ids)
+        pos = torch.arange(T)
+        for l in ("l0", "l1"):
+            x = P.rms_norm(h, t[f"{l}.n1.weight"], 1e-5)
+            q = P.head_rms_norm(P.linear(x, t[f"{l}.att.q_proj.weight"]).reshape(T, 2, 16), t[f"{l}.att.q_norm.weight"], 1e-6)
+            k = P.head_rms_norm(P.linear(x, t[f"{l}.att.k_proj.weight"]).reshape(T, 1, 16), t[f"{l}.att.k_norm.weight"], 1e-6)
+            v = P.linear(x, t[f"{l}.att.v_proj.weight"]).reshape(T, 1, 16)
+            q, k = P.rope_half_split(q, pos, 1000.0, 16), P.rope_half_split(k, pos, 1000.0, 16)
+            h = h + P.linear(P.causal_attention(q, k, v).reshape(T, 32), t[f"{l}.att.o_proj.weight"])
+            x = P.rms_norm(h, t[f"{l}.n2.weight"], 1e-5)
+            if l == "l0":
+                pick = (x @ t["l0.moe.router.weight"].t()).argmax(-1)
+                up = t["l0.moe.up.weight"].view(2, 24, 32)
+                down = t["l0.moe.down.weight"].view(2, 32, 24)
+                y = torch.stack([torch.relu(x[i] @ up[pick[i]].t()) @ down[pick[i]].t() for i in range(T)])
+                assert 0 < int(pick.sum()) < T, "both experts should be used"
+                h = h + y
+            else:
+                h = h + P.linear(P.swiglu(P.linear(x, t["l1.ffn.gate_proj.weight"]), P.linear(x, t["l1.ffn.up_proj.weight"])),
+                                 t["l1.ffn.down_proj.weight"])
+        return P.linear(P.rms_norm(h, t["out_norm.weight"], 1e-5), t["head.weight"])
+
+    g = torch.Generator().manual_seed(8)
+    seqs = [torch.randint(0, 70, (n,), generator=g).tolist() for n in (40, 13)]
+    slots = [eng.new_sequence() for _ in seqs]
+    got = eng.step([StepEntry(sl, s[:10], list(range(10))) for sl, s in zip(slots, seqs)]).cpu()
+    want = [reference(s) for s in seqs]
+    torch.testing.assert_close(got[:10], want[0][:10], atol=2e-5, rtol=1e-4)
+    torch.testing.assert_close(got[10:], want[1][:10], atol=2e-5, rtol=1e-4)
+    for i in range(10, 13):                                    # then token by token, from the cache
+        got = eng.step([StepEntry(sl, [s[i]], [0]) for sl, s in zip(slots, seqs)]).cpu()
+        torch.testing.assert_close(got[0], want[0][i], atol=2e-5, rtol=1e-4)
+        torch.testing.assert_close(got[1], want[1][i], atol=2e-5, rtol=1e-4)

@@ -19,7 +19,12 @@
 #define GEMV_WARPS 8
 #define GEMV_THREADS (GEMV_WARPS * 32)
 #define GEMV_ROWS 16
+#ifndef GEMV_UNROLL
 #define GEMV_UNROLL 4
+#endif
+#ifndef GEMV_MINBLOCKS
+#define GEMV_MINBLOCKS 1
+#endif
 
 __device__ __forceinline__ uint4 ld_stream16(const void* p) {
     uint4 v;
@@ -39,7 +44,7 @@ __device__ __forceinline__ void gemv_mma(float* c, unsigned a0, unsigned a1, uns
 // MODE 0: Y bf16 = acc; MODE 1: Y fp32 += acc; MODE 2: Y fp32 = acc; MODE 3: the block's 16 rows are
 // 8 gate + 8 up channels, Y bf16 [T, N/2] = silu(gate) * up.  NT: token tiles of 8.
 template <int NT, int MODE>
-__global__ void __launch_bounds__(GEMV_THREADS)
+__global__ void __launch_bounds__(GEMV_THREADS, GEMV_MINBLOCKS)
 gemv_bf16_kernel(void* __restrict__ Y, const __nv_bfloat16* __restrict__ X,
                  const __nv_bfloat16* __restrict__ W, int T, int N, int K, int ldx, int ldy) {
     __shared__ float red[GEMV_WARPS][NT][GEMV_ROWS][8];

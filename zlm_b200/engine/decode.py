@@ -54,6 +54,10 @@ class DecodeRunner:
         self.programs: Dict[Tuple, Optional[StreamProgram]] = {}
         self.program_generation = None
         self.out = torch.zeros(engine.max_batch, dtype=torch.int32, device=engine.device)
+        # where queued steps leave their tokens for the host: two buffers, so that a step can be
+        # queued while the one before it is still being read
+        self._landing = [torch.zeros(engine.max_batch, dtype=torch.int32, pin_memory=cuda) for _ in range(2)]
+        self._flip = 0
         self.last_logits: Optional[torch.Tensor] = None
         self.launches_per_step = 0
 
@@ -108,6 +112,29 @@ class DecodeRunner:
         e.cache.commit(growth)
         e.steps_run += 1
         return self.out[:R]
+
+    # ------------------------------------------------------------------ queued steps
+    def launch(self, slots: Sequence[int], tokens: Optional[Sequence[int]], params: SamplingParams,
+               requests: Optional[Sequence[int]] = None):
+        """``step`` without waiting: the sampled ids are copied to pinned host memory in stream
+        order (before a later step can overwrite them on the device).  At most two steps may
+        be unfetched at a time."""
+        R = len(slots)
+        out = self.step(slots, tokens, params, requests)
+        buf = self._landing[self._flip]
+        self._flip ^= 1
+        buf[:R].copy_(out, non_blocking=True)
+        done = None
+        if self.e.device.type == "cuda":
+            done = torch.cuda.Event()
+            done.record()
+        return done, buf, R
+
+    def fetch(self, handle) -> List[int]:
+        done, buf, R = handle
+        if done is not None:
+            done.synchronize()
+        return buf[:R].tolist()
 
     # ------------------------------------------------------------------ device work
     def _device_work(self, ctx, R: int, params: SamplingParams) -> None:

@@ -152,6 +152,17 @@ class Engine:
         """One decode step: feeds one token per row, returns the next ones on the host."""
         return self.decoder.step(slots, tokens, params, requests).tolist()
 
+    def decode_launch(self, slots: Sequence[int], tokens: Optional[Sequence[int]], params,
+                      requests: Sequence[int]):
+        """Queues one decode step and returns at once with a handle for ``decode_fetch``.
+        ``tokens`` None feeds, for the same rows in the same order, the tokens that the
+        step queued before this one samples; they never leave the device."""
+        return self.decoder.launch(slots, tokens, params, requests)
+
+    def decode_fetch(self, handle) -> List[int]:
+        """Waits for a queued step and returns its sampled token ids."""
+        return self.decoder.fetch(handle)
+
     def generate(self, prompts: Sequence[Sequence[int]], max_tokens: int = 256, temperature: float = 0.0,
                  top_k: int = 0, top_p: float = 1.0, seed: int = 0,
                  stop_token_ids: Optional[Sequence[int]] = None, include_stop: bool = False, on_token=None):

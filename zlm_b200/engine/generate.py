@@ -92,6 +92,12 @@ class BatchDecisions:
         self.max_seq_len = int(max_seq_len)
         self.include_stop = include_stop
 
+    def goes_on_unless_stopped(self, row: _Row) -> bool:
+        """Whether ``row`` will be live after the token of the step in flight, whatever
+        that token is, as long as it is no stop token (``row.length`` counts the token
+        that step feeds)."""
+        return len(row.out) + 1 < self.max_tokens and row.length + 1 <= self.max_seq_len
+
     def apply(self, rows: List[_Row], sampled: Sequence[int]) -> Tuple[List[_Row], List[_Row]]:
         """Returns (rows that go on and feed their new token, rows that ended)."""
         live, ended = [], []
@@ -129,7 +135,10 @@ def generate(engine, prompts: Sequence[Sequence[int]], max_tokens: int = 256,
     ``engine`` needs: config.eos_token_ids, max_tokens, max_batch, max_seq_len,
     new_sequence(), release(slot), prefill_sample(slots, prompts, params, requests)
     and decode_sample(slots, tokens, params, requests), both returning one token id
-    per row on the host."""
+    per row on the host.  If it also has decode_launch(slots, tokens or None, params,
+    requests) -> handle (queues a step; None feeds the tokens the step before sampled
+    for the same rows) and decode_fetch(handle) -> token ids, steps are queued one
+    ahead."""
     sampling = sampling or SamplingParams()
     if stop_token_ids is None:
         stop_token_ids = tuple(getattr(engine.config, "eos_token_ids", ()))
@@ -156,10 +165,11 @@ def generate(engine, prompts: Sequence[Sequence[int]], max_tokens: int = 256,
             stats.prefill_ms += (time.perf_counter() - t0) * 1e3
             stats.prefill_steps += 1
             stats.prompt_tokens += sum(r.length for r in rows)
-            while rows:
-                before = [len(r.out) for r in rows]
-                live, ended = decide.apply(rows, sampled)
-                for r, b in zip(rows, before):
+            def settle(rows_, sampled_):
+                """Applies one step's tokens: emits, frees the rows that ended; returns the live rows."""
+                before = [len(r.out) for r in rows_]
+                live, ended = decide.apply(rows_, sampled_)
+                for r, b in zip(rows_, before):
                     if on_token is not None and len(r.out) > b:
                         for tok in r.out[b:]:
                             on_token(r.request, tok)
@@ -167,16 +177,57 @@ def generate(engine, prompts: Sequence[Sequence[int]], max_tokens: int = 256,
                     engine.release(r.slot)
                     r.slot = -1
                     tokens[r.request], reasons[r.request] = r.out, r.reason
-                rows = live
-                if not rows:
-                    break
+                return live
+
+            rows = settle(rows, sampled)
+            launch = getattr(engine, "decode_launch", None)
+            if launch is None:
+                # one step at a time: feed, wait, decide
+                while rows:
+                    t0 = time.perf_counter()
+                    sampled = engine.decode_sample([r.slot for r in rows], [r.out[-1] for r in rows], sampling,
+                                                   [r.request for r in rows])
+                    for r in rows:
+                        r.length += 1
+                    stats.decode_ms += (time.perf_counter() - t0) * 1e3
+                    stats.decode_steps += 1
+                    rows = settle(rows, sampled)
+            else:
+                # One step ahead: while the device runs a step, the next one is already queued with
+                # the tokens it is about to sample (they stay on the device), and the host reads the
+                # tokens of the step before.  A step is queued ahead only if every row goes on
+                # unless it meets a stop token; when one does, the queued step has computed that
+                # row for nothing (its slot is freed all the same) and the rows that go on take
+                # their tokens from it.  After any change of the rows the next step is fed from the
+                # host again.
                 t0 = time.perf_counter()
-                sampled = engine.decode_sample([r.slot for r in rows], [r.out[-1] for r in rows], sampling,
-                                               [r.request for r in rows])
-                for r in rows:
-                    r.length += 1
+                cur = None
+                while rows:
+                    if cur is None:
+                        cur = launch([r.slot for r in rows], [r.out[-1] for r in rows], sampling,
+                                     [r.request for r in rows])
+                        for r in rows:
+                            r.length += 1
+                    ahead = None
+                    if all(decide.goes_on_unless_stopped(r) for r in rows):
+                        ahead = launch([r.slot for r in rows], None, sampling, [r.request for r in rows])
+                    sampled = engine.decode_fetch(cur)
+                    stats.decode_steps += 1
+                    was = rows
+                    rows = settle(rows, sampled)
+                    cur = None
+                    if ahead is None:
+                        continue
+                    for r in rows:
+                        r.length += 1                    # the queued step fed their token
+                    if len(rows) == len(was):
+                        cur = ahead
+                        continue
+                    sampled = engine.decode_fetch(ahead)
+                    stats.decode_steps += 1
+                    keep = {id(r) for r in rows}
+                    rows = settle(rows, [t for r, t in zip(was, sampled) if id(r) in keep])
                 stats.decode_ms += (time.perf_counter() - t0) * 1e3
-                stats.decode_steps += 1
         finally:
             for r in rows:
                 if r.slot >= 0:

@@ -33,16 +33,18 @@ def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
 
 
 def decode_splits(rows: int, nkv: int, len_bucket: int, blocks: Optional[int] = None):
-    """How the decode attention cuts a sequence's pages: (splits, pages per split).  The
-    parts are sized so that the work is one wave of the blocks that run at a time (148 SMs
-    x 3 blocks for the stand-alone kernel) for small batches (measured best at batch 8: a
-    block's fixed cost is paid once) and four for large ones (whose blocks are long, so
-    that an unfinished last wave costs more), and are at least two pages long.
+    """How the decode attention cuts a sequence's pages: (splits, pages per split).  A
+    block's start (the query, its first pages) and end (merging its warps, writing its
+    partial result) cost about as much as several pages, so the parts are as long as they
+    can be while every block that runs at a time (148 SMs x 3 for the stand-alone kernel)
+    still has one: one wave of blocks, two for large batches (measured at 2,100 tokens:
+    batch 16 4.2 TB/s with one wave against 3.7 with two; batch 64 5.7 TB/s with two
+    against 5.5 with four and 4.6 with sixteen), and at least two pages long.
     ``len_bucket`` is the longest sequence of the step in pages, rounded up, so that the
     choice (and a captured graph) holds for many steps."""
     blocks = blocks or 444
     work = len_bucket * rows * nkv
-    waves = 4 if work >= 8 * blocks else 1
+    waves = 2 if work >= 16 * blocks else 1
     per = max(2, -(-work // (blocks * waves)))
     per = min(per, max(1, len_bucket))
     splits = -(-len_bucket // per)
