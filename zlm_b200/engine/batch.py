@@ -35,7 +35,7 @@ class MetaLayout:
     them; their addresses depend only on (T, R), which is what a captured decode
     graph is keyed by."""
     ORDER = ("token_ids", "token_pos", "token_slot", "token_seq", "seq_slot", "seq_start", "seq_new",
-             "cu_seqlens", "want_rows")
+             "cu_seqlens", "want_rows", "sample_request", "sample_position")
 
     def __init__(self, max_tokens: int, max_seqs: int):
         self.max_tokens, self.max_seqs = int(max_tokens), int(max_seqs)
@@ -45,11 +45,14 @@ class MetaLayout:
     def offsets(T: int, R: int):
         return {"token_ids": 0, "token_pos": T, "token_slot": 2 * T, "token_seq": 3 * T,
                 "seq_slot": 4 * T, "seq_start": 4 * T + R, "seq_new": 4 * T + 2 * R,
-                "cu_seqlens": 4 * T + 3 * R, "want_rows": 4 * T + 4 * R + 1}
+                "cu_seqlens": 4 * T + 3 * R, "want_rows": 4 * T + 4 * R + 1,
+                # per row of a sampling decode step: the request's number and the position of the
+                # token being chosen (what the sampler's random numbers are counted by)
+                "sample_request": 5 * T + 4 * R + 1, "sample_position": 5 * T + 5 * R + 1}
 
     @staticmethod
     def used(T: int, R: int) -> int:
-        return 5 * T + 4 * R + 1
+        return 5 * T + 6 * R + 1
 
 
 class MetaStager:

@@ -94,13 +94,13 @@ class DecodeRunner:
             if tok.min() < 0 or tok.max() >= e.spec.vocab_size:
                 raise StepError(f"a token id is outside the vocabulary [0, {e.spec.vocab_size})")
             arrays["token_ids"] = tok.astype(np.int32)
+        if not params.greedy:
+            # they travel with the step's other integers: nothing here waits for the device
+            arrays["sample_request"] = np.asarray(requests if requests is not None else range(R), np.int32)
+            arrays["sample_position"] = start + 1
         e.stager.upload(arrays, R, R)
         if tokens is None:
             e.stager.view("token_ids", R).copy_(self.out[:R])
-        if not params.greedy:
-            req = np.asarray(requests if requests is not None else range(R), np.int32)
-            meta = torch.from_numpy(np.stack([req, start + 1]))
-            e._sample_meta[:, :R].copy_(meta)
         arrays.setdefault("token_ids", ar)   # make_context only needs the shapes
         ctx = make_context(e.stager, arrays, R, R, e.rt.ws)
         ctx.attention_blocks = self.attention_blocks
@@ -154,12 +154,11 @@ class DecodeRunner:
 
     def _choose(self, logits: torch.Tensor, R: int, params: SamplingParams) -> None:
         e = self.e
-        meta = e._sample_meta[:, :R]
         if params.greedy:
             e.rt.k.argmax(self.out[:R], logits)
         else:
             e.rt.k.sample(self.out[:R], logits, params.temperature, params.top_k, params.top_p, params.seed,
-                          meta[0], meta[1])
+                          e.stager.view("sample_request", R), e.stager.view("sample_position", R))
 
     # ------------------------------------------------------------------ the persistent kernel
     def _run_program(self, ctx, R: int, params: SamplingParams) -> bool:
