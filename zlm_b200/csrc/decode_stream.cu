@@ -434,14 +434,14 @@ __device__ __noinline__ void st_attn_items(const ZlmStreamOp* op, unsigned char*
     }
 }
 
-template <int NPL>
+template <int NPL, bool VEC>
 __device__ __noinline__ void st_rope_items(const ZlmStreamOp* op, float* sm, int gtid, GroupSync gs, int vgroup,
                                               int n_groups) {
     const int T = op->i[0], nq = op->i[5], nkv = op->i[6];
     const int chunks = (nq + 2 * nkv + ROPE_WARPS - 1) / ROPE_WARPS;
     VecW qw{op->p[1], op->i[9]}, kw{op->p[2], op->i[9]};
     for (int it = vgroup; it < T * chunks; it += n_groups) {
-        qk_norm_rope_write_item<__nv_bfloat16, NPL, false>(
+        qk_norm_rope_write_item<__nv_bfloat16, NPL, false, VEC>(
             sm, gtid, gs, it % T, it / T, (__nv_bfloat16*)op->p[0], op->i[1], qw, kw, op->i[2], op->f[0],
             (const float*)op->p[3], op->i[3], (const int*)op->p[4], (const int*)op->p[5], (const int*)op->p[6],
             op->i[4], (__nv_bfloat16*)op->p[7], nq, nkv, op->i[7], op->i[8], ROPE_WARPS);
@@ -483,9 +483,12 @@ __device__ __forceinline__ void st_other(const ZlmStreamOp* op, const StreamCtx&
         const int hd = op->i[7];
         float* sm = (float*)(area + group * (ST_GROUP_BYTES / 2));
         const int vg = blockIdx.x * 2 + group, ng = gridDim.x * 2;
-        if (hd <= 32) st_rope_items<1>(op, sm, gtid, gs, vg, ng);
-        else if (hd <= 64) st_rope_items<2>(op, sm, gtid, gs, vg, ng);
-        else st_rope_items<4>(op, sm, gtid, gs, vg, ng);
+        // the same form as the stand-alone kernel takes (the recorder asked zlm_rope_vector_form)
+        if (op->i[10] && hd == 64) st_rope_items<2, true>(op, sm, gtid, gs, vg, ng);
+        else if (op->i[10] && hd == 128) st_rope_items<4, true>(op, sm, gtid, gs, vg, ng);
+        else if (hd <= 32) st_rope_items<1, false>(op, sm, gtid, gs, vg, ng);
+        else if (hd <= 64) st_rope_items<2, false>(op, sm, gtid, gs, vg, ng);
+        else st_rope_items<4, false>(op, sm, gtid, gs, vg, ng);
         break;
     }
     case ZLM_STREAM_ATTN: {

@@ -7,7 +7,7 @@
 #include "common.cuh"
 #include "rope_kv.cuh"
 
-template <typename TA, int NPL>
+template <typename TA, int NPL, bool VEC>
 __global__ void __launch_bounds__(ROPE_WARPS * 32)
 qk_norm_rope_write_kernel(
     TA* __restrict__ qkv, int row_stride, VecW qw, VecW kw, int has_norm, float eps,
@@ -15,13 +15,13 @@ qk_norm_rope_write_kernel(
     const int* __restrict__ token_slot, const int* __restrict__ block_table, int table_stride,
     TA* __restrict__ pool, int nq, int nkv, int hd, int writes_kv, int heads_per_block) {
     extern __shared__ float sm[];
-    qk_norm_rope_write_item<TA, NPL, true>(sm, threadIdx.x, GroupSync{0, ROPE_WARPS * 32}, blockIdx.x, blockIdx.y,
-                                           qkv, row_stride, qw, kw, has_norm, eps, inv_freq, n_rot, token_pos,
-                                           token_slot, block_table, table_stride, pool, nq, nkv, hd, writes_kv,
-                                           heads_per_block);
+    qk_norm_rope_write_item<TA, NPL, true, VEC>(sm, threadIdx.x, GroupSync{0, ROPE_WARPS * 32}, blockIdx.x, blockIdx.y,
+                                                qkv, row_stride, qw, kw, has_norm, eps, inv_freq, n_rot, token_pos,
+                                                token_slot, block_table, table_stride, pool, nq, nkv, hd, writes_kv,
+                                                heads_per_block);
 }
 
-template <typename TA, int NPL>
+template <typename TA, int NPL, bool VEC>
 static void launch_rope(void* qkv, int row_stride, VecW qw, VecW kw, int has_norm, float eps,
                         const float* inv_freq, int n_rot, const int* token_pos, const int* token_slot,
                         const int* block_table, int table_stride, void* pool, int nq, int nkv, int hd,
@@ -32,9 +32,17 @@ static void launch_rope(void* qkv, int row_stride, VecW qw, VecW kw, int has_nor
     const int heads = nq + 2 * nkv;
     const int hpb = T >= 512 ? heads : ROPE_WARPS;
     dim3 grid(T, (heads + hpb - 1) / hpb);
-    zlm_launch(qk_norm_rope_write_kernel<TA, NPL>, grid, dim3(ROPE_WARPS * 32), smem, st,
+    zlm_launch(qk_norm_rope_write_kernel<TA, NPL, VEC>, grid, dim3(ROPE_WARPS * 32), smem, st,
         (TA*)qkv, row_stride, qw, kw, has_norm, eps, inv_freq, n_rot, token_pos, token_slot, block_table,
         table_stride, (TA*)pool, nq, nkv, hd, writes_kv, hpb);
+}
+
+// 1 if the vector form takes these heads: head_dim 64, 128 or 256 and rows (and the pool) aligned
+// for a lane's head_dim / 32 elements
+extern "C" int zlm_rope_vector_form(int hd, int elem_bytes, int row_stride, const void* qkv, const void* pool) {
+    if (hd != 64 && hd != 128 && hd != 256) return 0;
+    const size_t bytes = (size_t)(hd / 32) * elem_bytes;
+    return ((uintptr_t)qkv % bytes == 0 && (uintptr_t)pool % bytes == 0 && ((size_t)row_stride * elem_bytes) % bytes == 0) ? 1 : 0;
 }
 
 template <typename TA>
@@ -42,13 +50,19 @@ static void dispatch_rope(int hd, void* qkv, int row_stride, VecW qw, VecW kw, i
                           const float* inv_freq, int n_rot, const int* token_pos, const int* token_slot,
                           const int* block_table, int table_stride, void* pool, int nq, int nkv,
                           int writes_kv, int T, cudaStream_t st) {
-#define ZLM_ROPE(N) launch_rope<TA, N>(qkv, row_stride, qw, kw, has_norm, eps, inv_freq, n_rot, token_pos, \
-                                       token_slot, block_table, table_stride, pool, nq, nkv, hd, writes_kv, T, st)
-    if (hd <= 32) ZLM_ROPE(1);
-    else if (hd <= 64) ZLM_ROPE(2);
-    else if (hd <= 128) ZLM_ROPE(4);
-    else if (hd <= 256) ZLM_ROPE(8);
-    else ZLM_ROPE(16);
+#define ZLM_ROPE(N, V) launch_rope<TA, N, V>(qkv, row_stride, qw, kw, has_norm, eps, inv_freq, n_rot, token_pos, \
+                                             token_slot, block_table, table_stride, pool, nq, nkv, hd, writes_kv, T, st)
+    if (zlm_rope_vector_form(hd, (int)sizeof(TA), row_stride, qkv, pool)) {
+        if (hd == 64) ZLM_ROPE(2, true);
+        else if (hd == 128) ZLM_ROPE(4, true);
+        else ZLM_ROPE(8, true);
+        return;
+    }
+    if (hd <= 32) ZLM_ROPE(1, false);
+    else if (hd <= 64) ZLM_ROPE(2, false);
+    else if (hd <= 128) ZLM_ROPE(4, false);
+    else if (hd <= 256) ZLM_ROPE(8, false);
+    else ZLM_ROPE(16, false);
 #undef ZLM_ROPE
 }
 

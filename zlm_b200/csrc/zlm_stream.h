@@ -9,7 +9,7 @@
 #define ZLM_STREAM_EMBED 1      // i: T H V                         p: out table ids
 #define ZLM_STREAM_RMSNORM 2    // i: R H w_dtype vthreads  f: eps  p: out x w rows
 #define ZLM_STREAM_GEMV 3       // i: T N K ldx ldy mode unit_rows  p: Y X W tensor_map(W)
-#define ZLM_STREAM_ROPE 4       // i: T row_stride has_norm n_rot table_stride nq nkv hd writes_kv w_dtype
+#define ZLM_STREAM_ROPE 4       // i: T row_stride has_norm n_rot table_stride nq nkv hd writes_kv w_dtype vector_form
                                 // f: eps    p: qkv q_w k_w inv_freq token_pos token_slot block_table pool
 #define ZLM_STREAM_ATTN 5       // i: T out_stride q_stride table_stride nq nkv hd window splits per
                                 // f: scale  p: out q pool block_table token_pos token_slot part_o part_ml

@@ -149,7 +149,9 @@ class StepRecorder:
         if write:
             assert pool.dtype == qkv.dtype and pool.is_contiguous() and tuple(pool.shape[1:]) == (2, nkv, PAGE_TOKENS, hd)
         self._add(ROPE, (T, qkv.stride(0), int(has_norm), n_rot, block_table.stride(0) if block_table is not None else 0,
-                         nq, nkv, hd, int(write), _vec_dtype(q_w) if has_norm else F32),
+                         nq, nkv, hd, int(write), _vec_dtype(q_w) if has_norm else F32,
+                         self.k.lib.zlm_rope_vector_form(hd, 2, qkv.stride(0), c_void_p(qkv.data_ptr()),
+                                                         c_void_p(pool.data_ptr() if write else 0))),
                   (eps,), (qkv, q_w, k_w, inv_freq, token_pos, token_slot, block_table if write else None,
                            pool if write else None))
 
