@@ -33,10 +33,11 @@ def expected_token(logits, temperature, top_k, top_p, u):
     return (pick if pick is not None else idx[order[-1]]), gap
 
 
+@pytest.mark.parametrize("form", ["cluster", "block"])
 @pytest.mark.parametrize("V", [50, 1543, 151936])
 @pytest.mark.parametrize("temperature,top_k,top_p", [(0.8, 0, 1.0), (1.0, 40, 1.0), (0.7, 0, 0.9), (1.3, 50, 0.5),
                                                      (0.5, 1, 1.0), (1.0, 0, 1e-6)])
-def test_draws_match_the_plain_sampler(K, V, temperature, top_k, top_p):
+def test_draws_match_the_plain_sampler(K, V, temperature, top_k, top_p, form):
     R = 6
     g = torch.Generator().manual_seed(V + top_k)
     logits = torch.randn((R, V), generator=g) * 3.0
@@ -45,7 +46,7 @@ def test_draws_match_the_plain_sampler(K, V, temperature, top_k, top_p):
     req = torch.tensor([0, 5, 2, 9, 1, 3], dtype=torch.int32)
     pos = torch.tensor([10, 11, 500, 3, 77, 4095], dtype=torch.int32)
     out = torch.empty(R, dtype=torch.int32, device="cuda")
-    K.sample(out, logits.cuda(), temperature, top_k, top_p, 1234, req.cuda(), pos.cuda())
+    K.sample(out, logits.cuda(), temperature, top_k, top_p, 1234, req.cuda(), pos.cuda(), form=form)
     got = out.cpu().tolist()
     for r in range(R):
         u = uniform_for(1234, int(req[r]), int(pos[r]))
@@ -53,6 +54,27 @@ def test_draws_match_the_plain_sampler(K, V, temperature, top_k, top_p):
         kept, _ = P.kept_set(logits[r], temperature, top_k, top_p)
         assert got[r] in kept, f"row {r}: token {got[r]} is outside the kept set of {len(kept)}"
         assert got[r] == want or gap < 1e-5, f"row {r}: got {got[r]}, want {want} (gap {gap:.2e})"
+
+
+def test_the_two_forms_draw_the_same_tokens(K):
+    """The cluster form (8 blocks per row) and the one-block form keep the same set and walk
+    it in the same order; their 64-bit sums are grouped differently, so a draw may differ
+    only where the uniform falls within rounding of a boundary."""
+    R, V = 64, 40000
+    g = torch.Generator().manual_seed(11)
+    logits = (torch.randn((R, V), generator=g) * 2.5).cuda()
+    logits[3] = torch.round(logits[3])
+    req = torch.arange(R, dtype=torch.int32).cuda()
+    pos = torch.arange(100, 100 + R, dtype=torch.int32).cuda()
+    for temperature, top_k, top_p in [(0.9, 0, 1.0), (1.1, 64, 0.9), (0.6, 0, 0.7)]:
+        a = torch.empty(R, dtype=torch.int32, device="cuda")
+        b = torch.empty_like(a)
+        K.sample(a, logits, temperature, top_k, top_p, 5, req, pos, form="cluster")
+        K.sample(b, logits, temperature, top_k, top_p, 5, req, pos, form="block")
+        assert int((a != b).sum()) <= 1, (a != b).nonzero().tolist()
+    with pytest.raises(Exception, match="too long for the cluster form"):
+        K.sample(torch.empty(1, dtype=torch.int32, device="cuda"), torch.zeros((1, 300000), device="cuda"), 1.0, 0, 1.0, 1,
+                 req[:1].contiguous(), pos[:1].contiguous(), form="cluster")
 
 
 def test_one_and_tiny_p_are_greedy_and_rows_do_not_see_each_other(K):

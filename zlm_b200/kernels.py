@@ -305,17 +305,19 @@ class CudaKernels:
         return int(self.lib.zlm_stream_status())
 
     def sample(self, out: torch.Tensor, logits: torch.Tensor, temperature: float, top_k: int, top_p: float,
-               seed: int, request: torch.Tensor, position: torch.Tensor) -> None:
+               seed: int, request: torch.Tensor, position: torch.Tensor, form: Optional[str] = None) -> None:
         """out[r] = a draw from softmax(logits[r] / temperature) restricted to the top_k
         best and to the nucleus of mass top_p; the uniform of row r is a hash of
-        (seed, request[r], position[r])."""
+        (seed, request[r], position[r]).  ``form`` forces one of the kernel's two forms
+        (tests): "cluster" (8 blocks per row, the row in distributed shared memory) or
+        "block" (one block per row; rows too long for the cluster form)."""
         R, V = logits.shape
         assert logits.dtype == torch.float32 and logits.stride(1) == 1 and out.dtype == torch.int32
         assert request.dtype == torch.int32 and position.dtype == torch.int32
         self._call("zlm_sample", c_void_p(out.data_ptr()), c_void_p(logits.data_ptr()), c_int(R), c_int(V),
                    c_int(logits.stride(0)), c_float(temperature), c_int(top_k), c_float(top_p),
                    ctypes.c_ulonglong(seed & 0xFFFFFFFFFFFFFFFF), c_void_p(request.data_ptr()),
-                   c_void_p(position.data_ptr()), self._stream())
+                   c_void_p(position.data_ptr()), c_int({None: 0, "block": 1, "cluster": 2}[form]), self._stream())
 
 
 _KERNELS: Optional[CudaKernels] = None
