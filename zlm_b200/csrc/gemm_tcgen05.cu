@@ -224,6 +224,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 // the product warp already fills the other, and the TMA ring never stops between
 // tiles.  acc_full[b] / acc_empty[b] hand accumulator b back and forth.
 // ---------------------------------------------------------------------------
+#define TCP_ACC 256          // tensor-memory columns between the two accumulators (an allocation is a power of two)
 template <int BN, int STAGES, int MODE>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
@@ -253,7 +254,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n"
-                     ::"r"(smem_u32(tmem_slot)), "r"((unsigned)(2 * BN)) : "memory");
+                     ::"r"(smem_u32(tmem_slot)), "r"((unsigned)(2 * TCP_ACC)) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
     }
     tc_fence_before();
@@ -303,7 +304,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
                     const uint64_t ad = make_desc(smem_u32(sA + s * A_BYTES)), bd = make_desc(smem_u32(sB + s * B_BYTES));
 #pragma unroll
                     for (int k = 0; k < TC_BK / 16; ++k)
-                        tc_mma(tmem_base + buf * BN, ad + ((k * 32) >> 4), bd + ((k * 32) >> 4), idesc, (kb | k) != 0);
+                        tc_mma(tmem_base + buf * TCP_ACC, ad + ((k * 32) >> 4), bd + ((k * 32) >> 4), idesc, (kb | k) != 0);
                     tc_commit(&empty[s]);
                 }
                 tc_commit(&acc_full[buf]);
@@ -323,7 +324,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
 #pragma unroll 1
             for (int c = 0; c < BN; c += 16) {
                 float v[16];
-                tc_ld16(tmem_base + ((unsigned)(lg * 32) << 16) + buf * BN + (unsigned)c, v);
+                tc_ld16(tmem_base + ((unsigned)(lg * 32) << 16) + buf * TCP_ACC + (unsigned)c, v);
                 store_row16<MODE>(v, Y, arow, b0row + c, T, N, ldy);
             }
             tc_fence_before();
@@ -336,7 +337,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
     if (warp == 1) {
         __syncwarp();
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"((unsigned)(2 * BN)) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"((unsigned)(2 * TCP_ACC)) : "memory");
     }
 }
 
@@ -545,6 +546,21 @@ extern "C" int zlm_gemm_tc(void* Y, const void* X, const void* W, int T, int N, 
     if (T <= 32) return launch_tc<32, 8, true>(Y, X, W, T, N, K, ldx, ldy, mode, ks, scratch, st);
     if (T <= 64) return launch_tc<64, 8, true>(Y, X, W, T, N, K, ldx, ldy, mode, ks, scratch, st);
     if (T <= 384) return launch_tc<128, 6, true>(Y, X, W, T, N, K, ldx, ldy, mode, ks, scratch, st);
+    // The tile's width: tiles run in rounds of one per SM, and a round costs its width.  N = 4096 at
+    // 2,048 tokens is 256 tiles of 256 columns (2 rounds, the second 73 % full) or 288 of 240 (2 rounds,
+    // 97 % full).  A narrower tile re-reads the activations more often, so it has to win by more than
+    // 5 % in rounds x width (measured at 2,048 tokens: N = 4096 and 6144 gain 2-3 % with 240 columns,
+    // N = 24576 loses 3 % with 224 although it saves a round of 12).
+    const long long m_tiles = (T + TC_BM - 1) / TC_BM;
+    auto cost_of = [&](int bn) { return ((m_tiles * ((N + bn - 1) / bn) + sm_count() - 1) / sm_count()) * bn; };
+    int best = 256;
+    long long best_cost = cost_of(256);
+    for (int bn : {240, 224}) {
+        const long long cost = cost_of(bn);
+        if (cost * 100 < best_cost * 95 && cost < (best == 256 ? best_cost : cost_of(best))) best = bn;
+    }
+    if (best == 240) return launch_tc_persistent<240, 4>(Y, X, W, T, N, K, ldx, ldy, mode, st);
+    if (best == 224) return launch_tc_persistent<224, 4>(Y, X, W, T, N, K, ldx, ldy, mode, st);
     return launch_tc_persistent<256, 4>(Y, X, W, T, N, K, ldx, ldy, mode, st);
 }
 
