@@ -194,14 +194,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                         }
                     } else {
                         if (arow >= N) continue;
+                        if (MODE == 1) {
+                            // all sixteen old values first: one latency, not sixteen (the compiler may not
+                            // move a load above a store that could be to the same place)
+                            float old[16];
 #pragma unroll
-                        for (int i = 0; i < 16; ++i) {
-                            if (t0 + i >= T) break;
-                            const size_t off = (size_t)(t0 + i) * ldy + arow;
-                            if (MODE == 0) ((__nv_bfloat16*)Y)[off] = __float2bfloat16_rn(v[i]);
-                            else if (MODE == 1) ((float*)Y)[off] += v[i];
-                            else if (MODE == 2) ((float*)Y)[off] = v[i];
-                            else ((float*)Y)[((size_t)blockIdx.z * T + t0 + i) * N + arow] = v[i];
+                            for (int i = 0; i < 16; ++i)
+                                old[i] = t0 + i < T ? __ldcg((const float*)Y + (size_t)(t0 + i) * ldy + arow) : 0.f;
+#pragma unroll
+                            for (int i = 0; i < 16; ++i)
+                                if (t0 + i < T) ((float*)Y)[(size_t)(t0 + i) * ldy + arow] = old[i] + v[i];
+                        } else {
+#pragma unroll
+                            for (int i = 0; i < 16; ++i) {
+                                if (t0 + i >= T) break;
+                                const size_t off = (size_t)(t0 + i) * ldy + arow;
+                                if (MODE == 0) ((__nv_bfloat16*)Y)[off] = __float2bfloat16_rn(v[i]);
+                                else if (MODE == 2) ((float*)Y)[off] = v[i];
+                                else ((float*)Y)[((size_t)blockIdx.z * T + t0 + i) * N + arow] = v[i];
+                            }
                         }
                     }
                 }
