@@ -268,7 +268,7 @@ def profile(args) -> int:
     ps = [torch.randint(0, cfg.vocab_size, (L,), generator=g).tolist() for _ in range(B)]
     slots = [eng.new_sequence() for _ in ps]
     rt = torch.cuda.cudart()
-    greedy = SamplingParams()
+    greedy = SamplingParams(0.8, 40, 0.9, 1) if args.sample else SamplingParams()
     if args.profile == "prefill":
         eng.step([StepEntry(slots[0], ps[0], [L - 1])])          # warm
         eng.release(slots[0])
@@ -307,6 +307,8 @@ def main() -> int:
     ap.add_argument("--profile", choices=["decode", "prefill"], help="run a small case for ncu and exit")
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN)
     ap.add_argument("--pdl", action="store_true", help="decode kernels with programmatic dependent launch")
+    ap.add_argument("--sample", action="store_true",
+                    help="with --profile decode: temperature 0.8, top-k 40, top-p 0.9 instead of greedy")
     ap.add_argument("--decode", choices=["graph", "stream"], default="graph",
                     help="graph: a CUDA graph of one kernel per operation; stream: the persistent decode kernel where it applies")
     args = ap.parse_args()
