@@ -68,6 +68,39 @@ def test_stop_tokens_end_a_row_early(tmp_path):
     assert eng.cache.slots.held == 0
 
 
+def test_queued_steps_generate_what_single_steps_generate(tmp_path):
+    """The loop that queues decode steps one ahead against the loop that waits for every step,
+    on the same engine: rows that meet a stop token at different steps, rows that reach their
+    length, sampled and greedy.  In 32-bit a row's logits do not depend on the batch, so the
+    tokens must be the same."""
+    from zlm_b200 import Engine
+    from zlm_b200.engine.generate import generate
+    from zlm_b200.sampling import SamplingParams
+
+    class OneAtATime:
+        """The engine without its queued steps."""
+        def __init__(self, eng):
+            self._e = eng
+
+        def __getattr__(self, name):
+            if name in ("decode_launch", "decode_fetch"):
+                raise AttributeError(name)
+            return getattr(self._e, name)
+
+    folder, cfg, _ = make_model(tmp_path, "C", seed=15)
+    prompts = random_prompts(cfg.vocab_size, [4, 33, 9, 64, 2, 17], seed=8)
+    eng = Engine.from_pretrained(folder, dtype="float32", max_tokens=2048, max_batch=4)
+    for params in (SamplingParams(), SamplingParams(0.9, 20, 0.95, 3)):
+        free = generate(OneAtATime(eng), prompts, 14, params, stop_token_ids=()).tokens
+        stops = [free[0][2], free[3][9], free[5][0]]
+        want = generate(OneAtATime(eng), prompts, 14, params, stop_token_ids=stops)
+        got = generate(eng, prompts, 14, params, stop_token_ids=stops)
+        assert got.tokens == want.tokens and got.finish_reasons == want.finish_reasons
+        assert "stop" in got.finish_reasons and "length" in got.finish_reasons
+        assert eng.cache.slots.held == 0
+    eng.cache.check()
+
+
 def test_temperature_sampling_is_reproducible_and_batch_independent(tmp_path):
     from zlm_b200 import Engine
     folder, cfg, _ = make_model(tmp_path, "B", seed=13)
