@@ -101,6 +101,39 @@ def test_queued_steps_generate_what_single_steps_generate(tmp_path):
     eng.cache.check()
 
 
+def test_an_engine_dropped_earlier_does_not_disturb_a_later_capture(tmp_path):
+    """An engine that is no longer referenced is freed by Python's cycle collector at a moment
+    of its choosing; when that moment fell inside another engine's graph capture, the capture
+    was lost.  Here the dropped engine is kept from being collected until the second engine
+    captures, and a collection is forced in the middle of that capture: it must find nothing
+    left to free."""
+    import gc
+    from zlm_b200 import Engine
+    folder, cfg, _ = make_model(tmp_path, "B", seed=4)
+    prompts = random_prompts(cfg.vocab_size, [6, 3], seed=2)
+    first = Engine.from_pretrained(folder, dtype="bfloat16", max_tokens=256, max_batch=2)
+    want = first.generate(prompts, max_tokens=6)
+    assert first.decoder.graphs
+    gc.collect()
+    gc.disable()
+    try:
+        del first
+        second = Engine.from_pretrained(folder, dtype="bfloat16", max_tokens=256, max_batch=2)
+        argmax = second.rt.k.argmax
+        seen = []
+
+        def collecting_argmax(*a, **kw):
+            if torch.cuda.is_current_stream_capturing():
+                seen.append(gc.collect())
+            return argmax(*a, **kw)
+
+        second.rt.k.argmax = collecting_argmax
+        got = second.generate(prompts, max_tokens=6)
+    finally:
+        gc.enable()
+    assert seen and got.tokens == want.tokens
+
+
 def test_temperature_sampling_is_reproducible_and_batch_independent(tmp_path):
     from zlm_b200 import Engine
     folder, cfg, _ = make_model(tmp_path, "B", seed=13)

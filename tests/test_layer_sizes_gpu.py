@@ -1,7 +1,10 @@
 """The engine at the layer sizes of Qwen3-8B (width 4096, 32 query heads over 8 kv
-heads of size 128, feed-forward 12288; two layers and a reduced vocabulary so that
-the plain implementation finishes in seconds): every kernel at the shapes the
-benchmark runs, in 32-bit and in bfloat16, whole prompt, chunks and decode."""
+heads of size 128, feed-forward 12288), of Qwen3-0.6B (width 1024, 16 over 8 heads of
+128, so that heads x size is not the width; feed-forward 3072, tied head) and of
+Qwen3-32B (width 5120, 64 over 8 heads: groups of 8; feed-forward 25600), one or two
+layers each and a reduced vocabulary so that the plain implementation finishes in seconds:
+every kernel at the shapes the benchmark runs, in 32-bit and in bfloat16, whole prompt,
+chunks and decode."""
 import pytest
 import torch
 
@@ -25,12 +28,21 @@ SIZES_8B = {
 }
 
 
-@pytest.fixture(scope="module")
-def model():
+SIZES = {
+    "8B": SIZES_8B,
+    "0.6B": dict(SIZES_8B, hidden_size=1024, num_attention_heads=16, num_key_value_heads=8, intermediate_size=3072,
+                 tie_word_embeddings=True, vocab_size=8200),
+    "32B": dict(SIZES_8B, hidden_size=5120, num_attention_heads=64, num_key_value_heads=8, intermediate_size=25600,
+                vocab_size=4104, num_hidden_layers=1),
+}
+
+
+@pytest.fixture(scope="module", params=["8B", "0.6B", "32B"])
+def model(request):
     from zlm_b200.parts.model import DecoderModel
     from zlm_b200.registry import config_from_dict
     from zlm_b200.weights import random_tensors
-    cfg = config_from_dict(SIZES_8B)
+    cfg = config_from_dict(SIZES[request.param])
     tensors = random_tensors(DecoderModel(cfg.to_model_spec()).param_specs(), 5, "cpu", torch.float32)
     (prompt,) = random_prompts(cfg.vocab_size, [300], seed=9)
     want = {dt: plain_logits(reference_tensors(tensors, dt), cfg, prompt) for dt in ("float32", "bfloat16")}
@@ -53,16 +65,16 @@ def test_layer_sizes_of_the_benchmark(model, dtype):
     # whole (tcgen05 products and tiled attention in bfloat16)
     s = eng.new_sequence()
     got = eng.step([StepEntry(s, prompt, list(range(300)))]).clone()
-    assert_close(got, ref, dtype, f"8B sizes whole {dtype}", TOL_8B[dtype])
+    assert_close(got, ref, dtype, f"layer sizes whole {dtype}", TOL_8B[dtype])
     eng.release(s)
     # a long chunk, a short chunk (the few-token kernels), then single tokens through the decode path
     s = eng.new_sequence()
     parts = [eng.step([StepEntry(s, prompt[:200], list(range(200)))]).clone(),
              eng.step([StepEntry(s, prompt[200:240], list(range(40)))]).clone(),
              eng.step([StepEntry(s, prompt[240:250], list(range(10)))]).clone()]
-    assert_close(torch.cat(parts), ref[:250], dtype, f"8B sizes chunks {dtype}", TOL_8B[dtype])
+    assert_close(torch.cat(parts), ref[:250], dtype, f"layer sizes chunks {dtype}", TOL_8B[dtype])
     for t in range(250, 262):
         eng.decoder.step([s], [prompt[t]], SamplingParams())
-        assert_close(eng.decoder.last_logits.clone(), ref[t:t + 1], dtype, f"8B sizes decode {t} {dtype}", TOL_8B[dtype])
+        assert_close(eng.decoder.last_logits.clone(), ref[t:t + 1], dtype, f"layer sizes decode {t} {dtype}", TOL_8B[dtype])
     if dtype == "bfloat16":
         assert eng.rt.k.gemm_tc_status() == 0

@@ -22,6 +22,7 @@ a run of steps needs no host round trip unless the caller wants the tokens.
 """
 from __future__ import annotations
 
+import gc
 from typing import Dict, List, Optional, Sequence, Tuple
 
 import numpy as np
@@ -230,8 +231,19 @@ class DecodeRunner:
             g = torch.cuda.CUDAGraph()
             counter = getattr(e.rt.k, "launches", None)
             before = counter() if counter else 0
-            with torch.cuda.graph(g):
-                self._device_work(ctx, R, params)
+            # Python's cycle collector must not run inside the capture: what it frees there (an
+            # engine that was dropped earlier, with its graphs and their memory pools) makes
+            # CUDA calls that are not allowed while a stream captures, and the capture is lost.
+            # So garbage is collected now, and the collector rests until the capture has ended.
+            gc.collect()
+            collecting = gc.isenabled()
+            gc.disable()
+            try:
+                with torch.cuda.graph(g):
+                    self._device_work(ctx, R, params)
+            finally:
+                if collecting:
+                    gc.enable()
             if counter:
                 self.launches_per_step = counter() - before
             if gen != self._generation():
