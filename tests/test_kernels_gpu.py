@@ -318,6 +318,37 @@ def test_linear_bf16_tcgen05(K, T, N, K_):
     assert K.gemm_tc_status() == 0
 
 
+@pytest.mark.parametrize("form,width", [("single", 256), ("single", 240), ("single", 224), ("pair", 256),
+                                        ("pair", 240), ("pair", 224), (None, 0)])
+@pytest.mark.parametrize("T,N,K_", [(385, 300, 72), (700, 2064, 264), (1000, 1000, 520)])
+def test_linear_bf16_tcgen05_many_tokens(K, T, N, K_, form, width):
+    """The persistent many-token product in both forms (one block per tile; a pair of
+    blocks per tile, cta_group::2) at every tile width, several tiles per block, ragged
+    in T, N and K, all output modes and the fused gate/up epilogue."""
+    from zlm_b200.kernels import interleave_gate_up
+    x, w = rnd((T, K_), torch.bfloat16, 75), rnd((N, K_), torch.bfloat16, 76, 0.05)
+    want = x.double() @ w.double().t()
+    K.set_gemm_form(form, width)
+    try:
+        for out_dtype in (torch.bfloat16, torch.float32):
+            got = torch.full((T, N), 7.0, dtype=out_dtype, device="cuda")
+            K.linear(got, x.cuda(), w.cuda(), impl="tc")
+            close(got, want, out_dtype, atol=1e-3 if out_dtype == torch.float32 else 3e-2, rtol=1e-2)
+        base = rnd((T, N), torch.float32, 77)
+        acc = base.clone().cuda()
+        K.linear(acc, x.cuda(), w.cuda(), accumulate=True, impl="tc")
+        close(acc, base.double() + want, torch.float32, atol=1e-3, rtol=1e-3)
+        if N % 16 == 0:
+            gate, up = w[:N // 2], w[N // 2:]
+            g, u = x.double() @ gate.double().t(), x.double() @ up.double().t()
+            got = torch.full((T, N // 2), 7.0, dtype=torch.bfloat16, device="cuda")
+            K.linear_swiglu(got, x.cuda(), interleave_gate_up(gate.cuda(), up.cuda()), impl="tc")
+            close(got, (g / (1 + torch.exp(-g))) * u, torch.bfloat16, atol=3e-2, rtol=3e-2)
+    finally:
+        K.set_gemm_form(None, 0)
+    assert K.gemm_tc_status() == 0
+
+
 def test_linear_bf16_kernels_agree(K):
     """The three bf16 products give the same numbers up to the order of their sums."""
     x, w = rnd((16, 512), torch.bfloat16, 73), rnd((384, 512), torch.bfloat16, 74, 0.05)

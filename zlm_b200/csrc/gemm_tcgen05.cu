@@ -352,6 +352,141 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
     }
 }
 
+// ---------------------------------------------------------------------------
+// The persistent kernel on pairs of blocks (tcgen05 with cta_group::2): a cluster of two
+// blocks, on neighbouring SMs, walks tiles of 256 tokens x BN outputs.  Each block loads its
+// 128 tokens and its half of the BN rows of W; rank 0 issues 256 x BN x 16 products that read
+// both blocks' shared memory and accumulate into both blocks' tensor memory (each holds the
+// 128 rows of its own tokens).  Per product a block reads 128 x 16 of W instead of 256 x 16:
+// the single-block kernel's shared-memory pipe (operand reads plus TMA writes at the pipe's
+// 128 bytes a cycle) is what this relieves.  Barriers: full[s] lives in rank 0 and counts
+// the bytes of both blocks' loads; empty[s], acc_full[b] exist in both blocks and are
+// signalled by multicast commits; acc_empty[b] lives in rank 0 and is arrived at by the
+// epilogue warps of both blocks.
+// ---------------------------------------------------------------------------
+#define TCQ_BM 256
+template <int BN, int STAGES, int MODE>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                    void* __restrict__ Y, int T, int N, int K, int ldy) {
+    constexpr unsigned A_BYTES = TC_BM * TC_BK * 2, B_BYTES = (BN / 2) * TC_BK * 2;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    unsigned char* sA = smem;
+    unsigned char* sB = smem + STAGES * A_BYTES;
+    uint64_t* full = (uint64_t*)(sB + STAGES * B_BYTES);
+    uint64_t* empty = full + STAGES;
+    uint64_t* acc_full = empty + STAGES;       // [2]
+    uint64_t* acc_empty = acc_full + 2;        // [2]
+    unsigned* tmem_slot = (unsigned*)(acc_empty + 2);
+    volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const unsigned rank = cluster_rank();
+    const int pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+    const int KB = (K + TC_BK - 1) / TC_BK;
+    const int m_tiles = (T + TCQ_BM - 1) / TCQ_BM, n_tiles = (N + BN - 1) / BN;
+    const int tiles = m_tiles * n_tiles;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 8); }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;\n"
+                     ::"r"(smem_u32(tmem_slot)), "r"((unsigned)(2 * TCP_ACC)) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;\n" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();          // the other block's barriers are initialised before anything arrives there
+    tc_fence_after();
+    const unsigned tmem_base = *tmem_slot;
+    pdl_launch_dependents();
+    pdl_wait();
+
+    if (warp == 0) {
+        if (lane == 0) {
+            unsigned it = 0;
+            bool ok = true;
+            for (int tile = pair; tile < tiles && ok; tile += pairs) {
+                const int a0row = (tile % m_tiles) * TCQ_BM + rank * TC_BM;
+                const int b0row = (tile / m_tiles) * BN + rank * (BN / 2);
+                for (int kb = 0; kb < KB; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    if (!mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1, abort_flag, 1)) { ok = false; break; }
+                    if (rank == 0) mbar_expect_tx(&full[s], 2 * (A_BYTES + B_BYTES));
+                    const unsigned bar0 = cluster_addr(&full[s], 0);
+                    tma_load_2d_pair(sA + s * A_BYTES, &map_a, kb * TC_BK, a0row, bar0);
+                    tma_load_2d_pair(sB + s * B_BYTES, &map_b, kb * TC_BK, b0row, bar0);
+                }
+            }
+            if (*abort_flag && rank == 0) {
+                for (unsigned j = it > (unsigned)STAGES ? it - STAGES : 0; j < it; ++j)
+                    mbar_drain(&full[j % STAGES], (j / STAGES) & 1);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && rank == 0) {
+            // fp32 accumulate, bf16 x bf16, both K-major, N = BN, M = 256 over the two blocks
+            const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(BN >> 3) << 17) |
+                                   ((unsigned)(TCQ_BM >> 4) << 24);
+            unsigned it = 0, local = 0;
+            bool ok = true;
+            for (int tile = pair; tile < tiles && ok; tile += pairs, ++local) {
+                const unsigned buf = local & 1;
+                ok = mbar_wait_pair(&acc_empty[buf], ((local >> 1) & 1) ^ 1, abort_flag, 4);
+                if (!ok) break;
+                tc_fence_after();
+                for (int kb = 0; kb < KB; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    ok = mbar_wait(&full[s], (it / STAGES) & 1, abort_flag, 2);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint64_t ad = make_desc(smem_u32(sA + s * A_BYTES)), bd = make_desc(smem_u32(sB + s * B_BYTES));
+#pragma unroll
+                    for (int k = 0; k < TC_BK / 16; ++k)
+                        tc_mma_pair(tmem_base + buf * TCP_ACC, ad + ((k * 32) >> 4), bd + ((k * 32) >> 4), idesc, (kb | k) != 0);
+                    tc_commit_pair(&empty[s]);
+                }
+                tc_commit_pair(&acc_full[buf]);
+            }
+            if (!ok) { tc_commit_pair(&acc_full[0]); tc_commit_pair(&acc_full[1]); }     // let the epilogues out
+        }
+    } else {
+        const int lg = warp & 3;
+        unsigned local = 0;
+        const unsigned empty0[2] = {cluster_addr(&acc_empty[0], 0), cluster_addr(&acc_empty[1], 0)};
+        for (int tile = pair; tile < tiles; tile += pairs, ++local) {
+            const unsigned buf = local & 1;
+            const int a0row = (tile % m_tiles) * TCQ_BM + rank * TC_BM, b0row = (tile / m_tiles) * BN;
+            const bool ok = mbar_wait(&acc_full[buf], (local >> 1) & 1, abort_flag, 3);
+            tc_fence_after();
+            if (!ok || *abort_flag) break;
+            const int arow = a0row + lg * 32 + lane;
+#pragma unroll 1
+            for (int c = 0; c < BN; c += 16) {
+                float v[16];
+                tc_ld16(tmem_base + ((unsigned)(lg * 32) << 16) + buf * TCP_ACC + (unsigned)c, v);
+                store_row16<MODE>(v, Y, arow, b0row + c, T, N, ldy);
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_at(empty0[buf]);
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();          // neither block leaves while the other may still read its memory or signal it
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"((unsigned)(2 * TCP_ACC)) : "memory");
+    }
+}
+
 // adds the K shares up in the order 0 .. splits-1 and finishes the product in the wanted mode
 template <int MODE>
 __global__ void gemm_tc_reduce_kernel(void* __restrict__ Y, const float* __restrict__ part, int T, int N, int ldy,
@@ -512,6 +647,51 @@ static int launch_tc_persistent(void* Y, const void* X, const void* W, int T, in
     return zlm_check_launch("gemm_tc_persistent");
 }
 
+template <int BN, int STAGES>
+static int launch_tc_pair(void* Y, const void* X, const void* W, int T, int N, int K, int ldx, int ldy, int mode,
+                          cudaStream_t st) {
+    CUtensorMap mx, mw;
+    int rc = make_map(&mx, X, T, K, ldx, TC_BM);
+    if (rc) return rc;
+    rc = make_map(&mw, W, N, K, K, BN / 2);
+    if (rc) return rc;
+    const size_t smem = (size_t)STAGES * (TC_BM + BN / 2) * TC_BK * 2 + 1024 + 256;
+    const long long tiles = (long long)((T + TCQ_BM - 1) / TCQ_BM) * ((N + BN - 1) / BN);
+    const int pairs = (int)(tiles < sm_count() / 2 ? tiles : sm_count() / 2);
+#define ZLM_TCQ_LAUNCH(M)                                                                                  \
+    {                                                                                                      \
+        auto kern = gemm_tc_pair_kernel<BN, STAGES, M>;                                                    \
+        static bool attr_set = false;                                                                      \
+        if (!attr_set) {                                                                                   \
+            cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            if (e != cudaSuccess) {                                                                        \
+                zlm_set_error("gemm_tc: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e)); \
+                return ZLM_ERR_CUDA;                                                                       \
+            }                                                                                              \
+            attr_set = true;                                                                               \
+        }                                                                                                  \
+        zlm_launch(kern, dim3(2 * pairs), dim3(TC_THREADS), smem, st, mx, mw, Y, T, N, K, ldy);            \
+    }
+    if (mode == 0) ZLM_TCQ_LAUNCH(0)
+    else if (mode == 1) ZLM_TCQ_LAUNCH(1)
+    else if (mode == 2) ZLM_TCQ_LAUNCH(2)
+    else ZLM_TCQ_LAUNCH(3)
+#undef ZLM_TCQ_LAUNCH
+    return zlm_check_launch("gemm_tc_pair");
+}
+
+// Which many-token form runs, and how wide its tiles are: 0 lets the dispatcher choose (pairs of
+// blocks; the width by the rule in zlm_gemm_tc).  form 1: single blocks, 2: pairs; width 256, 240
+// or 224.  For tests and measurements.
+static int g_tc_form = 0, g_tc_width = 0;
+extern "C" int zlm_gemm_tc_set_form(int form, int width) {
+    ZLM_REQUIRE(form >= 0 && form <= 2, "gemm_tc: form %d", form);
+    ZLM_REQUIRE(width == 0 || width == 256 || width == 240 || width == 224, "gemm_tc: tile width %d", width);
+    g_tc_form = form;
+    g_tc_width = width;
+    return ZLM_OK;
+}
+
 // 1 if the tensor-memory kernel takes this product (else use zlm_gemm_bf16_mma)
 extern "C" int zlm_gemm_tc_supported(int T, int N, int K, int ldx) {
     return (T >= 1 && N >= 8 && K >= 8 && K % 8 == 0 && ldx % 8 == 0) ? 1 : 0;
@@ -562,6 +742,17 @@ extern "C" int zlm_gemm_tc(void* Y, const void* X, const void* W, int T, int N, 
     // 97 % full).  A narrower tile re-reads the activations more often, so it has to win by more than
     // 5 % in rounds x width (measured at 2,048 tokens: N = 4096 and 6144 gain 2-3 % with 240 columns,
     // N = 24576 loses 3 % with 224 although it saves a round of 12).
+    if (g_tc_form != 1) {
+        const long long m2 = (T + TCQ_BM - 1) / TCQ_BM, pairs = sm_count() / 2;
+        auto cost2 = [&](int bn) { return ((m2 * ((N + bn - 1) / bn) + pairs - 1) / pairs) * bn; };
+        int best = 256;
+        for (int bn : {240, 224})
+            if (cost2(bn) * 100 < cost2(256) * 95 && cost2(bn) < cost2(best)) best = bn;
+        if (g_tc_width) best = g_tc_width;
+        if (best == 240) return launch_tc_pair<240, 6>(Y, X, W, T, N, K, ldx, ldy, mode, st);
+        if (best == 224) return launch_tc_pair<224, 6>(Y, X, W, T, N, K, ldx, ldy, mode, st);
+        return launch_tc_pair<256, 6>(Y, X, W, T, N, K, ldx, ldy, mode, st);
+    }
     const long long m_tiles = (T + TC_BM - 1) / TC_BM;
     auto cost_of = [&](int bn) { return ((m_tiles * ((N + bn - 1) / bn) + sm_count() - 1) / sm_count()) * bn; };
     int best = 256;
@@ -570,6 +761,7 @@ extern "C" int zlm_gemm_tc(void* Y, const void* X, const void* W, int T, int N, 
         const long long cost = cost_of(bn);
         if (cost * 100 < best_cost * 95 && cost < (best == 256 ? best_cost : cost_of(best))) best = bn;
     }
+    if (g_tc_width) best = g_tc_width;
     if (best == 240) return launch_tc_persistent<240, 4>(Y, X, W, T, N, K, ldx, ldy, mode, st);
     if (best == 224) return launch_tc_persistent<224, 4>(Y, X, W, T, N, K, ldx, ldy, mode, st);
     return launch_tc_persistent<256, 4>(Y, X, W, T, N, K, ldx, ldy, mode, st);

@@ -131,6 +131,65 @@ __device__ __forceinline__ uint64_t make_desc_ex(unsigned smem_addr, unsigned lb
     return d;
 }
 
+// ---------------------------------------------------------------- a pair of blocks on one tile
+// Two blocks of a cluster (ranks 0 and 1) work on one tile: each loads its half of both operands,
+// rank 0 issues products that read both halves and write both blocks' tensor memory.
+__device__ __forceinline__ unsigned cluster_rank() {
+    unsigned r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;\n" : "=r"(r));
+    return r;
+}
+// every thread of both blocks
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+// the address, in the cluster's window, of block `rank`'s copy of a shared-memory object
+__device__ __forceinline__ unsigned cluster_addr(const void* p, unsigned rank) {
+    unsigned r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(r) : "r"(smem_u32(p)), "r"(rank));
+    return r;
+}
+// tile load into this block's shared memory whose bytes count at rank 0's mbarrier
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, int x, int y, unsigned bar_rank0) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n"
+        ::"r"(smem_u32(dst)), "l"(map), "r"(x), "r"(y), "r"(bar_rank0) : "memory");
+}
+__device__ __forceinline__ void tc_mma_pair(unsigned tmem_d, uint64_t desc_a, uint64_t desc_b, unsigned idesc, unsigned accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+// arrives, once the products issued so far have retired, at the mbarrier at this place in both blocks
+__device__ __forceinline__ void tc_commit_pair(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;\n"
+                 ::"r"(smem_u32(bar)), "h"((unsigned short)3) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_at(unsigned cluster_address) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];\n" ::"r"(cluster_address) : "memory");
+}
+// bounded wait on a barrier at which the other block of the pair arrives too
+__device__ __forceinline__ bool mbar_try_pair(uint64_t* bar, unsigned parity) {
+    unsigned ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}\n"
+        : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbar_wait_pair(uint64_t* bar, unsigned parity, volatile int* abort_flag, int where) {
+    if (mbar_try_pair(bar, parity)) return true;
+    const unsigned long long t0 = tc_now_ns();
+    for (unsigned it = 1;; ++it) {
+        if (mbar_try_pair(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if ((it & 63) == 0 && tc_now_ns() - t0 > TC_WAIT_NS) break;
+    }
+    *abort_flag = where;
+    atomicCAS(&g_tc_error, 0, where);
+    return false;
+}
+
 typedef CUresult (*ZlmEncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                      const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                      CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);

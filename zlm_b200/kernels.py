@@ -187,6 +187,14 @@ class CudaKernels:
         self._call(name, c_void_p(out.data_ptr()), c_void_p(x.data_ptr()), c_void_p(w.data_ptr()),
                    c_int(T), c_int(N), c_int(K), c_int(ldx), c_int(ldy), c_int(mode), self._stream())
 
+    def set_gemm_form(self, form: Optional[str] = None, width: int = 0) -> None:
+        """Forces the many-token tcgen05 product's form ("single": one block per tile,
+        "pair": two blocks per tile with cta_group::2) and tile width (256, 240, 224);
+        None / 0 give the choice back to the dispatcher.  For tests and measurements."""
+        code = {None: 0, "single": 1, "pair": 2}[form]
+        if self.lib.zlm_gemm_tc_set_form(c_int(code), c_int(width)) != 0:
+            raise KernelError(self.lib.zlm_last_error().decode())
+
     def linear_swiglu(self, out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, impl: Optional[str] = None) -> None:
         """out[t, c] = silu(x[t] . gate_c) * (x[t] . up_c) in one pass over w (bf16).  w is
         [2I, K] with the rows in groups of 16: 8 gate channels, then the 8 matching up
