@@ -349,6 +349,35 @@ def test_linear_bf16_tcgen05_many_tokens(K, T, N, K_, form, width):
     assert K.gemm_tc_status() == 0
 
 
+@pytest.mark.parametrize("T,N,K_", [(40, 19040, 1032), (300, 8000, 1024), (17, 24576, 520), (100, 37904, 264)])
+def test_linear_bf16_tcgen05_few_tokens_many_tiles(K, T, N, K_):
+    """The few-token product with more tiles than SMs: the persistent form, whose blocks walk
+    several tiles, computes as many full rounds of tiles in one piece and cuts the rest along K
+    (shares added up by the second kernel, from some output on); one or several token tiles;
+    all output modes and the fused gate/up epilogue; the same bits on a second run."""
+    from zlm_b200.kernels import interleave_gate_up
+    x, w = rnd((T, K_), torch.bfloat16, 86), rnd((N, K_), torch.bfloat16, 87, 0.05)
+    want = x.double() @ w.double().t()
+    outs = []
+    for rep in range(2):
+        for out_dtype in (torch.bfloat16, torch.float32):
+            got = torch.full((T, N), 7.0, dtype=out_dtype, device="cuda")
+            K.linear(got, x.cuda(), w.cuda(), impl="tc")
+            close(got, want, out_dtype, atol=1e-3 if out_dtype == torch.float32 else 3e-2, rtol=1e-2)
+            outs.append(got)
+    assert torch.equal(outs[0], outs[2]) and torch.equal(outs[1], outs[3])
+    base = rnd((T, N), torch.float32, 88)
+    acc = base.clone().cuda()
+    K.linear(acc, x.cuda(), w.cuda(), accumulate=True, impl="tc")
+    close(acc, base.double() + want, torch.float32, atol=1e-3, rtol=1e-3)
+    gate, up = w[:N // 2], w[N // 2:]
+    g, u = x.double() @ gate.double().t(), x.double() @ up.double().t()
+    got = torch.full((T, N // 2), 7.0, dtype=torch.bfloat16, device="cuda")
+    K.linear_swiglu(got, x.cuda(), interleave_gate_up(gate.cuda(), up.cuda()), impl="tc")
+    close(got, (g / (1 + torch.exp(-g))) * u, torch.bfloat16, atol=3e-2, rtol=3e-2)
+    assert K.gemm_tc_status() == 0
+
+
 def test_linear_bf16_kernels_agree(K):
     """The three bf16 products give the same numbers up to the order of their sums."""
     x, w = rnd((16, 512), torch.bfloat16, 73), rnd((384, 512), torch.bfloat16, 74, 0.05)

@@ -4,15 +4,21 @@
 // tcgen05.mma (128 x 256 x 16 per instruction), fp32 accumulators in tensor
 // memory, read back with tcgen05.ld for the epilogue.
 //
-// One block computes one tile of Y.  For many tokens the 128 rows of the product's
-// first operand are tokens and its up to 256 columns are outputs; for few tokens
-// (decode batches of 17 to a few hundred) the operands swap places: 128 rows of W
-// against a tile of 32, 64 or 128 tokens, so that W, which is what the step has to
-// read, still streams through full-height products.  Warp 0 is the TMA producer,
-// warp 1 allocates tensor memory and issues the products, warps 2..5 are the
-// epilogue.  A ring of (first-operand tile 128x64, second-operand tile BNx64) is
-// handed back and forth with mbarriers: `full` is completed by the TMA's byte
-// count, `empty` by tcgen05.commit when the products that read a stage have retired.
+// Three forms, by the number of tokens T:
+//  * many tokens (from 385): persistent, a cluster of two blocks per 256-token x BN-output
+//    tile (tcgen05 with cta_group::2, gemm_tc_pair_kernel); the single-block persistent kernel
+//    with 128 x BN tiles stays selectable (gemm_tc_persistent_kernel);
+//  * few tokens (17 to 384): the operands swap places, 128 rows of W against a tile of 32, 64
+//    or 128 tokens, so that W, which is what the step has to read, still streams through
+//    full-height products; one block per tile and share of K where that is one round of the
+//    GPU (gemm_tc_kernel), else persistent blocks (gemm_tc_few_kernel); K is cut into shares
+//    where the tiles alone would not fill the SMs, and a second kernel adds the shares in a
+//    fixed order.
+// In all of them warp 0 is the TMA producer, warp 1 allocates tensor memory and issues the
+// products, warps 2..5 are the epilogue.  A ring of (first-operand tile 128x64,
+// second-operand tile x64) is handed back and forth with mbarriers: `full` is completed by
+// the TMA's byte count, `empty` by tcgen05.commit when the products that read a stage have
+// retired.
 //
 // Every wait is bounded: a wait that does not come true sets an error word that
 // the host reads (zlm_gemm_tc_status) and makes every role leave its loop; the
@@ -487,34 +493,241 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     }
 }
 
-// adds the K shares up in the order 0 .. splits-1 and finishes the product in the wanted mode
+// ---------------------------------------------------------------------------
+// The few-token form (17 to 384 tokens) as a persistent kernel.  W is the 128-row operand,
+// the tokens are the product's N (a tile of BN = 32, 64 or 128).  A work item is a tile of
+// 128 outputs x BN tokens and one of `ks` shares of K; one block per SM walks the items, its
+// TMA ring and its two accumulators running on across items, so that an item's start and its
+// epilogue hide behind its neighbours' streams (the stand-alone blocks of gemm_tc_kernel pay
+// both for every item, which at a few hundred KB of W per item is most of their time).
+// The first `whole` tiles are items of their own (all of K, written in the wanted mode); each
+// of the other tiles is `ks` items, which leave their fp32 shares in scratch memory for
+// gemm_tc_reduce_kernel.  (Adding the shares up inside this kernel, by the epilogue warps of the
+// item that finishes a tile last, was built and gave the same bits; under the load of the weight
+// stream its reads of the shares took several times as long as the whole second kernel does.)
+// ---------------------------------------------------------------------------
+// this thread's output `row`, tokens t0 .. t0+15, in the wanted mode; every lane of the warp calls it
+template <int MODE>
+__device__ __forceinline__ void store_swapped16(const float* v, void* Y, int row, int t0, int T, int N, int ldy, int lane) {
+    if (MODE == 3) {
+        // lanes 0-7 and 16-23 hold gate channels, lanes 8-15 and 24-31 the matching up
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const float u = __shfl_down_sync(0xffffffffu, v[i], 8);
+            if ((lane & 8) == 0 && row < N && t0 + i < T) {
+                const int ch = (row >> 4) * 8 + (row & 7);
+                ((__nv_bfloat16*)Y)[(size_t)(t0 + i) * ldy + ch] = __float2bfloat16_rn(silu_mul(v[i], u));
+            }
+        }
+        return;
+    }
+    if (row >= N) return;
+    if (MODE == 1) {
+        float old[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) old[i] = t0 + i < T ? __ldcg((const float*)Y + (size_t)(t0 + i) * ldy + row) : 0.f;
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+            if (t0 + i < T) ((float*)Y)[(size_t)(t0 + i) * ldy + row] = old[i] + v[i];
+    } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            if (t0 + i >= T) break;
+            const size_t off = (size_t)(t0 + i) * ldy + row;
+            if (MODE == 0) ((__nv_bfloat16*)Y)[off] = __float2bfloat16_rn(v[i]);
+            else ((float*)Y)[off] = v[i];
+        }
+    }
+}
+
+template <int BN, int STAGES, int MODE>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tc_few_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                   void* __restrict__ Y, int T, int N, int K, int ldy, int whole, int ks,
+                   float* __restrict__ part) {
+    constexpr unsigned A_BYTES = TC_BM * TC_BK * 2, B_BYTES = BN * TC_BK * 2;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    unsigned char* sA = smem;
+    unsigned char* sB = smem + STAGES * A_BYTES;
+    uint64_t* full = (uint64_t*)(sB + STAGES * B_BYTES);
+    uint64_t* empty = full + STAGES;
+    uint64_t* acc_full = empty + STAGES;       // [2]
+    uint64_t* acc_empty = acc_full + 2;        // [2]
+    unsigned* tmem_slot = (unsigned*)(acc_empty + 2);
+    volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int KB_all = (K + TC_BK - 1) / TC_BK;
+    const int kb_per = (KB_all + ks - 1) / ks;
+    const int n_tiles = (N + TC_BM - 1) / TC_BM, t_tiles = (T + BN - 1) / BN;
+    const int rest = max(1, n_tiles * t_tiles - whole);       // tiles that are cut along K
+    const int items = whole + (n_tiles * t_tiles - whole) * ks;
+    constexpr unsigned ACC = BN < 32 ? 32 : BN;      // tensor-memory columns of one accumulator
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n"
+                     ::"r"(smem_u32(tmem_slot)), "r"(2 * ACC) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const unsigned tmem_base = *tmem_slot;
+    pdl_launch_dependents();
+    pdl_wait();
+
+    // item -> (tile of outputs, tile of tokens, share of K); the share's k blocks
+#define ZLM_ITEM(item)                                                        \
+    const bool split = (item) >= whole;                                       \
+    const int z = split ? ((item) - whole) / rest : 0;                        \
+    const int tile = split ? whole + ((item) - whole) % rest : (item);        \
+    const int a0row = (tile / t_tiles) * TC_BM, b0row = (tile % t_tiles) * BN; \
+    const int kb_lo = z * kb_per;                                             \
+    const int KB = split ? max(0, min(KB_all, kb_lo + kb_per) - kb_lo) : KB_all;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            unsigned it = 0;
+            bool ok = true;
+            for (int item = blockIdx.x; item < items && ok; item += gridDim.x) {
+                ZLM_ITEM(item)
+                for (int kb = 0; kb < KB; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    if (!mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1, abort_flag, 1)) { ok = false; break; }
+                    mbar_expect_tx(&full[s], A_BYTES + B_BYTES);
+                    tma_load_2d(sA + s * A_BYTES, &map_w, (kb_lo + kb) * TC_BK, a0row, &full[s]);
+                    tma_load_2d(sB + s * B_BYTES, &map_x, (kb_lo + kb) * TC_BK, b0row, &full[s]);
+                }
+            }
+            if (*abort_flag) {
+                for (unsigned j = it > (unsigned)STAGES ? it - STAGES : 0; j < it; ++j)
+                    mbar_drain(&full[j % STAGES], (j / STAGES) & 1);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const unsigned idesc = (1u << 4) | (1u << 7) | (1u << 10) | ((unsigned)(BN >> 3) << 17) |
+                                   ((unsigned)(TC_BM >> 4) << 24);
+            unsigned it = 0, local = 0;
+            bool ok = true;
+            for (int item = blockIdx.x; item < items && ok; item += gridDim.x, ++local) {
+                ZLM_ITEM(item)
+                (void)a0row; (void)b0row; (void)split;
+                const unsigned buf = local & 1;
+                ok = mbar_wait(&acc_empty[buf], ((local >> 1) & 1) ^ 1, abort_flag, 4);
+                if (!ok) break;
+                tc_fence_after();
+                for (int kb = 0; kb < KB; ++kb, ++it) {
+                    const int s = it % STAGES;
+                    ok = mbar_wait(&full[s], (it / STAGES) & 1, abort_flag, 2);
+                    if (!ok) break;
+                    tc_fence_after();
+                    const uint64_t ad = make_desc(smem_u32(sA + s * A_BYTES)), bd = make_desc(smem_u32(sB + s * B_BYTES));
+#pragma unroll
+                    for (int k = 0; k < TC_BK / 16; ++k)
+                        tc_mma(tmem_base + buf * ACC, ad + ((k * 32) >> 4), bd + ((k * 32) >> 4), idesc, (kb | k) != 0);
+                    tc_commit(&empty[s]);
+                }
+                tc_commit(&acc_full[buf]);
+            }
+            if (!ok) { tc_commit(&acc_full[0]); tc_commit(&acc_full[1]); }     // let the epilogue out
+        }
+    } else {
+        const int lg = warp & 3;
+        const size_t TN = (size_t)T * N;
+        unsigned local = 0;
+        for (int item = blockIdx.x; item < items; item += gridDim.x, ++local) {
+            ZLM_ITEM(item)
+            const unsigned buf = local & 1;
+            const bool ok = mbar_wait(&acc_full[buf], (local >> 1) & 1, abort_flag, 3);
+            tc_fence_after();
+            if (!ok || *abort_flag) break;
+            const int row = a0row + lg * 32 + lane;
+            const unsigned taddr = tmem_base + ((unsigned)(lg * 32) << 16) + buf * ACC;
+            if (!split) {
+#pragma unroll 1
+                for (int c = 0; c < BN; c += 16) {
+                    float v[16];
+                    tc_ld16(taddr + (unsigned)c, v);
+                    store_swapped16<MODE>(v, Y, row, b0row + c, T, N, ldy, lane);
+                }
+            } else {
+                // this item's share of the tile
+#pragma unroll 1
+                for (int c = 0; c < BN; c += 16) {
+                    float v[16];
+                    tc_ld16(taddr + (unsigned)c, v);
+                    if (row < N) {
+#pragma unroll
+                        for (int i = 0; i < 16; ++i)
+                            if (b0row + c + i < T) part[(size_t)z * TN + (size_t)(b0row + c + i) * N + row] = KB ? v[i] : 0.f;
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[buf]);
+        }
+    }
+#undef ZLM_ITEM
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(2 * ACC) : "memory");
+    }
+}
+
+// adds the K shares of the outputs from n_from on up in the order 0 .. splits-1 and finishes the
+// product there in the wanted mode (n_from is a multiple of 128)
 template <int MODE>
 __global__ void gemm_tc_reduce_kernel(void* __restrict__ Y, const float* __restrict__ part, int T, int N, int ldy,
-                                      int splits) {
+                                      int splits, int n_from) {
     pdl_launch_dependents();
     pdl_wait();
     const size_t total = (size_t)T * N;
-    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < (MODE == 3 ? total / 2 : total);
-         e += (size_t)gridDim.x * blockDim.x) {
+    const int width = N - n_from;
+    const size_t count = (size_t)T * (MODE == 3 ? width / 2 : width);
+    for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < count; e += (size_t)gridDim.x * blockDim.x) {
         if (MODE == 3) {
-            // element e of [T, N/2]: channel c of token t; gate at column (c/8)*16 + c%8, up 8 further
-            const size_t t = e / (N / 2);
-            const int c = (int)(e - t * (N / 2));
+            // channel c of token t; its gate is output (c/8)*16 + c%8, its up 8 further
+            const size_t t = e / (width / 2);
+            const int c = n_from / 2 + (int)(e - t * (width / 2));
             const size_t g = t * N + (size_t)(c >> 3) * 16 + (c & 7);
             float sg = 0.f, su = 0.f;
             for (int s = 0; s < splits; ++s) { sg += part[s * total + g]; su += part[s * total + g + 8]; }
             ((__nv_bfloat16*)Y)[t * ldy + c] = __float2bfloat16_rn(silu_mul(sg, su));
         } else {
-            const size_t t = e / N;
-            const int n = (int)(e - t * N);
+            const size_t t = e / width;
+            const int n = n_from + (int)(e - t * width);
             float sum = 0.f;
-            for (int s = 0; s < splits; ++s) sum += part[s * total + e];
+            for (int s = 0; s < splits; ++s) sum += part[s * total + t * N + n];
             const size_t off = t * ldy + n;
             if (MODE == 0) ((__nv_bfloat16*)Y)[off] = __float2bfloat16_rn(sum);
             else if (MODE == 1) ((float*)Y)[off] += sum;
             else ((float*)Y)[off] = sum;
         }
     }
+}
+
+static int launch_reduce(void* Y, const float* scratch, int T, int N, int ldy, int mode, int splits, int n_from,
+                         cudaStream_t st) {
+    const size_t elems = (size_t)T * (N - n_from) / (mode == 3 ? 2 : 1);
+    int blocks = (int)((elems + 255) / 256);
+    if (blocks > 148 * 8) blocks = 148 * 8;
+    if (mode == 0) zlm_launch(gemm_tc_reduce_kernel<0>, dim3(blocks), dim3(256), 0, st, Y, scratch, T, N, ldy, splits, n_from);
+    else if (mode == 1) zlm_launch(gemm_tc_reduce_kernel<1>, dim3(blocks), dim3(256), 0, st, Y, scratch, T, N, ldy, splits, n_from);
+    else if (mode == 2) zlm_launch(gemm_tc_reduce_kernel<2>, dim3(blocks), dim3(256), 0, st, Y, scratch, T, N, ldy, splits, n_from);
+    else zlm_launch(gemm_tc_reduce_kernel<3>, dim3(blocks), dim3(256), 0, st, Y, scratch, T, N, ldy, splits, n_from);
+    return zlm_check_launch("gemm_tc_reduce");
 }
 
 // ---------------------------------------------------------------- host side
@@ -594,14 +807,7 @@ static int launch_tc(void* Y, const void* X, const void* W, int T, int N, int K,
 #undef ZLM_TC_LAUNCH
     rc = zlm_check_launch("gemm_tc");
     if (rc || ksplit <= 1) return rc;
-    const size_t elems = (size_t)T * N / (mode == 3 ? 2 : 1);
-    int blocks = (int)((elems + 255) / 256);
-    if (blocks > 148 * 8) blocks = 148 * 8;
-    if (mode == 0) zlm_launch(gemm_tc_reduce_kernel<0>, dim3(blocks), dim3(256), 0, st, Y, (const float*)scratch, T, N, ldy, ksplit);
-    else if (mode == 1) zlm_launch(gemm_tc_reduce_kernel<1>, dim3(blocks), dim3(256), 0, st, Y, (const float*)scratch, T, N, ldy, ksplit);
-    else if (mode == 2) zlm_launch(gemm_tc_reduce_kernel<2>, dim3(blocks), dim3(256), 0, st, Y, (const float*)scratch, T, N, ldy, ksplit);
-    else zlm_launch(gemm_tc_reduce_kernel<3>, dim3(blocks), dim3(256), 0, st, Y, (const float*)scratch, T, N, ldy, ksplit);
-    return zlm_check_launch("gemm_tc_reduce");
+    return launch_reduce(Y, scratch, T, N, ldy, mode, ksplit, 0, st);
 }
 
 static int sm_count() {
@@ -692,33 +898,71 @@ extern "C" int zlm_gemm_tc_set_form(int form, int width) {
     return ZLM_OK;
 }
 
+// How the few-token form cuts a product: tokens in tiles of bn; the first `whole` tiles of
+// 128 outputs x bn tokens (as many full rounds of one tile per SM as there are) are computed
+// in one piece; each of the others is cut along K into `ks` shares, as many as fill the last
+// round (at most 8, each at least 8 k blocks), and a second kernel adds the shares up.
+struct FewPlan { int bn, whole, ks, t_tiles; };
+static FewPlan few_plan(int T, int N, int K) {
+    FewPlan p;
+    p.bn = T <= 32 ? 32 : (T <= 64 ? 64 : 128);
+    p.t_tiles = (T + p.bn - 1) / p.bn;
+    const int tiles = ((N + TC_BM - 1) / TC_BM) * p.t_tiles, sms = sm_count();
+    const int kb = (K + TC_BK - 1) / TC_BK;
+    p.whole = tiles / sms * sms;
+    p.whole -= p.whole % p.t_tiles;          // the split tiles are whole rows of token tiles: outputs from some n on
+    const int rest = tiles - p.whole;
+    p.ks = 1;
+    if (rest > 0) p.ks = max(1, min(min(8, sms / rest), kb / 8));
+    if (p.ks == 1) p.whole = tiles;
+    return p;
+}
+
+template <int BN, int STAGES>
+static int launch_tc_few(void* Y, const void* X, const void* W, int T, int N, int K, int ldx, int ldy, int mode,
+                         const FewPlan& plan, float* scratch, cudaStream_t st) {
+    CUtensorMap mx, mw;
+    int rc = make_map(&mx, X, T, K, ldx, BN);
+    if (rc) return rc;
+    rc = make_map(&mw, W, N, K, K, TC_BM);
+    if (rc) return rc;
+    const size_t smem = (size_t)STAGES * (TC_BM + BN) * TC_BK * 2 + 1024 + 256;
+    const int tiles = ((N + TC_BM - 1) / TC_BM) * plan.t_tiles;
+    const long long items = plan.whole + (long long)(tiles - plan.whole) * plan.ks;
+    const int blocks = (int)(items < sm_count() ? items : sm_count());
+#define ZLM_TCF_LAUNCH(M)                                                                                  \
+    {                                                                                                      \
+        auto kern = gemm_tc_few_kernel<BN, STAGES, M>;                                                     \
+        static bool attr_set = false;                                                                      \
+        if (!attr_set) {                                                                                   \
+            cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+            if (e != cudaSuccess) {                                                                        \
+                zlm_set_error("gemm_tc: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e)); \
+                return ZLM_ERR_CUDA;                                                                       \
+            }                                                                                              \
+            attr_set = true;                                                                               \
+        }                                                                                                  \
+        zlm_launch(kern, dim3(blocks), dim3(TC_THREADS), smem, st, mw, mx, Y, T, N, K, ldy, plan.whole, plan.ks, scratch); \
+    }
+    if (mode == 0) ZLM_TCF_LAUNCH(0)
+    else if (mode == 1) ZLM_TCF_LAUNCH(1)
+    else if (mode == 2) ZLM_TCF_LAUNCH(2)
+    else ZLM_TCF_LAUNCH(3)
+#undef ZLM_TCF_LAUNCH
+    rc = zlm_check_launch("gemm_tc_few");
+    if (rc || plan.ks <= 1) return rc;
+    return launch_reduce(Y, scratch, T, N, ldy, mode, plan.ks, plan.whole / plan.t_tiles * TC_BM, st);
+}
+
 // 1 if the tensor-memory kernel takes this product (else use zlm_gemm_bf16_mma)
 extern "C" int zlm_gemm_tc_supported(int T, int N, int K, int ldx) {
     return (T >= 1 && N >= 8 && K >= 8 && K % 8 == 0 && ldx % 8 == 0) ? 1 : 0;
 }
 
-// Into how many shares the few-token form cuts K.  The product streams W once; with `ctas`
-// output tiles on 148 SMs the time is the number of rounds the busiest SM runs, each round a
-// tile's share of W, plus writing and re-reading the fp32 partial products (mostly in L2,
-// counted at half weight).  The number of shares (at most 8, each at least 8 k blocks) that
-// makes this smallest is taken.
+// shares of K whose fp32 partial products need scratch memory (T * N floats each)
 extern "C" int zlm_gemm_tc_ksplit(int T, int N, int K) {
     if (T > 384) return 1;
-    const int bn = T <= 32 ? 32 : (T <= 64 ? 64 : 128);
-    const int ctas = ((N + TC_BM - 1) / TC_BM) * ((T + bn - 1) / bn);
-    const int kb = (K + TC_BK - 1) / TC_BK;
-    const int sms = 148;
-    const double w_bytes = 2.0 * N * K;
-    int best = 1;
-    double best_cost = 1e300;
-    for (int s = 1; s <= 8; ++s) {
-        if (s > 1 && kb / s < 8) break;
-        const int rounds = (ctas * s + sms - 1) / sms;
-        double cost = rounds * (w_bytes / ctas / s);
-        if (s > 1) cost += 0.5 * (2.0 * s * T * (double)N * 4.0) / sms;
-        if (cost < best_cost * 0.97) { best_cost = cost; best = s; }      // a new split must pay for its reduce launch
-    }
-    return best;
+    return few_plan(T, N, K).ks;
 }
 
 // mode 0: Y bf16 = X W^T; mode 1: Y fp32 += X W^T; mode 2: Y fp32 = X W^T;
@@ -734,9 +978,20 @@ extern "C" int zlm_gemm_tc(void* Y, const void* X, const void* W, int T, int N, 
     const int ks = zlm_gemm_tc_ksplit(T, N, K);
     ZLM_REQUIRE(ks == 1 || scratch, "gemm_tc: scratch for %d shares of K is missing", ks);
     // few tokens: W is the 128-row operand so that it streams at full height
-    if (T <= 32) return launch_tc<32, 8, true>(Y, X, W, T, N, K, ldx, ldy, mode, ks, scratch, st);
-    if (T <= 64) return launch_tc<64, 8, true>(Y, X, W, T, N, K, ldx, ldy, mode, ks, scratch, st);
-    if (T <= 384) return launch_tc<128, 6, true>(Y, X, W, T, N, K, ldx, ldy, mode, ks, scratch, st);
+    if (T <= 384) {
+        const FewPlan plan = few_plan(T, N, K);
+        const long long tiles = (long long)((N + TC_BM - 1) / TC_BM) * plan.t_tiles;
+        if (plan.whole + (tiles - plan.whole) * plan.ks <= sm_count()) {
+            // one round of blocks: nothing for a persistent block to overlap, and the stand-alone
+            // blocks are a microsecond or two faster there (here all tiles are cut alike)
+            if (T <= 32) return launch_tc<32, 8, true>(Y, X, W, T, N, K, ldx, ldy, mode, plan.ks, scratch, st);
+            if (T <= 64) return launch_tc<64, 8, true>(Y, X, W, T, N, K, ldx, ldy, mode, plan.ks, scratch, st);
+            return launch_tc<128, 6, true>(Y, X, W, T, N, K, ldx, ldy, mode, plan.ks, scratch, st);
+        }
+        if (T <= 32) return launch_tc_few<32, 8>(Y, X, W, T, N, K, ldx, ldy, mode, plan, scratch, st);
+        if (T <= 64) return launch_tc_few<64, 8>(Y, X, W, T, N, K, ldx, ldy, mode, plan, scratch, st);
+        return launch_tc_few<128, 6>(Y, X, W, T, N, K, ldx, ldy, mode, plan, scratch, st);
+    }
     // The tile's width: tiles run in rounds of one per SM, and a round costs its width.  N = 4096 at
     // 2,048 tokens is 256 tiles of 256 columns (2 rounds, the second 73 % full) or 288 of 240 (2 rounds,
     // 97 % full).  A narrower tile re-reads the activations more often, so it has to win by more than
