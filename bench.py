@@ -30,7 +30,13 @@ QWEN3_8B = {
     "vocab_size": 151936, "rope_theta": 1000000.0, "rms_norm_eps": 1e-6, "tie_word_embeddings": False,
     "max_position_embeddings": 40960, "hidden_act": "silu",
 }
-FULL_LAYERS = 36
+# the other layer sizes that the baseline's configurations name (--sizes); the default run stays Qwen3-8B
+OTHER_SIZES = {
+    "0.6b": dict(QWEN3_8B, num_hidden_layers=28, hidden_size=1024, num_attention_heads=16, num_key_value_heads=8,
+                 intermediate_size=3072, tie_word_embeddings=True),
+    "32b": dict(QWEN3_8B, num_hidden_layers=64, hidden_size=5120, num_attention_heads=64, num_key_value_heads=8,
+                intermediate_size=25600),
+}
 PROMPT_LEN = 2048
 CONTEXT = 4096
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
@@ -119,7 +125,10 @@ def run(args) -> dict:
     from zlm_b200.sampling import SamplingParams
 
     pk = peaks()
-    d = dict(QWEN3_8B)
+    d = dict(OTHER_SIZES.get(args.sizes, QWEN3_8B))
+    full_layers = d["num_hidden_layers"]
+    if args.layers is None:
+        args.layers = full_layers
     d["num_hidden_layers"] = args.layers
     cfg = config_from_dict(d)
     B = args.batch
@@ -227,12 +236,12 @@ def run(args) -> dict:
                 eng.release(sl)
 
     return {
-        "metric": "decode tokens/s (Qwen3-8B sizes, bf16, batch 8, 2048-token prompts, context 4096)",
+        "metric": f"decode tokens/s (Qwen3-{args.sizes.upper()} sizes, bf16, batch {B}, 2048-token prompts, context 4096)",
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
         "ms_per_step": round(ms / steps, 4), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic (random weights, uniform random token ids)",
         "impl": "zlm_b200",
-        "config": {"model": "qwen3-8b-sizes", "layers": args.layers, "layers_full": FULL_LAYERS,
+        "config": {"model": f"qwen3-{args.sizes}-sizes", "layers": args.layers, "layers_full": full_layers,
                    "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads,
                    "kv_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim,
                    "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size, "global_batch": B,
@@ -255,8 +264,8 @@ def profile(args) -> int:
     from zlm_b200 import Engine, StepEntry
     from zlm_b200.registry import config_from_dict
     from zlm_b200.sampling import SamplingParams
-    d = dict(QWEN3_8B)
-    d["num_hidden_layers"] = args.layers
+    d = dict(OTHER_SIZES.get(args.sizes, QWEN3_8B))
+    d["num_hidden_layers"] = args.layers if args.layers is not None else d["num_hidden_layers"]
     cfg = config_from_dict(d)
     B, L = args.batch, args.prompt_len
     eng = Engine.from_random(cfg, seed=0, dtype="bfloat16", device="cuda:0", max_tokens=B * (L + 256),
@@ -301,7 +310,9 @@ def main() -> int:
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="zlm_b200")
     ap.add_argument("--batch", type=int, default=8)
-    ap.add_argument("--layers", type=int, default=FULL_LAYERS)
+    ap.add_argument("--layers", type=int, default=None, help="fewer layers than the sizes' own (both numbers go into config)")
+    ap.add_argument("--sizes", choices=["8b", "0.6b", "32b"], default="8b",
+                    help="layer sizes: Qwen3-8B (the headline configuration), Qwen3-0.6B or Qwen3-32B")
     ap.add_argument("--point-steps", type=int, default=64)
     ap.add_argument("--no-points", action="store_true")
     ap.add_argument("--profile", choices=["decode", "prefill"], help="run a small case for ncu and exit")
