@@ -218,7 +218,9 @@ def run(args) -> dict:
     # ---- the same through the Python entry point ------------------------------------
     ps = prompts(B)
     n_e2e = min(steps, 128)
-    eng.generate(ps[:1], max_tokens=4)                       # warm the B=1 graph away from the timing
+    # warm-up: the same call once, so that the decode graphs of every context length the run
+    # passes through exist before the timed call (a capture costs as much as several steps)
+    eng.generate(ps, max_tokens=n_e2e + 1, stop_token_ids=())
     res = eng.generate(ps, max_tokens=n_e2e + 1, stop_token_ids=())
     st = res.stats
     e2e = {"value": round(st.new_tokens and (B * st.decode_steps) / st.decode_ms * 1e3, 1), "unit": "tokens/s",
