@@ -266,7 +266,7 @@ class PrefillPlan:
         self.len_bucket = 1
 
 
-@pytest.mark.parametrize("impl", ["mma", None])
+@pytest.mark.parametrize("impl", ["mma", None, "tc1", "tc2"])
 @pytest.mark.parametrize("nq,nkv,hd,window", [(4, 2, 16, 0), (6, 2, 48, 24), (5, 5, 80, 0), (8, 1, 128, 100),
                                               (32, 8, 128, 0), (6, 3, 32, 70), (4, 1, 64, 64), (3, 3, 128, 0),
                                               (4, 2, 128, 17)])
@@ -292,8 +292,14 @@ def test_attention_prefill_kernel(K, nq, nkv, hd, window, impl):
     PlainKernels().attention(want, q, pool, table, pos, slot, nq, nkv, hd, scale, window)
     got = torch.empty(T, nq * hd, dtype=dt, device="cuda")
     plan = PrefillPlan(slots, starts, news)
-    plan.attention_impl = impl          # None: the tcgen05 kernel where it takes the shape (head size 128)
-    K.attention(got, q.cuda(), pool.cuda(), table.cuda(), pos.cuda(), slot.cuda(), nq, nkv, hd, scale, window, plan)
+    # None: the tcgen05 kernel where it takes the shape (head size 128), with one or two heads of a
+    # kv group per block as it chooses; "tc1" / "tc2" force that number
+    plan.attention_impl = impl if impl == "mma" else None
+    K.set_prefill_attention_heads({"tc1": 1, "tc2": 2}.get(impl, 0))
+    try:
+        K.attention(got, q.cuda(), pool.cuda(), table.cuda(), pos.cuda(), slot.cuda(), nq, nkv, hd, scale, window, plan)
+    finally:
+        K.set_prefill_attention_heads(0)
     assert K.gemm_tc_status() == 0
     close(got, want, dt, atol=3e-2, rtol=3e-2)
     vfar = pool[page, 1, nkv - 1, far % PAGE, :].float()
@@ -319,7 +325,7 @@ def test_linear_bf16_tcgen05(K, T, N, K_):
 
 
 @pytest.mark.parametrize("form,width", [("single", 256), ("single", 240), ("single", 224), ("pair", 256),
-                                        ("pair", 240), ("pair", 224), (None, 0)])
+                                        ("pair", 240), ("pair", 224), ("pair", 128), (None, 0)])
 @pytest.mark.parametrize("T,N,K_", [(385, 300, 72), (700, 2064, 264), (1000, 1000, 520)])
 def test_linear_bf16_tcgen05_many_tokens(K, T, N, K_, form, width):
     """The persistent many-token product in both forms (one block per tile; a pair of

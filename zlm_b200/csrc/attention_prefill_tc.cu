@@ -24,6 +24,7 @@
 // (src/kernels/transformer/attention.zig:86-164; per-row bound in block prefill:
 // src/runtime/executor.zig:565-584; window start: :93-98).
 #include "tc_common.cuh"
+#include <math.h>
 
 #define FA_BM 128          // query rows per block
 #define FA_HD 128          // head size this kernel is built for
@@ -319,6 +320,8 @@ extern "C" int zlm_attention_prefill_tc_supported(int nq, int nkv, int hd, int q
 }
 
 // pool_rows: pages * 2 * nkv * 64 (all rows of the layer's pool, head size 128 each)
+static int g_fa_heads = 0;
+
 extern "C" int zlm_attention_prefill_tc(void* out, int out_stride, const void* q, int q_stride, int T,
                                         const void* pool, long long pool_pages, const int* block_table,
                                         int table_stride, const int* cu_seqlens, const int* seq_slot,
@@ -337,7 +340,26 @@ extern "C" int zlm_attention_prefill_tc(void* out, int out_stride, const void* q
     rc = zlm_make_map_2d(&mkv, pool, pool_pages * 2 * nkv * ZLM_PAGE, hd, hd, ZLM_PAGE, 64);
     if (rc) return rc;
     const int tiles = (max_new + FA_BM - 1) / FA_BM;
-    const int hpc = ((nq / nkv) % 2 == 0) ? 2 : 1;       // two heads of a kv group share a block if the group is even
+    // Two heads of a kv group can share a block (they share its keys and values, and one head's
+    // softmax runs under the other's products: measured 1.46 times the throughput per head), but
+    // the blocks are then half as many and the longest twice as long.  The step takes about as
+    // long as the larger of its longest block (the last tile of the longest prompt) and its whole
+    // work spread over the SMs; the form for which that is smaller runs (2,048 tokens, 16 heads
+    // over 8: 40 us with one head per block, 50 with two; 32 over 8: 76 and 57).
+    int hpc = 1;
+    if ((nq / nkv) % 2 == 0) {
+        static int sms = 0;
+        if (!sms) {
+            int dev = 0;
+            if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+                sms = 148;
+        }
+        const double pairs_cost = 2.0 / 1.46;                                   // a block of two heads, per page, against one head
+        const double work = (double)R * tiles * (tiles + 1) / 2 / sms;          // tiles' pages summed, per SM and head
+        const double two = fmax(tiles * pairs_cost, work * (nq / 2) * pairs_cost), one = fmax((double)tiles, work * nq);
+        hpc = two <= one ? 2 : 1;
+        if (g_fa_heads) hpc = g_fa_heads;
+    }
     ZLM_REQUIRE((long long)R * tiles * nq < 2147483647LL, "attention_prefill_tc: too many tiles");
     const size_t smem = (size_t)hpc * FA_BM * FA_HD * 2 + 2 * FA_STAGES * ZLM_PAGE * FA_HD * 2 +
                         (size_t)hpc * 2 * FA_BM * ZLM_PAGE * 2 + 1024 + 256;
@@ -362,6 +384,14 @@ extern "C" int zlm_attention_prefill_tc(void* out, int out_stride, const void* q
     else ZLM_FA_LAUNCH(1)
 #undef ZLM_FA_LAUNCH
     return zlm_check_launch("attention_prefill_tc");
+}
+
+// heads of a kv group per block: 0 lets the dispatcher choose; 1 or 2 force that many where the kv
+// groups are even (odd groups always take one).  For tests and measurements.
+extern "C" int zlm_attention_prefill_tc_set_heads(int heads) {
+    ZLM_REQUIRE(heads >= 0 && heads <= 2, "attention_prefill_tc: %d heads per block cannot be forced", heads);
+    g_fa_heads = heads;
+    return ZLM_OK;
 }
 
 extern "C" int zlm_attention_tc_status() {

@@ -888,11 +888,12 @@ static int launch_tc_pair(void* Y, const void* X, const void* W, int T, int N, i
 
 // Which many-token form runs, and how wide its tiles are: 0 lets the dispatcher choose (pairs of
 // blocks; the width by the rule in zlm_gemm_tc).  form 1: single blocks, 2: pairs; width 256, 240
-// or 224.  For tests and measurements.
+// or 224 (pairs: 128 too).  For tests and measurements.
 static int g_tc_form = 0, g_tc_width = 0;
 extern "C" int zlm_gemm_tc_set_form(int form, int width) {
     ZLM_REQUIRE(form >= 0 && form <= 2, "gemm_tc: form %d", form);
-    ZLM_REQUIRE(width == 0 || width == 256 || width == 240 || width == 224, "gemm_tc: tile width %d", width);
+    ZLM_REQUIRE(width == 0 || width == 256 || width == 240 || width == 224 || (width == 128 && form == 2),
+                "gemm_tc: tile width %d", width);
     g_tc_form = form;
     g_tc_width = width;
     return ZLM_OK;
@@ -1001,9 +1002,10 @@ extern "C" int zlm_gemm_tc(void* Y, const void* X, const void* W, int T, int N, 
         const long long m2 = (T + TCQ_BM - 1) / TCQ_BM, pairs = sm_count() / 2;
         auto cost2 = [&](int bn) { return ((m2 * ((N + bn - 1) / bn) + pairs - 1) / pairs) * bn; };
         int best = 256;
-        for (int bn : {240, 224})
+        for (int bn : {240, 224, 128})       // 128: products whose wider tiles would leave most pairs idle
             if (cost2(bn) * 100 < cost2(256) * 95 && cost2(bn) < cost2(best)) best = bn;
         if (g_tc_width) best = g_tc_width;
+        if (best == 128) return launch_tc_pair<128, 8>(Y, X, W, T, N, K, ldx, ldy, mode, st);
         if (best == 240) return launch_tc_pair<240, 6>(Y, X, W, T, N, K, ldx, ldy, mode, st);
         if (best == 224) return launch_tc_pair<224, 6>(Y, X, W, T, N, K, ldx, ldy, mode, st);
         return launch_tc_pair<256, 6>(Y, X, W, T, N, K, ldx, ldy, mode, st);

@@ -189,10 +189,16 @@ class CudaKernels:
 
     def set_gemm_form(self, form: Optional[str] = None, width: int = 0) -> None:
         """Forces the many-token tcgen05 product's form ("single": one block per tile,
-        "pair": two blocks per tile with cta_group::2) and tile width (256, 240, 224);
+        "pair": two blocks per tile with cta_group::2) and tile width (256, 240, 224; pairs also 128);
         None / 0 give the choice back to the dispatcher.  For tests and measurements."""
         code = {None: 0, "single": 1, "pair": 2}[form]
         if self.lib.zlm_gemm_tc_set_form(c_int(code), c_int(width)) != 0:
+            raise KernelError(self.lib.zlm_last_error().decode())
+
+    def set_prefill_attention_heads(self, heads: int = 0) -> None:
+        """Forces how many heads of a kv group share a block of the tcgen05 prefill attention
+        (1 or 2; 0 gives the choice back to the dispatcher).  For tests and measurements."""
+        if self.lib.zlm_attention_prefill_tc_set_heads(c_int(heads)) != 0:
             raise KernelError(self.lib.zlm_last_error().decode())
 
     def linear_swiglu(self, out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, impl: Optional[str] = None) -> None:
