@@ -97,6 +97,19 @@ __device__ __forceinline__ void qk_norm_rope_write_item(
 #pragma unroll
         for (int a = 0; a < 2; ++a)
             if (j0 + a * ROPE_WARPS < j_stop) rope_load_vec<TA, NPL>(nxt[a], base + (size_t)(j0 + a * ROPE_WARPS) * hd);
+        // what a lane needs of the token's rotation and of the norm weights is the same for every
+        // head: into registers once (at many tokens this kernel is bound by its instructions)
+        float rc[NPL], rs[NPL], wq[NPL], wk[NPL];
+        const bool low = lane * NPL < half;              // a lane's elements are all in one half of the head
+#pragma unroll
+        for (int r = 0; r < NPL; ++r) {
+            const int e = lane * NPL + r;
+            const int i = low ? e : e - half;
+            rc[r] = i < ang ? cs[i] : 1.f;
+            rs[r] = i < ang ? sn[i] : 0.f;
+            wq[r] = has_norm ? qw[e] : 1.f;
+            wk[r] = (has_norm && nkv > 0) ? kw[e] : 1.f;
+        }
         for (int j = j0; j < j_stop; j += ROPE_WARPS) {
             float v[NPL];
 #pragma unroll
@@ -110,19 +123,17 @@ __device__ __forceinline__ void qk_norm_rope_write_item(
                     for (int r = 0; r < NPL; ++r) ss = fmaf(v[r], v[r], ss);
                     ss = warp_sum(ss);
                     const float inv = 1.0f / sqrtf(ss / (float)hd + eps);
-                    const VecW& w = kind == 0 ? qw : kw;
 #pragma unroll
-                    for (int r = 0; r < NPL; ++r) v[r] = (v[r] * inv) * w[lane * NPL + r];
+                    for (int r = 0; r < NPL; ++r) v[r] = (v[r] * inv) * (kind == 0 ? wq[r] : wk[r]);
                 }
                 if (ang > 0) {
 #pragma unroll
                     for (int r = 0; r < NPL; ++r) {
                         const float other = __shfl_xor_sync(0xffffffffu, v[r], 16);
-                        const int e = lane * NPL + r;
-                        const int i = e < half ? e : e - half;
+                        const int i = low ? lane * NPL + r : lane * NPL + r - half;
                         if (i < ang) {
-                            const float x0 = e < half ? v[r] : other, x1 = e < half ? other : v[r];
-                            v[r] = e < half ? (x0 * cs[i] - x1 * sn[i]) : (x0 * sn[i] + x1 * cs[i]);
+                            const float x0 = low ? v[r] : other, x1 = low ? other : v[r];
+                            v[r] = low ? (x0 * rc[r] - x1 * rs[r]) : (x0 * rs[r] + x1 * rc[r]);
                         }
                     }
                 }
