@@ -2,7 +2,7 @@
 // Y[t, n] = sum_k X[t, k] W[n, k], fp32 accumulation.
 //
 // The step is bound by reading W once.  A block owns 16 rows of W; its 8 warps
-// split K between them (512 columns each of every 4096).  Every thread loads 16 bytes (8 consecutive k) of row g
+// split K between them (512 columns each of every 4096, or another even split).  Every thread loads 16 bytes (8 consecutive k) of row g
 // and of row g+8 straight from global memory into registers, and the 8 matching
 // k of token g of X; these registers are, as they are, the A and B fragments of
 // two m16n8k16 tensor-core products: a sum over k does not care in which order
@@ -46,7 +46,7 @@ __device__ __forceinline__ void gemv_mma(float* c, unsigned a0, unsigned a1, uns
 template <int NT, int MODE>
 __global__ void __launch_bounds__(GEMV_THREADS, GEMV_MINBLOCKS)
 gemv_bf16_kernel(void* __restrict__ Y, const __nv_bfloat16* __restrict__ X,
-                 const __nv_bfloat16* __restrict__ W, int T, int N, int K, int ldx, int ldy) {
+                 const __nv_bfloat16* __restrict__ W, int T, int N, int K, int ldx, int ldy, int SEG) {
     __shared__ float red[GEMV_WARPS][NT][GEMV_ROWS][8];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, q = lane & 3;
@@ -62,10 +62,11 @@ gemv_bf16_kernel(void* __restrict__ Y, const __nv_bfloat16* __restrict__ X,
     }
     // Four chains of sums per thread, so that four tensor-core products can be in flight
     // (one chain would run at the latency of the instruction).  K is cut into chunks of
-    // 8 x 512 columns; warp w takes the w-th 512 columns of every chunk, as 16 blocks of 32
+    // 8 x SEG columns; warp w takes the w-th SEG columns of every chunk, as blocks of 32
     // in ascending k; chain 2 * (i & 1) + h takes the h-th 16 k of block i.  The chains are
-    // added at the end, (0 + 1) + (2 + 3).  The persistent decode kernel (decode_stream.cu)
-    // adds in the same order.
+    // added at the end, (0 + 1) + (2 + 3).  SEG is 512 (the persistent decode kernel,
+    // decode_stream.cu, adds in that order) unless another width spreads K evenly over the
+    // warps where 512 would not (gemv_segment below).
     float ch[NT][4][4];
 #pragma unroll
     for (int j = 0; j < NT; ++j)
@@ -76,7 +77,7 @@ gemv_bf16_kernel(void* __restrict__ Y, const __nv_bfloat16* __restrict__ X,
 
     // GEMV_UNROLL blocks in flight.  The weights do not depend on the kernel before this one:
     // their first loads are issued before the wait for it, the activations after.
-    constexpr int SEG = 512, CHUNK = GEMV_WARPS * SEG;
+    const int CHUNK = GEMV_WARPS * SEG;
     pdl_launch_dependents();
     uint4 a[GEMV_UNROLL], b[GEMV_UNROLL];
     bool have = warp * SEG + GEMV_UNROLL * 32 <= K;
@@ -177,14 +178,27 @@ gemv_bf16_kernel(void* __restrict__ Y, const __nv_bfloat16* __restrict__ X,
     }
 }
 
+// The columns a warp takes of every chunk of K.  With 512, a K that is no multiple of 4096 leaves
+// warps idle in its last chunk: of K = 5120 two warps would read 1024 columns each and six 512,
+// of K = 1024 two warps would do everything.  Where K is a multiple of 1024 but not of 4096 the
+// widest of 640, 384, 256 and 128 columns that divides K into whole chunks is taken instead
+// (multiples of the 128 columns a warp has in flight).
+extern "C" int zlm_gemv_segment(int K) {
+    if (K % 4096 == 0 || K % 1024 != 0) return 512;
+    for (int seg : {640, 384, 256, 128})
+        if (K % (GEMV_WARPS * seg) == 0) return seg;
+    return 512;
+}
+
 template <int NT>
 static int launch_gemv(void* Y, const __nv_bfloat16* X, const __nv_bfloat16* W, int T, int N, int K,
                        int ldx, int ldy, int mode, cudaStream_t st) {
     const int blocks = (N + GEMV_ROWS - 1) / GEMV_ROWS;
-    if (mode == 0) zlm_launch(gemv_bf16_kernel<NT, 0>, blocks, GEMV_THREADS, 0, st, Y, X, W, T, N, K, ldx, ldy);
-    else if (mode == 1) zlm_launch(gemv_bf16_kernel<NT, 1>, blocks, GEMV_THREADS, 0, st, Y, X, W, T, N, K, ldx, ldy);
-    else if (mode == 2) zlm_launch(gemv_bf16_kernel<NT, 2>, blocks, GEMV_THREADS, 0, st, Y, X, W, T, N, K, ldx, ldy);
-    else zlm_launch(gemv_bf16_kernel<NT, 3>, blocks, GEMV_THREADS, 0, st, Y, X, W, T, N, K, ldx, ldy);
+    const int seg = zlm_gemv_segment(K);
+    if (mode == 0) zlm_launch(gemv_bf16_kernel<NT, 0>, blocks, GEMV_THREADS, 0, st, Y, X, W, T, N, K, ldx, ldy, seg);
+    else if (mode == 1) zlm_launch(gemv_bf16_kernel<NT, 1>, blocks, GEMV_THREADS, 0, st, Y, X, W, T, N, K, ldx, ldy, seg);
+    else if (mode == 2) zlm_launch(gemv_bf16_kernel<NT, 2>, blocks, GEMV_THREADS, 0, st, Y, X, W, T, N, K, ldx, ldy, seg);
+    else zlm_launch(gemv_bf16_kernel<NT, 3>, blocks, GEMV_THREADS, 0, st, Y, X, W, T, N, K, ldx, ldy, seg);
     return zlm_check_launch("gemv_bf16");
 }
 
