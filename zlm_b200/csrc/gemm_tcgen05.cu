@@ -1002,8 +1002,11 @@ extern "C" int zlm_gemm_tc(void* Y, const void* X, const void* W, int T, int N, 
         const long long m2 = (T + TCQ_BM - 1) / TCQ_BM, pairs = sm_count() / 2;
         auto cost2 = [&](int bn) { return ((m2 * ((N + bn - 1) / bn) + pairs - 1) / pairs) * bn; };
         int best = 256;
-        for (int bn : {240, 224, 128})       // 128: products whose wider tiles would leave most pairs idle
+        for (int bn : {240, 224})
             if (cost2(bn) * 100 < cost2(256) * 95 && cost2(bn) < cost2(best)) best = bn;
+        // 128 columns: half the reuse of the activations per product, so only where the wider tiles
+        // would leave a third of the pairs idle (N = 1024 at 2,048 tokens: 32 tiles on 74 pairs)
+        if (cost2(128) * 100 < cost2(best) * 70) best = 128;
         if (g_tc_width) best = g_tc_width;
         if (best == 128) return launch_tc_pair<128, 8>(Y, X, W, T, N, K, ldx, ldy, mode, st);
         if (best == 240) return launch_tc_pair<240, 6>(Y, X, W, T, N, K, ldx, ldy, mode, st);
