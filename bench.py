@@ -258,6 +258,35 @@ def run(args) -> dict:
     }
 
 
+def unequal(args) -> int:
+    """The baseline's small-model scenario: 64 prompts of unequal lengths (uniform in
+    [16, 2048]) prefilled as one batch, then 256 decode steps, through ``Engine.generate``
+    (host tokens in and out).  The call is made twice; the second is reported."""
+    import torch
+    from zlm_b200 import Engine
+    from zlm_b200.registry import config_from_dict
+    d = dict(OTHER_SIZES.get(args.sizes, QWEN3_8B))
+    full_layers = d["num_hidden_layers"]
+    d["num_hidden_layers"] = args.layers if args.layers is not None else full_layers
+    cfg = config_from_dict(d)
+    g = torch.Generator().manual_seed(0)
+    lens = torch.randint(16, 2049, (64,), generator=g).tolist()
+    ps = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in lens]
+    eng = Engine.from_random(cfg, seed=0, dtype="bfloat16", device="cuda:0", max_tokens=64 * 2368, max_batch=64,
+                             max_seq_len=CONTEXT)
+    for _ in range(2):
+        res = eng.generate(ps, max_tokens=256, stop_token_ids=())
+    st = res.stats
+    print(json.dumps({
+        "scenario": f"64 unequal prompts (16..2048 tokens) and 256 decode steps, Qwen3-{args.sizes.upper()} sizes, bf16",
+        "layers": d["num_hidden_layers"], "layers_full": full_layers, "prompt_tokens": st.prompt_tokens,
+        "prefill_ms": round(st.prefill_ms, 2), "prefill_tokens_per_s": round(st.prompt_tokens / st.prefill_ms * 1e3, 1),
+        "decode_steps": st.decode_steps, "decode_ms_per_step": round(st.decode_ms / st.decode_steps, 4),
+        "decode_tokens_per_s": round(64 * st.decode_steps / st.decode_ms * 1e3, 1), "batches": st.batches,
+        "bounded_waits_given_up": eng.rt.k.gemm_tc_status()}))
+    return 0
+
+
 def profile(args) -> int:
     """A small case for ncu: the engine at the bench's layer sizes with ``--layers``
     layers; the wanted phase runs eagerly (no graph) between cudaProfilerStart and
@@ -318,6 +347,8 @@ def main() -> int:
     ap.add_argument("--point-steps", type=int, default=64)
     ap.add_argument("--no-points", action="store_true")
     ap.add_argument("--profile", choices=["decode", "prefill"], help="run a small case for ncu and exit")
+    ap.add_argument("--unequal", action="store_true",
+                    help="instead of the headline run: 64 prompts of unequal lengths and 256 decode steps through generate")
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN)
     ap.add_argument("--pdl", action="store_true", help="decode kernels with programmatic dependent launch")
     ap.add_argument("--sample", action="store_true",
@@ -335,6 +366,8 @@ def main() -> int:
         return 2
     if args.profile:
         return profile(args)
+    if args.unequal:
+        return unequal(args)
     args.warmup = max(3, args.warmup)
     print(json.dumps(run(args)))
     return 0

@@ -384,6 +384,24 @@ def test_linear_bf16_tcgen05_few_tokens_many_tiles(K, T, N, K_):
     assert K.gemm_tc_status() == 0
 
 
+@pytest.mark.parametrize("form", ["single", "pair"])
+def test_linear_bf16_tcgen05_groups_of_token_tiles(K, form):
+    """A product whose token tiles are walked in more than one group (a group's activations
+    are sized to stay in L2: with K = 16384 that is 8 tiles of 256 tokens, 16 of 128), the
+    last group not full."""
+    T, N, K_ = 2400, 300, 16384
+    x, w = rnd((T, K_), torch.bfloat16, 78), rnd((N, K_), torch.bfloat16, 79, 0.02)
+    want = (x.cuda().double() @ w.cuda().double().t()).cpu()
+    K.set_gemm_form(form, 0)
+    try:
+        got = torch.full((T, N), 7.0, dtype=torch.float32, device="cuda")
+        K.linear(got, x.cuda(), w.cuda(), impl="tc")
+    finally:
+        K.set_gemm_form(None, 0)
+    close(got, want, torch.float32, atol=2e-3, rtol=1e-3)
+    assert K.gemm_tc_status() == 0
+
+
 def test_linear_bf16_kernels_agree(K):
     """The three bf16 products give the same numbers up to the order of their sums."""
     x, w = rnd((16, 512), torch.bfloat16, 73), rnd((384, 512), torch.bfloat16, 74, 0.05)

@@ -241,11 +241,30 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 // the product warp already fills the other, and the TMA ring never stops between
 // tiles.  acc_full[b] / acc_empty[b] hand accumulator b back and forth.
 // ---------------------------------------------------------------------------
+// The order in which the persistent kernels walk the tiles of Y: token tiles fastest, so that the
+// blocks that run together share a tile of W; but in groups of `gm` token tiles, all output tiles
+// of a group before the next group, so that a group's activations (gm x BM x K) stay in L2 while
+// its output tiles are walked.  Without the groups a step of 65,000 tokens re-reads its 534 MB of
+// activations from DRAM for every output tile.
+__device__ __forceinline__ void tile_of(int tile, int m_tiles, int n_tiles, int gm, int& m, int& n) {
+    const int per_group = gm * n_tiles;
+    const int group = tile / per_group, r = tile - group * per_group;
+    const int m0 = group * gm, gm_here = min(gm, m_tiles - m0);
+    n = r / gm_here;
+    m = m0 + r - n * gm_here;
+}
+// token tiles per group: the group's activations take about 64 MB of the 126 MB L2
+static int tile_group(int bm, int K) {
+    const long long bytes = (long long)bm * K * 2;
+    const long long g = (64ll << 20) / (bytes > 0 ? bytes : 1);
+    return (int)(g < 4 ? 4 : g);
+}
+
 #define TCP_ACC 256          // tensor-memory columns between the two accumulators (an allocation is a power of two)
 template <int BN, int STAGES, int MODE>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                          void* __restrict__ Y, int T, int N, int K, int ldy) {
+                          void* __restrict__ Y, int T, int N, int K, int ldy, int gm) {
     constexpr unsigned A_BYTES = TC_BM * TC_BK * 2, B_BYTES = BN * TC_BK * 2;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -286,7 +305,9 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
             unsigned it = 0;            // k blocks issued so far, over all tiles
             bool ok = true;
             for (int tile = blockIdx.x; tile < tiles && ok; tile += gridDim.x) {
-                const int a0row = (tile % m_tiles) * TC_BM, b0row = (tile / m_tiles) * BN;
+                int tm, tn;
+                tile_of(tile, m_tiles, n_tiles, gm, tm, tn);
+                const int a0row = tm * TC_BM, b0row = tn * BN;
                 for (int kb = 0; kb < KB; ++kb, ++it) {
                     const int s = it % STAGES;
                     if (!mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1, abort_flag, 1)) { ok = false; break; }
@@ -333,7 +354,9 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
         unsigned local = 0;
         for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++local) {
             const unsigned buf = local & 1;
-            const int a0row = (tile % m_tiles) * TC_BM, b0row = (tile / m_tiles) * BN;
+            int tm, tn;
+            tile_of(tile, m_tiles, n_tiles, gm, tm, tn);
+            const int a0row = tm * TC_BM, b0row = tn * BN;
             const bool ok = mbar_wait(&acc_full[buf], (local >> 1) & 1, abort_flag, 3);
             tc_fence_after();
             if (!ok || *abort_flag) break;
@@ -374,7 +397,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
 template <int BN, int STAGES, int MODE>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                    void* __restrict__ Y, int T, int N, int K, int ldy) {
+                    void* __restrict__ Y, int T, int N, int K, int ldy, int gm) {
     constexpr unsigned A_BYTES = TC_BM * TC_BK * 2, B_BYTES = (BN / 2) * TC_BK * 2;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -418,8 +441,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             unsigned it = 0;
             bool ok = true;
             for (int tile = pair; tile < tiles && ok; tile += pairs) {
-                const int a0row = (tile % m_tiles) * TCQ_BM + rank * TC_BM;
-                const int b0row = (tile / m_tiles) * BN + rank * (BN / 2);
+                int tm, tn;
+                tile_of(tile, m_tiles, n_tiles, gm, tm, tn);
+                const int a0row = tm * TCQ_BM + rank * TC_BM;
+                const int b0row = tn * BN + rank * (BN / 2);
                 for (int kb = 0; kb < KB; ++kb, ++it) {
                     const int s = it % STAGES;
                     if (!mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1, abort_flag, 1)) { ok = false; break; }
@@ -467,7 +492,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         const unsigned empty0[2] = {cluster_addr(&acc_empty[0], 0), cluster_addr(&acc_empty[1], 0)};
         for (int tile = pair; tile < tiles; tile += pairs, ++local) {
             const unsigned buf = local & 1;
-            const int a0row = (tile % m_tiles) * TCQ_BM + rank * TC_BM, b0row = (tile / m_tiles) * BN;
+            int tm, tn;
+            tile_of(tile, m_tiles, n_tiles, gm, tm, tn);
+            const int a0row = tm * TCQ_BM + rank * TC_BM, b0row = tn * BN;
             const bool ok = mbar_wait(&acc_full[buf], (local >> 1) & 1, abort_flag, 3);
             tc_fence_after();
             if (!ok || *abort_flag) break;
@@ -843,7 +870,7 @@ static int launch_tc_persistent(void* Y, const void* X, const void* W, int T, in
             }                                                                                              \
             attr_set = true;                                                                               \
         }                                                                                                  \
-        zlm_launch(kern, dim3(blocks), dim3(TC_THREADS), smem, st, mx, mw, Y, T, N, K, ldy);               \
+        zlm_launch(kern, dim3(blocks), dim3(TC_THREADS), smem, st, mx, mw, Y, T, N, K, ldy, tile_group(TC_BM, K)); \
     }
     if (mode == 0) ZLM_TCP_LAUNCH(0)
     else if (mode == 1) ZLM_TCP_LAUNCH(1)
@@ -876,7 +903,7 @@ static int launch_tc_pair(void* Y, const void* X, const void* W, int T, int N, i
             }                                                                                              \
             attr_set = true;                                                                               \
         }                                                                                                  \
-        zlm_launch(kern, dim3(2 * pairs), dim3(TC_THREADS), smem, st, mx, mw, Y, T, N, K, ldy);            \
+        zlm_launch(kern, dim3(2 * pairs), dim3(TC_THREADS), smem, st, mx, mw, Y, T, N, K, ldy, tile_group(TCQ_BM, K)); \
     }
     if (mode == 0) ZLM_TCQ_LAUNCH(0)
     else if (mode == 1) ZLM_TCQ_LAUNCH(1)
