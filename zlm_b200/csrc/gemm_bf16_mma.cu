@@ -126,7 +126,7 @@ gemm_bf16_mma_kernel(void* __restrict__ Y, const __nv_bfloat16* __restrict__ X,
     cp_async_wait<0>();
 
     const int g = lane >> 2, q = lane & 3;
-    if (MODE == 3) {
+    if constexpr (MODE == 3) {
         // n-tiles come in pairs: 8 gate channels, then the 8 matching up channels
 #pragma unroll
         for (int i = 0; i < MT; ++i)
@@ -146,8 +146,7 @@ gemm_bf16_mma_kernel(void* __restrict__ Y, const __nv_bfloat16* __restrict__ X,
                     }
                 }
             }
-        return;
-    }
+    } else {
 #pragma unroll
     for (int i = 0; i < MT; ++i) {
 #pragma unroll
@@ -161,6 +160,7 @@ gemm_bf16_mma_kernel(void* __restrict__ Y, const __nv_bfloat16* __restrict__ X,
                 if (n + 1 < N) store_out<MODE>(Y, (size_t)m * ldy + n + 1, acc[i][j][half * 2 + 1]);
             }
         }
+    }
     }
 }
 

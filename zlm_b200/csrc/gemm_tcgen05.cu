@@ -81,12 +81,47 @@ __device__ __forceinline__ void store_row16(const float* v, void* Y, int row, in
 #undef ZLM_PK
 }
 
+// this thread's output `row`, tokens t0 .. t0+15, in the wanted mode; every lane of the warp calls it
+template <int MODE>
+__device__ __forceinline__ void store_swapped16(const float* v, void* Y, int row, int t0, int T, int N, int ldy, int lane) {
+    if (MODE == 3) {
+        // lanes 0-7 and 16-23 hold gate channels, lanes 8-15 and 24-31 the matching up
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            const float u = __shfl_down_sync(0xffffffffu, v[i], 8);
+            if ((lane & 8) == 0 && row < N && t0 + i < T) {
+                const int ch = (row >> 4) * 8 + (row & 7);
+                ((__nv_bfloat16*)Y)[(size_t)(t0 + i) * ldy + ch] = __float2bfloat16_rn(silu_mul(v[i], u));
+            }
+        }
+        return;
+    }
+    if (row >= N) return;
+    if (MODE == 1) {
+        float old[16];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) old[i] = t0 + i < T ? __ldcg((const float*)Y + (size_t)(t0 + i) * ldy + row) : 0.f;
+#pragma unroll
+        for (int i = 0; i < 16; ++i)
+            if (t0 + i < T) ((float*)Y)[(size_t)(t0 + i) * ldy + row] = old[i] + v[i];
+    } else {
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            if (t0 + i >= T) break;
+            const size_t off = (size_t)(t0 + i) * ldy + row;
+            if (MODE == 0) ((__nv_bfloat16*)Y)[off] = __float2bfloat16_rn(v[i]);
+            else ((float*)Y)[off] = v[i];
+        }
+    }
+}
+
 // MODE 0: Y bf16 = acc; MODE 1: Y fp32 += acc; MODE 2: Y fp32 = acc;
 // MODE 3: the outputs come in groups of 16 = 8 gate + 8 up channels; Y bf16 [T, N/2] = silu(gate) * up;
-// MODE 4 (swapped form only): the block sums its share of K (blockIdx.z of gridDim.z) and stores the
-// fp32 partial product to Y [gridDim.z][T][N]; zlm_gemm_tc adds the shares up in a second kernel.
-// SWAP false: first operand = X (rows are tokens), second = W; true: first = W, second = X.
-template <int BN, int STAGES, bool SWAP, int MODE>
+// MODE 4: the block sums its share of K (blockIdx.z of gridDim.z) and stores the fp32 partial
+// product to Y [gridDim.z][T][N]; zlm_gemm_tc adds the shares up in a second kernel.
+// The few-token form as stand-alone blocks: the first operand is W (128 outputs), the second X
+// (a tile of BN tokens); one block per tile and share of K.
+template <int BN, int STAGES, int MODE>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                void* __restrict__ Y, int T, int N, int K, int ldy) {
@@ -182,45 +217,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 #pragma unroll
                     for (int i = 0; i < 16; ++i) v[i] = 0.f;     // a share of K with nothing in it
                 }
-                if (!SWAP) {
-                    store_row16<MODE>(v, Y, arow, b0row + c, T, N, ldy);
-                } else {
-                    // this thread: output arow, tokens b0row + c .. + 15; a warp's lanes are 32
-                    // neighbouring outputs, so every token's store is one coalesced line
-                    const int t0 = b0row + c;
-                    if (MODE == 3) {
-                        // lanes 0-7 and 16-23 hold gate channels, lanes 8-15 and 24-31 the matching up
+                // this thread: output arow, tokens b0row + c .. + 15; a warp's lanes are 32
+                // neighbouring outputs, so every token's store is one coalesced line
+                const int t0 = b0row + c;
+                if constexpr (MODE == 4) {
+                    if (arow < N) {
 #pragma unroll
-                        for (int i = 0; i < 16; ++i) {
-                            const float u = __shfl_down_sync(0xffffffffu, v[i], 8);
-                            if ((lane & 8) == 0 && arow + 8 < N + 8 && arow < N && t0 + i < T) {
-                                const int ch = (arow >> 4) * 8 + (arow & 7);
-                                ((__nv_bfloat16*)Y)[(size_t)(t0 + i) * ldy + ch] = __float2bfloat16_rn(silu_mul(v[i], u));
-                            }
-                        }
-                    } else {
-                        if (arow >= N) continue;
-                        if (MODE == 1) {
-                            // all sixteen old values first: one latency, not sixteen (the compiler may not
-                            // move a load above a store that could be to the same place)
-                            float old[16];
-#pragma unroll
-                            for (int i = 0; i < 16; ++i)
-                                old[i] = t0 + i < T ? __ldcg((const float*)Y + (size_t)(t0 + i) * ldy + arow) : 0.f;
-#pragma unroll
-                            for (int i = 0; i < 16; ++i)
-                                if (t0 + i < T) ((float*)Y)[(size_t)(t0 + i) * ldy + arow] = old[i] + v[i];
-                        } else {
-#pragma unroll
-                            for (int i = 0; i < 16; ++i) {
-                                if (t0 + i >= T) break;
-                                const size_t off = (size_t)(t0 + i) * ldy + arow;
-                                if (MODE == 0) ((__nv_bfloat16*)Y)[off] = __float2bfloat16_rn(v[i]);
-                                else if (MODE == 2) ((float*)Y)[off] = v[i];
-                                else ((float*)Y)[((size_t)blockIdx.z * T + t0 + i) * N + arow] = v[i];
-                            }
-                        }
+                        for (int i = 0; i < 16; ++i)
+                            if (t0 + i < T) ((float*)Y)[((size_t)blockIdx.z * T + t0 + i) * N + arow] = v[i];
                     }
+                } else {
+                    store_swapped16<MODE>(v, Y, arow, t0, T, N, ldy, lane);
                 }
             }
         }
@@ -533,40 +540,6 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 // item that finishes a tile last, was built and gave the same bits; under the load of the weight
 // stream its reads of the shares took several times as long as the whole second kernel does.)
 // ---------------------------------------------------------------------------
-// this thread's output `row`, tokens t0 .. t0+15, in the wanted mode; every lane of the warp calls it
-template <int MODE>
-__device__ __forceinline__ void store_swapped16(const float* v, void* Y, int row, int t0, int T, int N, int ldy, int lane) {
-    if (MODE == 3) {
-        // lanes 0-7 and 16-23 hold gate channels, lanes 8-15 and 24-31 the matching up
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-            const float u = __shfl_down_sync(0xffffffffu, v[i], 8);
-            if ((lane & 8) == 0 && row < N && t0 + i < T) {
-                const int ch = (row >> 4) * 8 + (row & 7);
-                ((__nv_bfloat16*)Y)[(size_t)(t0 + i) * ldy + ch] = __float2bfloat16_rn(silu_mul(v[i], u));
-            }
-        }
-        return;
-    }
-    if (row >= N) return;
-    if (MODE == 1) {
-        float old[16];
-#pragma unroll
-        for (int i = 0; i < 16; ++i) old[i] = t0 + i < T ? __ldcg((const float*)Y + (size_t)(t0 + i) * ldy + row) : 0.f;
-#pragma unroll
-        for (int i = 0; i < 16; ++i)
-            if (t0 + i < T) ((float*)Y)[(size_t)(t0 + i) * ldy + row] = old[i] + v[i];
-    } else {
-#pragma unroll
-        for (int i = 0; i < 16; ++i) {
-            if (t0 + i >= T) break;
-            const size_t off = (size_t)(t0 + i) * ldy + row;
-            if (MODE == 0) ((__nv_bfloat16*)Y)[off] = __float2bfloat16_rn(v[i]);
-            else ((float*)Y)[off] = v[i];
-        }
-    }
-}
-
 template <int BN, int STAGES, int MODE>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_few_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
@@ -797,23 +770,22 @@ static int make_map(CUtensorMap* m, const void* ptr, int rows, int K, int ld, in
     return zlm_make_map_2d(m, ptr, rows, K, ld, box_rows, TC_BK);
 }
 
-template <int BN, int STAGES, bool SWAP>
+template <int BN, int STAGES>
 static int launch_tc(void* Y, const void* X, const void* W, int T, int N, int K, int ldx, int ldy, int mode,
                      int ksplit, float* scratch, cudaStream_t st) {
     CUtensorMap mx, mw;
-    int rc = make_map(&mx, X, T, K, ldx, SWAP ? BN : TC_BM);
+    int rc = make_map(&mx, X, T, K, ldx, BN);
     if (rc) return rc;
-    rc = make_map(&mw, W, N, K, K, SWAP ? TC_BM : BN);
+    rc = make_map(&mw, W, N, K, K, TC_BM);
     if (rc) return rc;
     const size_t smem = (size_t)STAGES * (TC_BM + BN) * TC_BK * 2 + 1024 + 256;
-    dim3 grid(SWAP ? (N + TC_BM - 1) / TC_BM : (T + TC_BM - 1) / TC_BM, SWAP ? (T + BN - 1) / BN : (N + BN - 1) / BN,
-              ksplit);
+    dim3 grid((N + TC_BM - 1) / TC_BM, (T + BN - 1) / BN, ksplit);
     ZLM_REQUIRE(grid.y <= 65535, "gemm_tc: the product is too large (T=%d N=%d)", T, N);
     const int kmode = ksplit > 1 ? 4 : mode;
     void* dst = ksplit > 1 ? (void*)scratch : Y;
 #define ZLM_TC_LAUNCH(M)                                                                                   \
     {                                                                                                      \
-        auto kern = gemm_tc_kernel<BN, STAGES, SWAP, M>;                                                   \
+        auto kern = gemm_tc_kernel<BN, STAGES, M>;                                                         \
         static bool attr_set = false;                                                                      \
         if (!attr_set) {                                                                                   \
             cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
@@ -823,14 +795,13 @@ static int launch_tc(void* Y, const void* X, const void* W, int T, int N, int K,
             }                                                                                              \
             attr_set = true;                                                                               \
         }                                                                                                  \
-        if (SWAP) zlm_launch(kern, grid, dim3(TC_THREADS), smem, st, mw, mx, dst, T, N, K, ldy);           \
-        else zlm_launch(kern, grid, dim3(TC_THREADS), smem, st, mx, mw, dst, T, N, K, ldy);                \
+        zlm_launch(kern, grid, dim3(TC_THREADS), smem, st, mw, mx, dst, T, N, K, ldy);                     \
     }
     if (kmode == 0) ZLM_TC_LAUNCH(0)
     else if (kmode == 1) ZLM_TC_LAUNCH(1)
     else if (kmode == 2) ZLM_TC_LAUNCH(2)
     else if (kmode == 3) ZLM_TC_LAUNCH(3)
-    else if (SWAP) ZLM_TC_LAUNCH(4)
+    else ZLM_TC_LAUNCH(4)
 #undef ZLM_TC_LAUNCH
     rc = zlm_check_launch("gemm_tc");
     if (rc || ksplit <= 1) return rc;
@@ -1012,9 +983,9 @@ extern "C" int zlm_gemm_tc(void* Y, const void* X, const void* W, int T, int N, 
         if (plan.whole + (tiles - plan.whole) * plan.ks <= sm_count()) {
             // one round of blocks: nothing for a persistent block to overlap, and the stand-alone
             // blocks are a microsecond or two faster there (here all tiles are cut alike)
-            if (T <= 32) return launch_tc<32, 8, true>(Y, X, W, T, N, K, ldx, ldy, mode, plan.ks, scratch, st);
-            if (T <= 64) return launch_tc<64, 8, true>(Y, X, W, T, N, K, ldx, ldy, mode, plan.ks, scratch, st);
-            return launch_tc<128, 6, true>(Y, X, W, T, N, K, ldx, ldy, mode, plan.ks, scratch, st);
+            if (T <= 32) return launch_tc<32, 8>(Y, X, W, T, N, K, ldx, ldy, mode, plan.ks, scratch, st);
+            if (T <= 64) return launch_tc<64, 8>(Y, X, W, T, N, K, ldx, ldy, mode, plan.ks, scratch, st);
+            return launch_tc<128, 6>(Y, X, W, T, N, K, ldx, ldy, mode, plan.ks, scratch, st);
         }
         if (T <= 32) return launch_tc_few<32, 8>(Y, X, W, T, N, K, ldx, ldy, mode, plan, scratch, st);
         if (T <= 64) return launch_tc_few<64, 8>(Y, X, W, T, N, K, ldx, ldy, mode, plan, scratch, st);

@@ -148,7 +148,7 @@ gemv_bf16_kernel(void* __restrict__ Y, const __nv_bfloat16* __restrict__ X,
         red[warp][j][g + 8][2 * q + 1] = acc[j][3];
     }
     __syncthreads();
-    if (MODE == 3) {
+    if constexpr (MODE == 3) {
         for (int idx = tid; idx < NT * 8 * 8; idx += GEMV_THREADS) {
             const int j = idx / 64, rem = idx % 64;
             const int tok = j * 8 + rem / 8, row = rem % 8;
@@ -161,8 +161,7 @@ gemv_bf16_kernel(void* __restrict__ Y, const __nv_bfloat16* __restrict__ X,
             }
             ((__nv_bfloat16*)Y)[(size_t)tok * ldy + n0 / 2 + row] = __float2bfloat16_rn((sg / (1.0f + expf(-sg))) * su);
         }
-        return;
-    }
+    } else {
     for (int idx = tid; idx < NT * GEMV_ROWS * 8; idx += GEMV_THREADS) {
         const int j = idx / (GEMV_ROWS * 8), rem = idx % (GEMV_ROWS * 8);
         const int tok = j * 8 + rem / GEMV_ROWS, row = rem % GEMV_ROWS;   // rows fastest: coalesced stores
@@ -175,6 +174,7 @@ gemv_bf16_kernel(void* __restrict__ Y, const __nv_bfloat16* __restrict__ X,
         if (MODE == 0) ((__nv_bfloat16*)Y)[o] = __float2bfloat16_rn(s);
         else if (MODE == 1) ((float*)Y)[o] += s;
         else ((float*)Y)[o] = s;
+    }
     }
 }
 
