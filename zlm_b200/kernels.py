@@ -172,10 +172,13 @@ class CudaKernels:
 
     def _bf16_product(self, out, x, w, T, N, K, ldx, ldy, mode, impl) -> None:
         if impl is None:
-            # measured at Qwen3-8B sizes: the register-fragment GEMV wins up to 8 tokens, the
-            # swapped tcgen05 form from 9 on
+            # measured at Qwen3-8B sizes: the register-fragment GEMV wins up to 16 tokens (a layer's
+            # four products at 9 / 16 tokens: 78 / 84 us against 88 / 90 us), except for the head,
+            # whose 1,187 tiles the persistent tcgen05 form streams faster from 9 tokens on
+            # (191 against 197 to 216 us); from 17 tokens on the tcgen05 forms
             tc_ok = self.lib.zlm_gemm_tc_supported(T, N, K, ldx)
-            impl = "gemv" if (T <= 8 or (T <= 16 and not tc_ok)) else ("tc" if tc_ok else "mma")
+            small = T <= 8 or (T <= 16 and N < 65536)
+            impl = "gemv" if (small or (T <= 16 and not tc_ok)) else ("tc" if tc_ok else "mma")
         if impl == "tc":
             ks = self.lib.zlm_gemm_tc_ksplit(T, N, K)
             scratch = self.scratch("gemm_tc.partials", ks * T * N, torch.float32, out.device) if ks > 1 else None
