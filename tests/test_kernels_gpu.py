@@ -108,6 +108,33 @@ def test_linear_bf16(K, T, N, K_):
     close(acc, base.double() + want, torch.float32, atol=1e-3, rtol=1e-3)
 
 
+@pytest.mark.parametrize("T", [1, 7, 8, 13, 16])
+@pytest.mark.parametrize("K_,seg", [(1024, 128), (2048, 256), (3072, 384), (5120, 640), (7168, 128), (4096, 512),
+                                    (12288, 512), (1000, 512), (4104, 512)])
+def test_linear_bf16_gemv_segments(K, T, K_, seg):
+    """The weight-streaming product at every width of a warp's share of K (chosen so that K
+    spreads evenly over the warps; 512 where K is a multiple of 4096 or ragged), one and two
+    token tiles, a ragged number of outputs, all output modes and the fused gate/up epilogue."""
+    from zlm_b200.kernels import interleave_gate_up
+    assert K.lib.zlm_gemv_segment(K_) == seg
+    N = 208 + 9
+    x, w = rnd((T, K_), torch.bfloat16, 13), rnd((N, K_), torch.bfloat16, 14, 0.03)
+    want = x.double() @ w.double().t()
+    for out_dtype in (torch.bfloat16, torch.float32):
+        got = torch.full((T, N), 7.0, dtype=out_dtype, device="cuda")
+        K.linear(got, x.cuda(), w.cuda(), impl="gemv")
+        close(got, want, out_dtype, atol=1e-3 if out_dtype == torch.float32 else 3e-2, rtol=1e-2)
+    base = rnd((T, N), torch.float32, 15)
+    acc = base.clone().cuda()
+    K.linear(acc, x.cuda(), w.cuda(), accumulate=True, impl="gemv")
+    close(acc, base.double() + want, torch.float32, atol=1e-3, rtol=1e-3)
+    gate, up = w[:104], w[104:208]
+    g, u = x.double() @ gate.double().t(), x.double() @ up.double().t()
+    got = torch.full((T, 104), 7.0, dtype=torch.bfloat16, device="cuda")
+    K.linear_swiglu(got, x.cuda(), interleave_gate_up(gate.cuda(), up.cuda()), impl="gemv")
+    close(got, (g / (1 + torch.exp(-g))) * u, torch.bfloat16, atol=3e-2, rtol=3e-2)
+
+
 def test_linear_bf16_refuses_odd_inner_size(K):
     from zlm_b200.kernels import KernelError
     x, w = rnd((4, 36), torch.bfloat16, 1).cuda(), rnd((8, 36), torch.bfloat16, 2).cuda()
