@@ -133,18 +133,21 @@ def run(args) -> dict:
     cfg = config_from_dict(d)
     B = args.batch
     steps, warmup = args.steps, args.warmup
-    big = 0 if args.no_points else 64
-    room = PROMPT_LEN + max(steps + warmup, args.point_steps + warmup) + 64
-    max_tokens = max(B * CONTEXT, big * room)
     torch.cuda.set_device(0)
-    eng = Engine.from_random(cfg, seed=0, dtype="bfloat16", device="cuda:0", max_tokens=max_tokens,
-                             max_batch=max(B, big, 1), max_seq_len=CONTEXT,
-                             max_step_tokens=max(B, 8) * PROMPT_LEN)
     greedy = SamplingParams()
-    if args.pdl:
-        eng.decoder.use_pdl = True
-    if args.decode == "stream":
-        eng.decoder.use_stream = eng.decoder.can_stream
+
+    def make_engine(batch, tokens):
+        # the headline numbers come from an engine whose cache is sized for the headline
+        # configuration (batch x context); the batch-64 point gets an engine of its own
+        e = Engine.from_random(cfg, seed=0, dtype="bfloat16", device="cuda:0", max_tokens=tokens,
+                               max_batch=batch, max_seq_len=CONTEXT, max_step_tokens=max(B, 8) * PROMPT_LEN)
+        if args.pdl or args.no_pdl:
+            e.decoder.use_pdl = bool(args.pdl)
+        if args.decode == "stream":
+            e.decoder.use_stream = e.decoder.can_stream
+        return e
+
+    eng = make_engine(max(B, 1), B * CONTEXT)
     g = torch.Generator().manual_seed(0)
     per_layer, weight_bytes, kv_per_tok = model_numbers(cfg, args.layers)
     k = eng.rt.k
@@ -231,6 +234,11 @@ def run(args) -> dict:
     points = {}
     if not args.no_points:
         for b in (1, 64):
+            if b > eng.max_batch or b * (PROMPT_LEN + args.point_steps + warmup + 64) > eng.max_tokens:
+                del eng, k
+                torch.cuda.empty_cache()
+                eng = make_engine(b, b * (PROMPT_LEN + args.point_steps + warmup + 64))
+                k = eng.rt.k
             slots, first = prefill(prompts(b))
             pm, _, _ = timed_decode(slots, first, warmup, args.point_steps)
             points[f"decode_b{b}"] = round(b * args.point_steps / pm * 1e3, 1)
@@ -350,7 +358,9 @@ def main() -> int:
     ap.add_argument("--unequal", action="store_true",
                     help="instead of the headline run: 64 prompts of unequal lengths and 256 decode steps through generate")
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN)
-    ap.add_argument("--pdl", action="store_true", help="decode kernels with programmatic dependent launch")
+    ap.add_argument("--pdl", action="store_true",
+                    help="decode kernels with programmatic dependent launch at every batch size (default: up to 16 rows)")
+    ap.add_argument("--no-pdl", action="store_true", help="decode kernels in plain stream order")
     ap.add_argument("--sample", action="store_true",
                     help="with --profile decode: temperature 0.8, top-k 40, top-p 0.9 instead of greedy")
     ap.add_argument("--decode", choices=["graph", "stream"], default="graph",

@@ -43,10 +43,13 @@ class DecodeRunner:
         self.can_stream = bool(cuda and engine.dtype == torch.bfloat16 and engine.model.kernels_only
                                and self.stream_blocks > 0)
         self.use_stream = bool(use_stream) and self.can_stream
-        # programmatic dependent launch between the step's kernels: off.  Measured at batch 8,
-        # Qwen3-8B sizes: 5.32 ms a step with early triggers and weight prefetch before the
-        # wait, 4.46 ms with late triggers, 4.49 ms in plain stream order.
-        self.use_pdl = False
+        # Programmatic dependent launch between the step's kernels (a kernel's blocks may be
+        # scheduled while the kernel before it drains; each waits before it reads what that one
+        # wrote): None = for steps of up to 16 rows.  Measured against plain stream order:
+        # Qwen3-8B sizes, batch 8: 2,074 -> 2,097 tokens/s, batch 1: 296 -> 299; 0.6B sizes,
+        # batch 8: 5,940 -> 6,100, batch 1: 964 -> 1,028; at batch 64 (one block per SM with
+        # nearly all its shared memory) 8,446 -> 8,475 and 16,450 -> 16,120: left off there.
+        self.use_pdl: Optional[bool] = None
         # blocks the decode attention cuts its work for: None lets each path take its own
         # (what runs at a time: 3 per SM stand-alone, 1 per SM in the persistent kernel)
         self.attention_blocks: Optional[int] = None
@@ -138,8 +141,11 @@ class DecodeRunner:
         return buf[:R].tolist()
 
     # ------------------------------------------------------------------ device work
+    def _pdl(self, R: int) -> bool:
+        return self.use_pdl if self.use_pdl is not None else R <= 16
+
     def _device_work(self, ctx, R: int, params: SamplingParams) -> None:
-        if self.use_pdl:
+        if self._pdl(R):
             self.e.rt.k.set_pdl(True)
             try:
                 self._device_work_inner(ctx, R, params)
@@ -218,7 +224,7 @@ class DecodeRunner:
 
     def _replay(self, ctx, R: int, params: SamplingParams) -> None:
         e = self.e
-        key = (R, ctx.len_bucket, params)
+        key = (R, ctx.len_bucket, params, self._pdl(R))
         if self.graph_generation != self._generation():
             self.graphs.clear()
         g = self.graphs.get(key)
