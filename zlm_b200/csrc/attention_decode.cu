@@ -38,7 +38,7 @@ attention_decode_combine_kernel(__nv_bfloat16* __restrict__ out, int out_stride,
                                 int hd, int splits, int per, int window) {
     __shared__ float fs[COMB_MAX_SPLITS];
     __shared__ float red[32];
-    pdl_launch_dependents();
+    pdl_trigger();
     pdl_wait();
     attention_decode_combine_item(fs, red, threadIdx.x, GroupSync{0, COMB_THREADS}, blockIdx.x, blockIdx.y, out,
                                   out_stride, part_o, part_ml, token_pos, nq, hd, splits, per, window);

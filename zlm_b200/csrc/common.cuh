@@ -136,13 +136,17 @@ __device__ __forceinline__ float group_max(float v, float* red, int tid, const G
 // scratch); what it reads before the wait must be constant during the step (weights,
 // tables, the step's integer arrays, which are uploaded before the step's first
 // kernel).  Without the attribute the calls do nothing.
-// The trigger that lets the next kernel start is the implicit one at a block's end:
-// an explicit trigger at a kernel's start was measured slower (the next kernel's
-// blocks then sit on the SMs that this kernel's later waves need: 5.32 against
-// 4.46 ms a step at Qwen3-8B sizes), so pdl_launch_dependents() is kept only as the
-// place where such a trigger would go.
+// The trigger that lets the next kernel start is, for the kernels that stream weights or
+// the cache, the implicit one at a block's end: an explicit trigger at their start was
+// measured slower (the next kernel's blocks then sit on the SMs that this kernel's later
+// waves need: 5.32 against 4.46 ms a step at Qwen3-8B sizes), so there
+// pdl_launch_dependents() only marks the place.  The small kernels of a decode step (norm,
+// rotation and cache write, combine, embedding: a few blocks, all resident at once) trigger
+// at their start with pdl_trigger(): the product that follows them is launched, and has its
+// first weights on the way, while they run.
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ void pdl_launch_dependents() {}
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;\n" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
 
 int zlm_pdl_enabled();

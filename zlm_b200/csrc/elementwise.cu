@@ -38,7 +38,7 @@ extern "C" int zlm_page_tokens() { return ZLM_PAGE; }
 template <typename TW>
 __global__ void embed_kernel(float* __restrict__ out, const TW* __restrict__ table,
                              const int* __restrict__ ids, int H, int V) {
-    pdl_launch_dependents();
+    pdl_trigger();
     const int t = blockIdx.x;
     pdl_wait();                 // the ids may be what the previous step's sampler wrote
     embed_row(out + (size_t)t * H, table, ids[t], H, V, threadIdx.x, blockDim.x);
@@ -67,7 +67,7 @@ template <typename TO>
 __global__ void rmsnorm_kernel(TO* __restrict__ out, const float* __restrict__ x, VecW w,
                                const int* __restrict__ rows, int H, float eps) {
     __shared__ float red[32];
-    pdl_launch_dependents();
+    pdl_trigger();
     const int r = blockIdx.x;
     const int src = rows ? rows[r] : r;
     pdl_wait();

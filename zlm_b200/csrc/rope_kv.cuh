@@ -72,7 +72,7 @@ __device__ __forceinline__ void qk_norm_rope_write_item(
     float* sn = sm + ang;                 // [ang]
     float* bufs = sm + 2 * ang;           // [ROPE_WARPS][hd]
     const int lane = tid & 31, warp = tid >> 5;
-    if (PDL) pdl_launch_dependents();
+    if (PDL) pdl_trigger();
     const int pos = token_pos[t];
     for (int i = tid; i < ang; i += ROPE_WARPS * 32) {
         float s, c;
