@@ -13,6 +13,7 @@ reads to the measured copy bandwidth; ``points`` holds decode at batch 1 and 64.
 from __future__ import annotations
 
 import argparse
+import gc
 import json
 import os
 import statistics
@@ -236,6 +237,7 @@ def run(args) -> dict:
         for b in (1, 64):
             if b > eng.max_batch or b * (PROMPT_LEN + args.point_steps + warmup + 64) > eng.max_tokens:
                 del eng, k
+                gc.collect()                 # the engine and its decode runner refer to each other
                 torch.cuda.empty_cache()
                 eng = make_engine(b, b * (PROMPT_LEN + args.point_steps + warmup + 64))
                 k = eng.rt.k
