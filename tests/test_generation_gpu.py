@@ -114,6 +114,7 @@ def test_an_engine_dropped_earlier_does_not_disturb_a_later_capture(tmp_path):
     first = Engine.from_pretrained(folder, dtype="bfloat16", max_tokens=256, max_batch=2)
     want = first.generate(prompts, max_tokens=6)
     assert first.decoder.graphs
+    first.myself = first                 # a cycle: only the collector can free this engine now
     gc.collect()
     gc.disable()
     try:
@@ -132,6 +133,29 @@ def test_an_engine_dropped_earlier_does_not_disturb_a_later_capture(tmp_path):
     finally:
         gc.enable()
     assert seen and got.tokens == want.tokens
+
+
+def test_a_dropped_engine_is_freed_at_once(tmp_path):
+    """Nothing in an engine refers back to it strongly: when the last reference goes, its
+    weights, cache and graphs go with it, without waiting for the cycle collector."""
+    import gc
+    import weakref
+    from zlm_b200 import Engine
+    folder, cfg, _ = make_model(tmp_path, "B", seed=4)
+    gc.collect()
+    gc.disable()
+    try:
+        eng = Engine.from_pretrained(folder, dtype="bfloat16", max_tokens=256, max_batch=2)
+        eng.generate(random_prompts(cfg.vocab_size, [6, 3], seed=2), max_tokens=4)
+        assert eng.decoder.graphs
+        gone = weakref.ref(eng)
+        runner = eng.decoder
+        del eng
+        assert gone() is None
+        with pytest.raises(RuntimeError, match="gone"):
+            runner.step([0], [1], None)
+    finally:
+        gc.enable()
 
 
 def test_temperature_sampling_is_reproducible_and_batch_independent(tmp_path):

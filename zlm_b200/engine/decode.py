@@ -23,6 +23,7 @@ a run of steps needs no host round trip unless the caller wants the tokens.
 from __future__ import annotations
 
 import gc
+import weakref
 from typing import Dict, List, Optional, Sequence, Tuple
 
 import numpy as np
@@ -36,7 +37,9 @@ from .stream import NotStreamable, StepRecorder, StreamProgram, stream_blocks
 
 class DecodeRunner:
     def __init__(self, engine, use_graphs: Optional[bool] = None, use_stream: Optional[bool] = None):
-        self.e = engine
+        # the engine owns this runner: a weak reference back, so that dropping the engine frees
+        # its weights and cache at once instead of when the cycle collector next runs
+        self._engine = weakref.ref(engine)
         cuda = engine.device.type == "cuda"
         self.use_graphs = (cuda and engine.model.graph_safe) if use_graphs is None else use_graphs
         self.stream_blocks = stream_blocks(engine.rt.k) if cuda else 0
@@ -64,6 +67,13 @@ class DecodeRunner:
         self._flip = 0
         self.last_logits: Optional[torch.Tensor] = None
         self.launches_per_step = 0
+
+    @property
+    def e(self):
+        engine = self._engine()
+        if engine is None:
+            raise RuntimeError("the engine of this decode runner is gone")
+        return engine
 
     # ------------------------------------------------------------------ one step
     def step(self, slots: Sequence[int], tokens: Optional[Sequence[int]], params: SamplingParams,
