@@ -1,0 +1,49 @@
+"""The host-side choices of the kernel library that need no GPU: how the weight-streaming
+product spreads K over its warps, and into how many shares of K the few-token tcgen05
+product cuts the tiles that do not fill a round of the GPU.  The library loads without a
+GPU (it is compiled at the first call, a few seconds, if this checkout has not built it
+yet); without nvcc the tests are skipped."""
+import ctypes
+
+import pytest
+
+
+@pytest.fixture(scope="module")
+def lib():
+    from zlm_b200.csrc.build import find_nvcc, library_path
+    try:
+        find_nvcc()
+    except Exception as e:                          # no compiler here: nothing to test against
+        pytest.skip(f"nvcc is not available: {e}")
+    return ctypes.CDLL(library_path(build_if_needed=True, verbose=False))
+
+
+@pytest.mark.parametrize("K,seg", [(4096, 512), (8192, 512), (12288, 512),          # multiples of 4096: 512, the order
+                                   (1024, 128), (2048, 256), (3072, 384),            # the persistent kernel adds in
+                                   (5120, 640), (25600, 640), (6144, 384), (7168, 128),
+                                   (1000, 512), (520, 512), (4104, 512), (64, 512)])  # ragged: 512 and a tail
+def test_gemv_segment_spreads_k_evenly(lib, K, seg):
+    assert lib.zlm_gemv_segment(K) == seg
+    if K % 1024 == 0:
+        assert K % (8 * seg) == 0                   # whole chunks of 8 warps x seg columns: no warp idles
+
+
+@pytest.mark.parametrize("T,N,K,shares", [
+    (64, 6144, 4096, 3),        # 48 tiles: three shares fill 144 of 148 SMs
+    (64, 4096, 4096, 4),        # 32 tiles x 4
+    (64, 4096, 12288, 4),
+    (64, 24576, 4096, 3),       # 192 tiles: 148 in one piece, 44 x 3 shares
+    (64, 151936, 4096, 8),      # 1,187 tiles: 8 rounds in one piece, the last 3 tiles x 8
+    (64, 18944, 4096, 1),       # 148 tiles: exactly one round, nothing to cut
+    (300, 8000, 1024, 2),       # three token tiles per output tile; shares of at least 8 k blocks
+    (40, 4096, 264, 1),         # K too short to cut
+    (2048, 4096, 4096, 1),      # many tokens: the persistent forms, no shares
+])
+def test_few_token_shares_of_k(lib, T, N, K, shares):
+    assert lib.zlm_gemm_tc_ksplit(T, N, K) == shares
+
+
+def test_tcgen05_product_takes_what_tma_can_address(lib):
+    assert lib.zlm_gemm_tc_supported(64, 4096, 4096, 4096) == 1
+    assert lib.zlm_gemm_tc_supported(64, 4096, 4100, 4100) == 0      # rows of K elements must be 16-byte multiples
+    assert lib.zlm_gemm_tc_supported(64, 4096, 4096, 4100) == 0
