@@ -47,3 +47,30 @@ def test_tcgen05_product_takes_what_tma_can_address(lib):
     assert lib.zlm_gemm_tc_supported(64, 4096, 4096, 4096) == 1
     assert lib.zlm_gemm_tc_supported(64, 4096, 4100, 4100) == 0      # rows of K elements must be 16-byte multiples
     assert lib.zlm_gemm_tc_supported(64, 4096, 4096, 4100) == 0
+
+
+@pytest.mark.parametrize("T,N,K,width", [
+    (2048, 4096, 4096, 240),     # 144 tiles of 240 on 74 pairs: two full rounds (128 of 256: the second 73 % full)
+    (2048, 6144, 4096, 240),
+    (2048, 24576, 4096, 256),    # 768 tiles: 11 rounds either way, the wide tile reuses the activations more
+    (2048, 5120, 8192, 224),     # three rounds at every width: the narrowest of them
+    (2048, 1024, 2048, 128),     # 32 tiles of 256 would leave more than half of the pairs idle
+    (65143, 4096, 4096, 256),    # many rounds: the width hardly matters, so the widest
+    (300, 4096, 4096, 0),        # few tokens: the other forms
+])
+def test_many_token_tile_width(lib, T, N, K, width):
+    assert lib.zlm_gemm_tc_tile_width(T, N, K) == width
+
+
+@pytest.mark.parametrize("R,max_new,nq,nkv,heads", [
+    (1, 2048, 32, 8, 2),     # 256 blocks of two heads: enough for 148 SMs
+    (1, 2048, 16, 8, 1),     # two heads per block would be 128 blocks, the longest twice as long
+    (1, 8192, 16, 8, 2),     # long prompt: the spread work outweighs the longest block
+    (1, 2048, 64, 8, 2),
+    (1, 2048, 8, 8, 1),      # groups of one head
+    (1, 2048, 24, 8, 1),     # odd groups
+    (5, 300, 32, 8, 2),
+    (64, 2048, 16, 8, 2),    # many prompts: plenty of blocks
+])
+def test_prefill_attention_heads_per_block(lib, R, max_new, nq, nkv, heads):
+    assert lib.zlm_attention_prefill_tc_heads(R, max_new, nq, nkv) == heads

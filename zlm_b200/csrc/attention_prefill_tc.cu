@@ -322,6 +322,28 @@ extern "C" int zlm_attention_prefill_tc_supported(int nq, int nkv, int hd, int q
 // pool_rows: pages * 2 * nkv * 64 (all rows of the layer's pool, head size 128 each)
 static int g_fa_heads = 0;
 
+// Heads of a kv group per block.  Two heads can share a block (they share its keys and values,
+// and one head's softmax runs under the other's products: measured 1.46 times the throughput per
+// head), but the blocks are then half as many and the longest twice as long.  The step takes about
+// as long as the larger of its longest block (the last tile of the longest prompt) and its whole
+// work spread over the SMs; the form for which that is smaller runs (2,048 tokens, 16 heads over
+// 8: 40 us with one head per block, 50 with two; 32 over 8: 76 and 57).  Odd groups take one.
+extern "C" int zlm_attention_prefill_tc_heads(int R, int max_new, int nq, int nkv) {
+    if (nkv <= 0 || nq % nkv != 0 || (nq / nkv) % 2 != 0) return 1;
+    if (g_fa_heads) return g_fa_heads;
+    static int sms = 0;
+    if (!sms) {
+        int dev = 0;
+        if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+            sms = 148;
+    }
+    const int tiles = (max_new + FA_BM - 1) / FA_BM;
+    const double pairs_cost = 2.0 / 1.46;                                   // a block of two heads, per page, against one head
+    const double work = (double)R * tiles * (tiles + 1) / 2 / sms;          // tiles' pages summed, per SM and head
+    const double two = fmax(tiles * pairs_cost, work * (nq / 2) * pairs_cost), one = fmax((double)tiles, work * nq);
+    return two <= one ? 2 : 1;
+}
+
 extern "C" int zlm_attention_prefill_tc(void* out, int out_stride, const void* q, int q_stride, int T,
                                         const void* pool, long long pool_pages, const int* block_table,
                                         int table_stride, const int* cu_seqlens, const int* seq_slot,
@@ -340,26 +362,7 @@ extern "C" int zlm_attention_prefill_tc(void* out, int out_stride, const void* q
     rc = zlm_make_map_2d(&mkv, pool, pool_pages * 2 * nkv * ZLM_PAGE, hd, hd, ZLM_PAGE, 64);
     if (rc) return rc;
     const int tiles = (max_new + FA_BM - 1) / FA_BM;
-    // Two heads of a kv group can share a block (they share its keys and values, and one head's
-    // softmax runs under the other's products: measured 1.46 times the throughput per head), but
-    // the blocks are then half as many and the longest twice as long.  The step takes about as
-    // long as the larger of its longest block (the last tile of the longest prompt) and its whole
-    // work spread over the SMs; the form for which that is smaller runs (2,048 tokens, 16 heads
-    // over 8: 40 us with one head per block, 50 with two; 32 over 8: 76 and 57).
-    int hpc = 1;
-    if ((nq / nkv) % 2 == 0) {
-        static int sms = 0;
-        if (!sms) {
-            int dev = 0;
-            if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
-                sms = 148;
-        }
-        const double pairs_cost = 2.0 / 1.46;                                   // a block of two heads, per page, against one head
-        const double work = (double)R * tiles * (tiles + 1) / 2 / sms;          // tiles' pages summed, per SM and head
-        const double two = fmax(tiles * pairs_cost, work * (nq / 2) * pairs_cost), one = fmax((double)tiles, work * nq);
-        hpc = two <= one ? 2 : 1;
-        if (g_fa_heads) hpc = g_fa_heads;
-    }
+    const int hpc = zlm_attention_prefill_tc_heads(R, max_new, nq, nkv);
     ZLM_REQUIRE((long long)R * tiles * nq < 2147483647LL, "attention_prefill_tc: too many tiles");
     const size_t smem = (size_t)hpc * FA_BM * FA_HD * 2 + 2 * FA_STAGES * ZLM_PAGE * FA_HD * 2 +
                         (size_t)hpc * 2 * FA_BM * ZLM_PAGE * 2 + 1024 + 256;

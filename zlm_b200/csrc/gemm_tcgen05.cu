@@ -964,6 +964,29 @@ extern "C" int zlm_gemm_tc_ksplit(int T, int N, int K) {
     return few_plan(T, N, K).ks;
 }
 
+// The width of the many-token forms' tiles (0 for the few-token forms, up to 384 tokens).  Tiles run
+// in rounds of one per SM (or pair of SMs), and a round costs its width: N = 4096 at 2,048 tokens
+// is 128 tiles of 256 columns on 74 pairs (2 rounds, the second 73 % full) or 144 of 240 (2 rounds,
+// 97 % full).  A narrower tile re-reads the activations more often, so it has to win by more than
+// 5 % in rounds x width (measured at 2,048 tokens: N = 4096 and 6144 gain 2-3 % with 240 columns,
+// N = 24576 loses 3 % with 224 although it saves a round of 12).  128 columns (pairs only): half
+// the reuse of the activations per product, so only where the wider tiles would leave a third of
+// the pairs idle (N = 1024 at 2,048 tokens: 32 tiles on 74 pairs).
+extern "C" int zlm_gemm_tc_tile_width(int T, int N, int K) {
+    (void)K;
+    if (T <= 384) return 0;
+    if (g_tc_width) return g_tc_width;
+    const bool pairs = g_tc_form != 1;
+    const long long m_tiles = pairs ? (T + TCQ_BM - 1) / TCQ_BM : (T + TC_BM - 1) / TC_BM;
+    const long long slots = pairs ? sm_count() / 2 : sm_count();
+    auto cost = [&](int bn) { return ((m_tiles * ((N + bn - 1) / bn) + slots - 1) / slots) * bn; };
+    int best = 256;
+    for (int bn : {240, 224})
+        if (cost(bn) * 100 < cost(256) * 95 && cost(bn) < cost(best)) best = bn;
+    if (pairs && cost(128) * 100 < cost(best) * 70) best = 128;
+    return best;
+}
+
 // mode 0: Y bf16 = X W^T; mode 1: Y fp32 += X W^T; mode 2: Y fp32 = X W^T;
 // mode 3: Y bf16 [T, N/2] = silu(gate) * up, W's rows in groups of 8 gate + 8 up (N a multiple of 16).
 // scratch: zlm_gemm_tc_ksplit(T, N, K) * T * N floats if that number of shares is more than 1, else unused.
@@ -991,37 +1014,15 @@ extern "C" int zlm_gemm_tc(void* Y, const void* X, const void* W, int T, int N, 
         if (T <= 64) return launch_tc_few<64, 8>(Y, X, W, T, N, K, ldx, ldy, mode, plan, scratch, st);
         return launch_tc_few<128, 6>(Y, X, W, T, N, K, ldx, ldy, mode, plan, scratch, st);
     }
-    // The tile's width: tiles run in rounds of one per SM, and a round costs its width.  N = 4096 at
-    // 2,048 tokens is 256 tiles of 256 columns (2 rounds, the second 73 % full) or 288 of 240 (2 rounds,
-    // 97 % full).  A narrower tile re-reads the activations more often, so it has to win by more than
-    // 5 % in rounds x width (measured at 2,048 tokens: N = 4096 and 6144 gain 2-3 % with 240 columns,
-    // N = 24576 loses 3 % with 224 although it saves a round of 12).
+    const int width = zlm_gemm_tc_tile_width(T, N, K);
     if (g_tc_form != 1) {
-        const long long m2 = (T + TCQ_BM - 1) / TCQ_BM, pairs = sm_count() / 2;
-        auto cost2 = [&](int bn) { return ((m2 * ((N + bn - 1) / bn) + pairs - 1) / pairs) * bn; };
-        int best = 256;
-        for (int bn : {240, 224})
-            if (cost2(bn) * 100 < cost2(256) * 95 && cost2(bn) < cost2(best)) best = bn;
-        // 128 columns: half the reuse of the activations per product, so only where the wider tiles
-        // would leave a third of the pairs idle (N = 1024 at 2,048 tokens: 32 tiles on 74 pairs)
-        if (cost2(128) * 100 < cost2(best) * 70) best = 128;
-        if (g_tc_width) best = g_tc_width;
-        if (best == 128) return launch_tc_pair<128, 8>(Y, X, W, T, N, K, ldx, ldy, mode, st);
-        if (best == 240) return launch_tc_pair<240, 6>(Y, X, W, T, N, K, ldx, ldy, mode, st);
-        if (best == 224) return launch_tc_pair<224, 6>(Y, X, W, T, N, K, ldx, ldy, mode, st);
+        if (width == 128) return launch_tc_pair<128, 8>(Y, X, W, T, N, K, ldx, ldy, mode, st);
+        if (width == 240) return launch_tc_pair<240, 6>(Y, X, W, T, N, K, ldx, ldy, mode, st);
+        if (width == 224) return launch_tc_pair<224, 6>(Y, X, W, T, N, K, ldx, ldy, mode, st);
         return launch_tc_pair<256, 6>(Y, X, W, T, N, K, ldx, ldy, mode, st);
     }
-    const long long m_tiles = (T + TC_BM - 1) / TC_BM;
-    auto cost_of = [&](int bn) { return ((m_tiles * ((N + bn - 1) / bn) + sm_count() - 1) / sm_count()) * bn; };
-    int best = 256;
-    long long best_cost = cost_of(256);
-    for (int bn : {240, 224}) {
-        const long long cost = cost_of(bn);
-        if (cost * 100 < best_cost * 95 && cost < (best == 256 ? best_cost : cost_of(best))) best = bn;
-    }
-    if (g_tc_width) best = g_tc_width;
-    if (best == 240) return launch_tc_persistent<240, 4>(Y, X, W, T, N, K, ldx, ldy, mode, st);
-    if (best == 224) return launch_tc_persistent<224, 4>(Y, X, W, T, N, K, ldx, ldy, mode, st);
+    if (width == 240) return launch_tc_persistent<240, 4>(Y, X, W, T, N, K, ldx, ldy, mode, st);
+    if (width == 224) return launch_tc_persistent<224, 4>(Y, X, W, T, N, K, ldx, ldy, mode, st);
     return launch_tc_persistent<256, 4>(Y, X, W, T, N, K, ldx, ldy, mode, st);
 }
 
