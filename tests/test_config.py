@@ -94,3 +94,28 @@ def test_schedule_validation():
         replace(spec, schedule=(ScheduleEntry(5),)).validate()
     with pytest.raises(ConfigError, match="earlier entry"):
         replace(spec, schedule=(ScheduleEntry(0, cache_of=1), ScheduleEntry(1))).validate()
+
+
+def test_rope_parameters_object_is_read_and_what_it_may_hide_is_refused():
+    """A config.json from a newer writer carries the rotary base inside ``rope_parameters``
+    and no top-level ``rope_theta``: the base must come from there, not from the default."""
+    base = {k: v for k, v in TINY_A.items() if k != "rope_theta"}
+    moved = {**base, "rope_parameters": {"rope_theta": 10000.0, "rope_type": "default"}}
+    assert config_from_dict(moved).rope_theta == 10000.0
+    assert config_from_dict({**moved, "rope_theta": 10000}).rope_theta == 10000.0
+    assert config_from_dict({**base, "rope_parameters": {"rope_type": "default"}}).rope_theta == 1_000_000.0
+    assert config_from_dict({**TINY_A, "rope_parameters": {"rope_type": "default"}}).rope_theta == 10000.0
+    assert config_from_dict({**TINY_A, "rope_scaling": {"rope_type": "default"}}).rope_theta == 10000.0
+    with pytest.raises(ConfigError, match="differ"):
+        config_from_dict({**moved, "rope_theta": 1e6})
+    for bad in ({"rope_theta": 1e4, "rope_type": "yarn", "factor": 4.0},
+                {"rope_theta": 1e4, "rope_type": "linear"},
+                {"rope_theta": 1e4, "rope_type": "default", "factor": 2.0},
+                {"rope_theta": 1e4, "partial_rotary_factor": 0.5},
+                {"rope_theta": 1e4, "mrope_section": [1, 2]}):
+        with pytest.raises(ConfigError, match="rope_parameters"):
+            config_from_dict({**base, "rope_parameters": bad})
+    with pytest.raises(ConfigError, match="partial_rotary_factor"):
+        config_from_dict({**TINY_A, "partial_rotary_factor": 0.5})
+    with pytest.raises(ConfigError, match="must be an object"):
+        config_from_dict({**base, "rope_parameters": 3})

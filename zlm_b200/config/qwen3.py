@@ -21,6 +21,21 @@ from .spec import (ConfigError, LayerSpec, ModelSpec, PartSpec, ScheduleEntry,
 
 ARCHITECTURE = "Qwen3ForCausalLM"
 
+# keys that a ``rope_parameters`` / ``rope_scaling`` object may hold while still meaning
+# plain rotary; anything else (factor, beta_fast, mrope_section, ...) changes the angles
+_PLAIN_ROPE_KEYS = {"rope_theta", "rope_type", "type", "partial_rotary_factor"}
+
+
+def _is_plain_rope(p: Mapping[str, Any]) -> bool:
+    if not isinstance(p, Mapping):
+        return False
+    if any(k not in _PLAIN_ROPE_KEYS for k in p):
+        return False
+    kind = p.get("rope_type", p.get("type", "default"))
+    if kind not in (None, "default"):
+        return False
+    return p.get("partial_rotary_factor", 1.0) in (1, 1.0, None)
+
 
 @dataclass(frozen=True)
 class Qwen3Config:
@@ -54,7 +69,7 @@ class Qwen3Config:
         vocab = require(d, "vocab_size", int)
         max_pos = require(d, "max_position_embeddings", int)
         eps = optional(d, "rms_norm_eps", float, 1e-6)
-        theta = optional(d, "rope_theta", float, 1_000_000.0)
+        theta = cls._rope_theta(d)
         tied = optional(d, "tie_word_embeddings", bool, False)
 
         if heads % kv_heads != 0:
@@ -65,8 +80,11 @@ class Qwen3Config:
             raise ConfigError(f"config.json: head_dim={head_dim} must be even (rotary pairs)")
         if optional(d, "attention_bias", bool, False):
             raise ConfigError("config.json: attention_bias=true is not supported (Qwen3 dense has no bias)")
-        if d.get("rope_scaling") is not None:
+        scaling = d.get("rope_scaling")
+        if scaling is not None and not _is_plain_rope(scaling):
             raise ConfigError("config.json: rope_scaling is not supported (plain rotary only)")
+        if optional(d, "partial_rotary_factor", float, 1.0) != 1.0:
+            raise ConfigError("config.json: partial_rotary_factor must be 1 (the whole head is rotated)")
         act = optional(d, "hidden_act", str, "silu")
         if act != "silu":
             raise ConfigError(f"config.json: hidden_act='{act}' is not supported (silu only)")
@@ -92,6 +110,31 @@ class Qwen3Config:
 
         return cls(hidden, layers, heads, kv_heads, head_dim, inter, vocab, max_pos,
                    eps, theta, tied, windows, eos_ids)
+
+    @staticmethod
+    def _rope_theta(d: Mapping[str, Any]) -> float:
+        """The rotary base: the top-level ``rope_theta``, or ``rope_parameters.rope_theta``
+        where a newer writer of config.json has moved it (the two must agree if both are
+        there); default 1,000,000, float or integer
+        (src/architectures/impl/qwen3/config.zig:39-40).  ``rope_parameters`` may say
+        nothing but plain rotary: any other ``rope_type``, a ``factor`` or a partial
+        rotation is refused rather than ignored."""
+        top = optional(d, "rope_theta", float, None)
+        params = d.get("rope_parameters")
+        if params is None:
+            return 1_000_000.0 if top is None else top
+        if not isinstance(params, Mapping):
+            raise ConfigError(f"config.json: 'rope_parameters' must be an object, got {params!r}")
+        if not _is_plain_rope(params):
+            raise ConfigError(
+                f"config.json: rope_parameters={dict(params)!r} asks for scaled or partial rotary; "
+                "plain rotary only (rope_type 'default', no factor, partial_rotary_factor 1)")
+        inner = optional(params, "rope_theta", float, None)
+        if top is not None and inner is not None and top != inner:
+            raise ConfigError(f"config.json: rope_theta={top} and rope_parameters.rope_theta={inner} differ")
+        if inner is not None:
+            return inner
+        return 1_000_000.0 if top is None else top
 
     @staticmethod
     def _windows(d: Mapping[str, Any], layers: int) -> Tuple[int, ...]:
