@@ -74,7 +74,7 @@ class PlainKernels:
                 pool[page, 1, :, p % PAGE, :] = x[t, nq + nkv:].to(pool.dtype)
 
     def attention(self, out, q, pool, block_table, token_pos, token_slot, nq, nkv, hd, scale, window,
-                  plan=None):
+                  plan=None, len_bucket=None):
         T = q.shape[0]
         group = nq // nkv
         for t in range(T):

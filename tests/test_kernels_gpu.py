@@ -237,8 +237,8 @@ def test_argmax_ties_to_lowest_index(K):
 class FakePlan:
     """What the attention kernel wants to know about a step."""
 
-    def __init__(self, len_bucket):
-        self.is_decode, self.len_bucket = True, len_bucket
+    def __init__(self):
+        self.is_decode = True
         self.bufs = {}
 
     def scratch(self, name, shape, dtype):
@@ -269,9 +269,10 @@ def test_attention_decode_kernel(K, nq, nkv, hd, window, len_bucket):
     want = torch.empty(T, nq * hd, dtype=dt)
     PlainKernels().attention(want, q, pool, table, pos, slot, nq, nkv, hd, scale, window)
     got = torch.empty(T, nq * hd, dtype=dt, device="cuda")
-    plan = FakePlan(len_bucket)
-    K.attention(got, q.cuda(), pool.cuda(), table.cuda(), pos.cuda(), slot.cuda(), nq, nkv, hd, scale, window, plan)
-    assert (decode_splits(T, nkv, len_bucket)[0] > 1) == bool(plan.bufs)
+    plan = FakePlan()
+    K.attention(got, q.cuda(), pool.cuda(), table.cuda(), pos.cuda(), slot.cuda(), nq, nkv, hd, scale, window, plan,
+                len_bucket=len_bucket)
+    assert (decode_splits(T, nkv, len_bucket, K.sm_count * 3)[0] > 1) == bool(plan.bufs)
     close(got, want, dt, atol=3e-2, rtol=3e-2)
     vfar = pool[page, 1, nkv - 1, far % PAGE, :].float()
     assert (got[0, (nq - 1) * hd:].float().cpu() - vfar).abs().max() < 0.05 * vfar.abs().max() + 0.05
@@ -290,7 +291,6 @@ class PrefillPlan:
         self.cu_seqlens = torch.tensor(cu, dtype=torch.int32).cuda()
         self.seq_slot = torch.tensor(slots, dtype=torch.int32).cuda()
         self.seq_start = torch.tensor(starts, dtype=torch.int32).cuda()
-        self.len_bucket = 1
 
 
 @pytest.mark.parametrize("impl", ["mma", None, "tc1", "tc2"])

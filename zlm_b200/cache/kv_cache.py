@@ -32,12 +32,62 @@ def pages_for(tokens: int) -> int:
     return (tokens + PAGE_TOKENS - 1) // PAGE_TOKENS
 
 
+class TableStager:
+    """Carries new block-table entries to the GPU without making the host wait.
+
+    A copy from pageable memory blocks the host until the stream has drained, which
+    would stop a decode loop that queues steps ahead every time a row crosses a page
+    edge.  So the entries of one ``reserve`` are written into one of a few pinned
+    buffers and copied from there in stream order; a buffer is written again only
+    after the copies that read it have run (an event per buffer)."""
+
+    RING = 4
+
+    def __init__(self, capacity: int, device):
+        self.device = torch.device(device)
+        self.cuda = self.device.type == "cuda"
+        self.capacity = max(1, int(capacity))
+        self.bufs = [torch.zeros(self.capacity, dtype=torch.int32, pin_memory=self.cuda) for _ in range(self.RING)]
+        self.events: List[Optional["torch.cuda.Event"]] = [None] * self.RING
+        self.turn = 0
+        self.fill = 0
+        self.open = False
+
+    def begin(self) -> None:
+        self.turn = (self.turn + 1) % self.RING
+        ev = self.events[self.turn]
+        if ev is not None:
+            ev.synchronize()
+            self.events[self.turn] = None
+        self.fill = 0
+        self.open = True
+
+    def copy(self, dst: torch.Tensor, values: Sequence[int]) -> None:
+        """dst (a slice of a device table) = values."""
+        k = len(values)
+        if not self.open or self.fill + k > self.capacity:
+            dst.copy_(torch.tensor(values, dtype=torch.int32))      # no staging room: the plain, waiting way
+            return
+        src = self.bufs[self.turn][self.fill:self.fill + k]
+        src.numpy()[:] = values
+        self.fill += k
+        dst.copy_(src, non_blocking=True)
+
+    def end(self) -> None:
+        if self.open and self.fill and self.cuda:
+            ev = torch.cuda.Event()
+            ev.record()
+            self.events[self.turn] = ev
+        self.open = False
+
+
 class CacheGroup:
     """Storage of the schedule entries that share one CacheRequest."""
 
     def __init__(self, request: CacheRequest, entries: List[int], num_pages: int, num_slots: int,
-                 max_pages_per_slot: int, dtype: torch.dtype, device):
+                 max_pages_per_slot: int, dtype: torch.dtype, device, stager: Optional[TableStager] = None):
         self.request = request
+        self.stager = stager
         self.entries = entries
         self.num_pages = num_pages
         self.pages = FreeList(num_pages, "page")
@@ -65,7 +115,10 @@ class CacheGroup:
         new = self.pages.take(need)
         a = len(have)
         have.extend(new)
-        self.block_table[slot, a:a + need] = torch.tensor(new, dtype=torch.int32)
+        if self.stager is not None:
+            self.stager.copy(self.block_table[slot, a:a + need], new)
+        else:
+            self.block_table[slot, a:a + need] = torch.tensor(new, dtype=torch.int32)
 
     def trim(self, slot: int, length: int) -> None:
         """Window groups: give back the pages whose keys can no longer be read.  The
@@ -105,7 +158,9 @@ class KVCache:
             raise ValueError("the cache needs room for at least one page of tokens")
         self.max_slots = int(max_slots)
         self.max_seq_len = int(max_seq_len)
-        max_pages_per_slot = min(self.num_pages, pages_for(self.max_seq_len))
+        # a table row has a place for every page of the longest sequence: a window group gives
+        # pages back as it goes, so its sequences may be longer than the pool
+        max_pages_per_slot = pages_for(self.max_seq_len)
         self.slots = FreeList(self.max_slots, "slot")
         self.lengths: Dict[int, int] = {}
 
@@ -114,8 +169,10 @@ class KVCache:
         for i, (e, r) in enumerate(zip(schedule, requests)):
             if r is not None and e.cache_of is None:
                 by_req.setdefault(r, []).append(i)
+        self.table_stager = TableStager(self.num_pages * max(1, len(by_req)), device)
         self.groups: List[CacheGroup] = [
-            CacheGroup(r, ents, self.num_pages, self.max_slots, max_pages_per_slot, dtype, device)
+            CacheGroup(r, ents, self.num_pages, self.max_slots, max_pages_per_slot, dtype, device,
+                       self.table_stager)
             for r, ents in by_req.items()]
         where: Dict[int, Tuple[CacheGroup, int]] = {}
         for g in self.groups:
@@ -174,9 +231,13 @@ class KVCache:
             if need > g.pages.available:
                 raise CacheFull(f"the step needs {need} more pages of {PAGE_TOKENS} tokens, "
                                 f"{g.pages.available} of {g.num_pages} are free")
-        for g in self.groups:
-            for slot, n in growth:
-                g.extend(slot, self.lengths[slot] + n)
+        self.table_stager.begin()
+        try:
+            for g in self.groups:
+                for slot, n in growth:
+                    g.extend(slot, self.lengths[slot] + n)
+        finally:
+            self.table_stager.end()
 
     def commit(self, growth: Sequence[Tuple[int, int]]) -> None:
         """After the step ran: the sequences are longer now."""

@@ -2,12 +2,21 @@
 (src/cli/commands/run.zig:62-133): the same option names with the same meanings
 and defaults where the reference has them (--prompt/-p, --max-tokens 256,
 --temperature 0, --top-k 0, --top-p 1, --stream/--no-stream, --metrics[=full],
---verbose); the positional argument is a model folder instead of a tuned plan's
+--profile, --verbose); the positional argument is a model folder instead of a tuned plan's
 alias, and prompts are token ids because tokenizing happens before this library.
 
     python -m zlm_b200 run MODEL_DIR -p "1 2 3" --max-tokens 32
     python -m zlm_b200 run MODEL_DIR --random-prompts 8 --min-len 5 --max-len 40 --temperature 0.8 --seed 1
+    python -m zlm_b200 run MODEL_DIR -p "1 2 3" --profile --dump-logits logits.f32
     python -m zlm_b200 random-model --config config.json --seed 0 --out DIR
+
+``--profile`` prints, for one prefill step and a few decode steps of the given prompts,
+every operation's time by CUDA events with the bytes it moves and GB/s (the reference's
+per-op profile with weight bytes per token and matvec GB/s: src/cli/commands/run.zig:233-299).
+``--dump-logits FILE`` writes the fp32 logits every generated token was chosen from, one
+row [vocab] per token in the order of emission, and FILE.json with each row's request,
+position, chosen token and its logit (the reference's ``--verbose=all`` trace of
+{id, logit} per token: src/runtime/session.zig:89-104,1556-1576).
 """
 from __future__ import annotations
 
@@ -46,6 +55,10 @@ def _parser() -> argparse.ArgumentParser:
     run.add_argument("--no-stream", dest="stream", action="store_false")
     run.add_argument("--metrics", nargs="?", const="", default=None, help="print timings (=full for phases)")
     run.add_argument("--verbose", nargs="?", const="min", default=None)
+    run.add_argument("--profile", nargs="?", type=int, const=8, default=None, metavar="STEPS",
+                     help="time every operation of one prefill and STEPS decode steps (default 8), then generate")
+    run.add_argument("--dump-logits", metavar="FILE",
+                     help="write the logits every generated token was chosen from (float32 rows) and FILE.json")
     run.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     run.add_argument("--cache-tokens", type=int, default=0, help="tokens the cache holds (default: what the requests need)")
     run.add_argument("--max-batch", type=int, default=0)
@@ -86,9 +99,39 @@ def _run(a) -> int:
     def on_token(req: int, tok: int) -> None:
         print(f"{req}\t{tok}", flush=True)
 
+    if a.profile is not None:
+        from .profiling import format_table, profile_engine
+        batch = prompts[: eng.max_batch]
+        print(format_table(profile_engine(eng, batch, a.profile)), file=sys.stderr)
+
+    dump, index = None, []
+    on_logits = None
+    if a.dump_logits:
+        dump = open(a.dump_logits, "wb")
+
+        def on_logits(requests, positions, logits) -> None:
+            rows = logits[: len(requests)].detach().to("cpu", torch.float32).contiguous()
+            rows.numpy().astype("<f4", copy=False).tofile(dump)
+            for r, p in zip(requests, positions):
+                index.append({"request": int(r), "position": int(p)})
+
     res = eng.generate(prompts, max_tokens=a.max_tokens, temperature=a.temperature, top_k=a.top_k,
                        top_p=a.top_p, seed=a.seed, stop_token_ids=a.stop,
-                       on_token=on_token if a.stream else None)
+                       on_token=on_token if a.stream else None, on_logits=on_logits)
+    if dump is not None:
+        dump.close()
+        import numpy as np
+        rows = np.fromfile(a.dump_logits, dtype="<f4").reshape(len(index), -1) if index else None
+        # the token chosen at (request, position): the request's output at position - len(prompt);
+        # a stop token that was chosen but not emitted has no entry in the output
+        for i, rec in enumerate(index):
+            out = res.tokens[rec["request"]]
+            j = rec["position"] - len(prompts[rec["request"]])
+            if 0 <= j < len(out):
+                rec["token"] = int(out[j])
+                rec["logit"] = float(rows[i, out[j]])
+        with open(a.dump_logits + ".json", "w") as f:
+            json.dump({"vocab": int(cfg.vocab_size), "rows": index}, f)
     if not a.stream:
         for i, t in enumerate(res.tokens):
             print(f"{i}\t{' '.join(map(str, t))}")

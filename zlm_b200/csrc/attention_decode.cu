@@ -53,7 +53,7 @@ static int launch_decode(__nv_bfloat16* out, int out_stride, const __nv_bfloat16
     const size_t merge_bytes = (size_t)DEC_WARPS * 16 * (HD + 2) * sizeof(float);
     const size_t smem = stage_bytes > merge_bytes ? stage_bytes : merge_bytes;
     auto kern = attention_decode_kernel<HD>;
-    static bool attr_set = false;
+    static bool attr_set_dev[64] = {}; bool& attr_set = attr_set_dev[zlm_device_index()];
     if (!attr_set) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) {
@@ -140,7 +140,9 @@ extern "C" int zlm_attention_decode_static(void* out, int out_stride, const void
         zlm_set_error("attention_decode_static: cannot tell the current device (%s)", cudaGetErrorString(e));
         return ZLM_ERR_CUDA;
     }
-    if (!g_decode_scratch_ptr[dev]) {
+    // one split needs no partials: nothing to look up, and the call may then be a device's first
+    // even inside a stream capture
+    if (splits > 1 && !g_decode_scratch_ptr[dev]) {
         // once per device, with that device current: in host code the array's name is
         // only a handle; the address a kernel can use has to be asked for
         float* p = nullptr;
@@ -152,8 +154,10 @@ extern "C" int zlm_attention_decode_static(void* out, int out_stride, const void
         }
         g_decode_scratch_ptr[dev] = p;
     }
-    float* part_o = g_decode_scratch_ptr[dev];
-    float* part_ml = part_o + (size_t)T * nq * splits * hd;
+    float* part_o = splits > 1 ? g_decode_scratch_ptr[dev] : nullptr;
+    float* part_ml = splits > 1 ? part_o + (size_t)T * nq * splits * hd : nullptr;
     return zlm_attention_decode(out, out_stride, q, q_stride, pool, block_table, table_stride, token_pos,
                                 token_slot, T, nq, nkv, hd, scale, window, splits, per, part_o, part_ml, st);
 }
+
+ZLM_TRANSLATION_UNIT(attention_decode)

@@ -135,3 +135,5 @@ extern "C" int zlm_attention_generic(void* out, int out_stride, const void* q, i
         ZLM_REQUIRE(false, "attention: unsupported dtype %d", dtype);
     return zlm_check_launch("attention_generic");
 }
+
+ZLM_TRANSLATION_UNIT(attention_generic)

@@ -208,7 +208,7 @@ static int launch_prefill(__nv_bfloat16* out, int out_stride, const __nv_bfloat1
                           int nq, int nkv, float scale, int window, cudaStream_t st) {
     const size_t smem = (size_t)4 * ZLM_PAGE * HD * sizeof(__nv_bfloat16);
     auto kern = attention_prefill_kernel<HD>;
-    static bool attr_set = false;
+    static bool attr_set_dev[64] = {}; bool& attr_set = attr_set_dev[zlm_device_index()];
     if (!attr_set) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) {
@@ -252,3 +252,5 @@ extern "C" int zlm_attention_prefill(void* out, int out_stride, const void* q, i
 #undef ZLM_PRE_CASE
     ZLM_REQUIRE(false, "attention_prefill: head_dim=%d", hd);
 }
+
+ZLM_TRANSLATION_UNIT(attention_prefill)

@@ -23,6 +23,7 @@
 // Formula: s_t = (q . k_t) / sqrt(hd) for t in [t_start, pos], softmax, o = sum p_t v_t
 // (src/kernels/transformer/attention.zig:86-164; per-row bound in block prefill:
 // src/runtime/executor.zig:565-584; window start: :93-98).
+#define TC_FAMILY 2
 #include "tc_common.cuh"
 #include <math.h>
 
@@ -368,7 +369,7 @@ extern "C" int zlm_attention_prefill_tc(void* out, int out_stride, const void* q
                         (size_t)hpc * 2 * FA_BM * ZLM_PAGE * 2 + 1024 + 256;
 #define ZLM_FA_LAUNCH(H)                                                                                          \
     {                                                                                                             \
-        static bool attr_set = false;                                                                             \
+        static bool attr_set_dev[64] = {}; bool& attr_set = attr_set_dev[zlm_device_index()];                                                                             \
         if (!attr_set) {                                                                                          \
             cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<H>,                                  \
                                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);         \
@@ -397,8 +398,5 @@ extern "C" int zlm_attention_prefill_tc_set_heads(int heads) {
     return ZLM_OK;
 }
 
-extern "C" int zlm_attention_tc_status() {
-    int v = 0;
-    if (cudaMemcpyFromSymbol(&v, g_tc_error, sizeof(int)) != cudaSuccess) return -1;
-    return v;
-}
+
+ZLM_TRANSLATION_UNIT(attention_prefill_tc)

@@ -20,6 +20,99 @@
 void zlm_set_error(const char* fmt, ...);
 int zlm_check_launch(const char* what);
 
+// ---------------------------------------------------------------------------
+// The library's status block: one small structure in pinned host memory that the GPU
+// writes directly.  A bounded wait that gives up, or (in the bounds-check build) an
+// access outside every registered range, leaves its mark there, and the host reads it
+// without synchronising or copying.  Each translation unit has its own device-side
+// pointers to the block and to the bounds table (`g_zlm`), bound once per device by zlm_bind_shared(),
+// which the library's set-up calls for every translation unit before anything runs.
+// ---------------------------------------------------------------------------
+#define ZLM_BC_MAX_RANGES 256
+struct ZlmShared {                       // pinned host memory
+    int status;                          // first give-up: (kernel family << 8) | where
+    int bc_violations;                   // accesses refused by the bounds-check build
+    int bc_first_site;                   // (file id << 16) | line of the first one
+    int pad;
+    unsigned long long bc_first_addr;
+};
+struct ZlmBoundsTable {                  // device memory; only the bounds-check build reads it
+    int n, pad;
+    unsigned long long lo[ZLM_BC_MAX_RANGES], hi[ZLM_BC_MAX_RANGES];
+};
+struct ZlmBinding {
+    ZlmShared* shared;
+    ZlmBoundsTable* bounds;
+};
+int zlm_runtime_binding(ZlmBinding* out);        // the current device's block and table (made on first use)
+static __device__ ZlmBinding g_zlm = {nullptr, nullptr};
+
+static inline int zlm_bind_shared() {
+    static bool bound[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) {
+        zlm_set_error("cannot tell the current device");
+        return ZLM_ERR_CUDA;
+    }
+    if (bound[dev]) return ZLM_OK;
+    ZlmBinding b;
+    int rc = zlm_runtime_binding(&b);
+    if (rc != ZLM_OK) return rc;
+    cudaError_t e = cudaMemcpyToSymbol(g_zlm, &b, sizeof(b));
+    if (e != cudaSuccess) {
+        zlm_set_error("cannot bind the status block on device %d: %s", dev, cudaGetErrorString(e));
+        return ZLM_ERR_CUDA;
+    }
+    bound[dev] = true;
+    return ZLM_OK;
+}
+// every .cu file ends with ZLM_TRANSLATION_UNIT(name); status.cu lists the names
+#define ZLM_TRANSLATION_UNIT(name) extern "C" int zlm_bind_##name() { return zlm_bind_shared(); }
+
+__device__ __forceinline__ void zlm_report_status(int code) {
+    ZlmShared* s = g_zlm.shared;
+    if (s && *(volatile int*)&s->status == 0) {
+        *(volatile int*)&s->status = code;
+        __threadfence_system();
+    }
+}
+
+// The bounds-check build (-DZLM_BOUNDS_CHECK): every global-memory access of the hand-written
+// kernels that is not a TMA copy (those are bounded by their tensor maps) first asks
+// ZLM_CHK(pointer, bytes); an access that does not lie inside one of the ranges the caller
+// registered (the tensors it passed) is counted, its place recorded, and skipped.  Nothing
+// traps.  In the ordinary build the macro is `true` and the compiler drops it.
+#ifdef ZLM_BOUNDS_CHECK
+#ifndef ZLM_FILE_ID
+#define ZLM_FILE_ID 0
+#endif
+__device__ __noinline__ static bool zlm_bc_ok(const void* p, unsigned long long bytes, int line) {
+    ZlmShared* s = g_zlm.shared;
+    const ZlmBoundsTable* t = g_zlm.bounds;
+    if (!s || !t) return true;
+    const unsigned long long a = (unsigned long long)p;
+    const int n = t->n;
+    for (int i = 0; i < n; ++i)
+        if (a >= t->lo[i] && a + bytes <= t->hi[i]) return true;
+    if (atomicAdd_system(&s->bc_violations, 1) == 0) {
+        s->bc_first_site = (ZLM_FILE_ID << 16) | line;
+        s->bc_first_addr = a;
+    }
+    __threadfence_system();
+    return false;
+}
+#define ZLM_CHK(p, bytes) zlm_bc_ok((const void*)(p), (unsigned long long)(bytes), __LINE__)
+#else
+#define ZLM_CHK(p, bytes) true
+#endif
+
+// the current device, for per-device "done once" flags (function attributes are per device)
+static inline int zlm_device_index() {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 0;
+    return dev;
+}
+
 #define ZLM_REQUIRE(cond, ...)                 \
     do {                                       \
         if (!(cond)) {                         \

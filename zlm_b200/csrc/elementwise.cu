@@ -135,3 +135,5 @@ extern "C" int zlm_swiglu(void* out, const void* gu, int dtype, int T, int I, cu
     return zlm_check_launch("swiglu");
 }
 
+
+ZLM_TRANSLATION_UNIT(elementwise)

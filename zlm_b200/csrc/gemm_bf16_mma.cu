@@ -173,7 +173,7 @@ static int launch_mma(void* Y, const __nv_bfloat16* X, const __nv_bfloat16* W, i
 #define ZLM_LAUNCH_MODE(M)                                                                           \
     {                                                                                                \
         auto kern = gemm_bf16_mma_kernel<BM, BN, WARPS_M, WARPS_N, M>;                               \
-        static bool attr_set = false;                                                                \
+        static bool attr_set_dev[64] = {}; bool& attr_set = attr_set_dev[zlm_device_index()];                                                                \
         if (!attr_set) {                                                                             \
             cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,  \
                                                  (int)smem);                                         \
@@ -212,3 +212,5 @@ extern "C" int zlm_gemm_bf16_mma(void* Y, const void* X, const void* W, int T, i
     if (T > 16) return launch_mma<32, 64, 2, 4>(Y, x, w, T, N, K, ldx, ldy, mode, st);
     return launch_mma<16, 128, 1, 8>(Y, x, w, T, N, K, ldx, ldy, mode, st);
 }
+
+ZLM_TRANSLATION_UNIT(gemm_bf16_mma)

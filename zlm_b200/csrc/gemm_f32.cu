@@ -75,3 +75,5 @@ extern "C" int zlm_gemm_f32(float* Y, const float* X, const float* W, int T, int
     else gemm_f32_kernel<0><<<grid, 256, 0, st>>>(Y, X, W, T, N, K, ldy);
     return zlm_check_launch("gemm_f32");
 }
+
+ZLM_TRANSLATION_UNIT(gemm_f32)

@@ -20,14 +20,15 @@
 // the TMA's byte count, `empty` by tcgen05.commit when the products that read a stage have
 // retired.
 //
-// Every wait is bounded: a wait that does not come true sets an error word that
-// the host reads (zlm_gemm_tc_status) and makes every role leave its loop; the
+// Every wait is bounded: a wait that does not come true leaves its mark in the library's
+// status word (zlm_status, in pinned host memory) and makes every role leave its loop; the
 // block then waits, again bounded, for copies still in flight, frees its tensor
 // memory and returns.
 //
 // out_i = sum_j W[i,j] x_j with bf16 operands and fp32 accumulation
 // (src/kernels/linear/matvec/kernels/bfloat.zig:43-67; the reference's batched
 // product: src/kernels/linear/matmul/root.zig:62-81).
+#define TC_FAMILY 1
 #include "tc_common.cuh"
 
 __device__ __forceinline__ float silu_mul(float g, float u) { return (g / (1.0f + expf(-g))) * u; }
@@ -786,7 +787,7 @@ static int launch_tc(void* Y, const void* X, const void* W, int T, int N, int K,
 #define ZLM_TC_LAUNCH(M)                                                                                   \
     {                                                                                                      \
         auto kern = gemm_tc_kernel<BN, STAGES, M>;                                                         \
-        static bool attr_set = false;                                                                      \
+        static bool attr_set_dev[64] = {}; bool& attr_set = attr_set_dev[zlm_device_index()];                                                                      \
         if (!attr_set) {                                                                                   \
             cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
             if (e != cudaSuccess) {                                                                        \
@@ -832,7 +833,7 @@ static int launch_tc_persistent(void* Y, const void* X, const void* W, int T, in
 #define ZLM_TCP_LAUNCH(M)                                                                                  \
     {                                                                                                      \
         auto kern = gemm_tc_persistent_kernel<BN, STAGES, M>;                                              \
-        static bool attr_set = false;                                                                      \
+        static bool attr_set_dev[64] = {}; bool& attr_set = attr_set_dev[zlm_device_index()];                                                                      \
         if (!attr_set) {                                                                                   \
             cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
             if (e != cudaSuccess) {                                                                        \
@@ -865,7 +866,7 @@ static int launch_tc_pair(void* Y, const void* X, const void* W, int T, int N, i
 #define ZLM_TCQ_LAUNCH(M)                                                                                  \
     {                                                                                                      \
         auto kern = gemm_tc_pair_kernel<BN, STAGES, M>;                                                    \
-        static bool attr_set = false;                                                                      \
+        static bool attr_set_dev[64] = {}; bool& attr_set = attr_set_dev[zlm_device_index()];                                                                      \
         if (!attr_set) {                                                                                   \
             cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
             if (e != cudaSuccess) {                                                                        \
@@ -932,7 +933,7 @@ static int launch_tc_few(void* Y, const void* X, const void* W, int T, int N, in
 #define ZLM_TCF_LAUNCH(M)                                                                                  \
     {                                                                                                      \
         auto kern = gemm_tc_few_kernel<BN, STAGES, M>;                                                     \
-        static bool attr_set = false;                                                                      \
+        static bool attr_set_dev[64] = {}; bool& attr_set = attr_set_dev[zlm_device_index()];                                                                      \
         if (!attr_set) {                                                                                   \
             cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
             if (e != cudaSuccess) {                                                                        \
@@ -1028,8 +1029,82 @@ extern "C" int zlm_gemm_tc(void* Y, const void* X, const void* W, int T, int N, 
 
 // 0 if no bounded wait of the kernel ever gave up; else 1 (producer), 2 (product issuer) or 3 (epilogue).
 // Synchronises the device.
-extern "C" int zlm_gemm_tc_status() {
-    int v = 0;
-    if (cudaMemcpyFromSymbol(&v, g_tc_error, sizeof(int)) != cudaSuccess) return -1;
-    return v;
+// ---------------------------------------------------------------------------------------
+// The give-up path on purpose.  One block with the roles of the product kernels, built from
+// the same helpers: the producer loads one tile of `src` by TMA; the issuer allocates tensor
+// memory and then waits, with the short limit given, on a barrier at which nobody ever
+// arrives; an epilogue warp waits with the ordinary limit on another such barrier and must
+// be released by the abort flag, not by its own clock.  Then everyone walks to the end as the
+// product kernels do: the producer lets its copy land, tensor memory is freed, the kernel
+// returns.  Nothing faults and nothing is left waiting.  out[0] = the status code it reported,
+// out[1] = 1 if the epilogue warp was released by the flag, out[2] = nanoseconds the kernel took,
+// out[3] = 1 if the tile had landed when the producer looked.
+// ---------------------------------------------------------------------------------------
+#define TC_TEST_WHERE 0x7e
+__global__ void __launch_bounds__(96, 1)
+gemm_tc_giveup_kernel(const __grid_constant__ CUtensorMap map, unsigned long long limit_ns, int* __restrict__ out) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* full = (uint64_t*)(smem + TC_BM * TC_BK * 2);
+    uint64_t* never_a = full + 1;
+    uint64_t* never_b = full + 2;
+    unsigned* tmem_slot = (unsigned*)(full + 3);
+    volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const unsigned long long t0 = tc_now_ns();
+    if (threadIdx.x == 0) {
+        mbar_init(full, 1);
+        mbar_init(never_a, 1);
+        mbar_init(never_b, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n"
+                     ::"r"(smem_u32(tmem_slot)), "r"(64u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const unsigned tmem_base = *tmem_slot;
+    if (warp == 0) {
+        if (lane == 0) {
+            mbar_expect_tx(full, TC_BM * TC_BK * 2);
+            tma_load_2d(smem, &map, 0, 0, full);
+            // the producer's own wait: released by the flag once the issuer has given up
+            const bool ok = mbar_wait(never_b, 0, abort_flag, 1);
+            if (!ok) mbar_drain(full, 0);
+            out[3] = mbar_try(full, 0) ? 1 : 0;
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const bool ok = mbar_wait(never_a, 0, abort_flag, TC_TEST_WHERE, limit_ns);
+            out[0] = ok ? 0 : ((TC_FAMILY << 8) | TC_TEST_WHERE);
+        }
+    } else {
+        const bool ok = mbar_wait(never_b, 0, abort_flag, 3);
+        if (lane == 0) out[1] = (!ok && *abort_flag == TC_TEST_WHERE) ? 1 : 0;
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        __syncwarp();
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_base), "r"(64u) : "memory");
+    }
+    if (threadIdx.x == 0) out[2] = (int)min(tc_now_ns() - t0, 2000000000ull);
 }
+
+// For tests: runs the give-up path once with a wait limit of `limit_ns` (at most 100 ms).
+// src: 128 x 64 bf16, 16-byte aligned; out: 4 ints (see the kernel).
+extern "C" int zlm_test_bounded_wait(const void* src, int* out, unsigned long long limit_ns, cudaStream_t st) {
+    ZLM_REQUIRE(limit_ns > 0 && limit_ns <= 100000000ull, "test_bounded_wait: the limit must be at most 100 ms");
+    CUtensorMap m;
+    int rc = zlm_make_map_2d(&m, src, TC_BM, TC_BK, TC_BK, TC_BM, TC_BK);
+    if (rc) return rc;
+    zlm_launch(gemm_tc_giveup_kernel, dim3(1), dim3(96), TC_BM * TC_BK * 2 + 1024 + 256, st, m, limit_ns, out);
+    return zlm_check_launch("test_bounded_wait");
+}
+
+ZLM_TRANSLATION_UNIT(gemm_tcgen05)

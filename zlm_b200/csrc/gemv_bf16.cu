@@ -219,3 +219,5 @@ extern "C" int zlm_gemv_bf16(void* Y, const void* X, const void* W, int T, int N
     if (T <= 8) return launch_gemv<1>(Y, x, w, T, N, K, ldx, ldy, mode, st);
     return launch_gemv<2>(Y, x, w, T, N, K, ldx, ldy, mode, st);
 }
+
+ZLM_TRANSLATION_UNIT(gemv_bf16)

@@ -91,3 +91,5 @@ extern "C" int zlm_qk_norm_rope_write(void* qkv, int dtype, int row_stride, cons
         ZLM_REQUIRE(false, "qk_norm_rope_write: unsupported dtype %d", dtype);
     return zlm_check_launch("qk_norm_rope_write");
 }
+
+ZLM_TRANSLATION_UNIT(rope_kv)

@@ -789,7 +789,7 @@ extern "C" int zlm_sample(int* out, const float* logits, int R, int V, int ld, f
     ZLM_REQUIRE(form != 2, "sample: a row of %d logits is too long for the cluster form", V);
     ZLM_REQUIRE(form >= 0 && form <= 2, "sample: form %d", form);
     const size_t smem = hist;
-    static bool attr_set = false;
+    static bool attr_set_dev[64] = {}; bool& attr_set = attr_set_dev[zlm_device_index()];
     if (!attr_set) {
         cudaError_t e = cudaFuncSetAttribute(sample_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) {
@@ -806,3 +806,5 @@ extern "C" int zlm_sample(int* out, const float* logits, int R, int V, int ld, f
 extern "C" unsigned long long zlm_sample_hash(unsigned long long seed, int request, int position) {
     return splitmix64(seed ^ splitmix64(((unsigned long long)(unsigned)request << 32) | (unsigned)position));
 }
+
+ZLM_TRANSLATION_UNIT(sampling)

@@ -9,9 +9,11 @@
 #define TC_BK 64
 #define TC_THREADS 192
 #define TC_WAIT_NS 2000000000ull        // a wait gives up after two seconds
-
-// set when a bounded wait gives up; one copy per translation unit (each has its own status call)
-static __device__ int g_tc_error = 0;
+// which kernel family a give-up is reported for: the including file defines it (1: products,
+// 2: prefill attention); the status word holds (family << 8) | place of the wait
+#ifndef TC_FAMILY
+#define TC_FAMILY 0
+#endif
 
 // ---------------------------------------------------------------- PTX wrappers
 __device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -36,16 +38,17 @@ __device__ __forceinline__ unsigned long long tc_now_ns() {
     asm volatile("mov.u64 %0, %%globaltimer;\n" : "=l"(t));
     return t;
 }
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity, volatile int* abort_flag, int where) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity, volatile int* abort_flag, int where,
+                                          unsigned long long limit_ns = TC_WAIT_NS) {
     if (mbar_try(bar, parity)) return true;
     const unsigned long long t0 = tc_now_ns();
     for (unsigned it = 1;; ++it) {
         if (mbar_try(bar, parity)) return true;
         if (*abort_flag) return false;
-        if ((it & 63) == 0 && tc_now_ns() - t0 > TC_WAIT_NS) break;
+        if ((it & 63) == 0 && tc_now_ns() - t0 > limit_ns) break;
     }
     *abort_flag = where;
-    atomicCAS(&g_tc_error, 0, where);
+    zlm_report_status((TC_FAMILY << 8) | where);
     return false;
 }
 // after a wait gave up: lets copies that are still in flight land (at most 10 ms each)
@@ -186,7 +189,7 @@ __device__ __forceinline__ bool mbar_wait_pair(uint64_t* bar, unsigned parity, v
         if ((it & 63) == 0 && tc_now_ns() - t0 > TC_WAIT_NS) break;
     }
     *abort_flag = where;
-    atomicCAS(&g_tc_error, 0, where);
+    zlm_report_status((TC_FAMILY << 8) | where);
     return false;
 }
 

@@ -22,7 +22,10 @@
 //   * No cudaMalloc, cudaFree or allocating library routine is called.
 //   * The first call on a device looks the array's device address up
 //     (cudaGetSymbolAddress, with that device current) and remembers it; make
-//     that first call outside any stream capture.
+//     that first call outside any stream capture, and from one host thread at a
+//     time (the remembered address and the kernels' per-device set-up are
+//     written without a lock).  A call with splits == 1 uses no scratch and
+//     looks nothing up.
 //   * All calls share the one array, which keeps whatever the last call left
 //     there.  Nothing has to start at zero: every partial that the combining
 //     kernel reads is written by the same call first.  Two calls whose kernels

@@ -150,6 +150,9 @@ def plan_step(entries: Sequence[StepEntry], lengths, vocab_size: int, layout: Me
                 raise StepError(f"wanted place {w} is outside the {n} tokens of slot {e.slot}")
             want.append(t + w)
         t += n
+    if len(want) > T:
+        # a place named twice: the wanted rows have room for one row per token
+        raise StepError(f"{len(want)} places are wanted among {T} tokens; a place may be named once")
     arrays = {"token_ids": ids, "token_pos": pos, "token_slot": slot, "token_seq": seq,
               "seq_slot": s_slot, "seq_start": s_start, "seq_new": s_new, "cu_seqlens": cu,
               "want_rows": np.asarray(want, np.int32)}
@@ -160,16 +163,8 @@ def make_context(stager: MetaStager, arrays, T: int, R: int, workspace=None) -> 
     s_new = arrays["seq_new"]
     s_start = arrays["seq_start"]
     max_len = int((s_start + s_new).max())
-    pages = (max_len + 63) // 64
-    # the longest sequence in pages, rounded up: powers of two up to 8, then multiples of 8
-    # (what the decode attention sizes its grid by, and a captured graph is keyed by)
-    bucket = 1
-    while bucket < pages and bucket < 8:
-        bucket *= 2
-    if bucket < pages:
-        bucket = (pages + 7) // 8 * 8
     return StepContext(
-        len_bucket=bucket, workspace=workspace,
+        workspace=workspace,
         T=T, R=R,
         token_ids=stager.view("token_ids", T), token_pos=stager.view("token_pos", T),
         token_slot=stager.view("token_slot", T), token_seq=stager.view("token_seq", T),

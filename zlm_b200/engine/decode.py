@@ -1,29 +1,27 @@
-"""Decode steps as replayed CUDA graphs, or as one persistent kernel.
+"""Decode steps as replayed CUDA graphs.
 
 A decode step (one token for each of R live sequences, logits at every row, one
 sampled token per row) is a chain of a few hundred small operations; launched one
-by one the GPU finishes them faster than the host can launch them.  Both remedies
-rest on the fact that all inputs of a step live at fixed device addresses (the
-per-step integer arrays in the engine's staging buffer, the block tables, the
-scratch buffers) and only their content changes from step to step:
-
-* the step's device work is captured once per (R, length bucket, sampling
-  parameters) as a CUDA graph and replayed: the default;
-* ``use_stream``: bf16 steps of up to 8 rows whose parts launch nothing but the
-  library's kernels are recorded once per (R, length bucket) as a program of the
-  persistent decode kernel (``stream.py``) and run as one cooperative launch.  It
-  gives the same bits as the graph; measured at Qwen3-8B sizes it is slower than
-  the graph (its products stream the weights at 4.4 TB/s against 4.7 TB/s for the
-  stand-alone kernels, and its attention runs on one warp group per SM), so it is
-  off unless asked for.
+by one the GPU finishes them faster than the host can launch them.  All inputs of
+a step live at fixed device addresses (the per-step integer arrays in the engine's
+staging buffer, the block tables, the scratch buffers) and only their content
+changes from step to step, so the step's device work is captured once per (rows,
+what the parts say changes their launches, sampling parameters) as a CUDA graph and
+replayed.
 
 Sampled tokens stay on the device and can be fed to the next step from there, so
 a run of steps needs no host round trip unless the caller wants the tokens.
+
+A persistent kernel that walked a recorded step in one cooperative launch was built
+and measured against the graph; it lost at every size (Qwen3-8B sizes, batch 8: 6.7
+against 3.9 ms a step; Qwen3-0.6B sizes, batch 1 / 8: 580 / 2,580 against 1,010 /
+6,160 tokens a second) and was taken out.
 """
 from __future__ import annotations
 
 import gc
 import weakref
+from collections import OrderedDict
 from typing import Dict, List, Optional, Sequence, Tuple
 
 import numpy as np
@@ -31,21 +29,17 @@ import torch
 
 from ..sampling import SamplingParams
 from .batch import StepError, make_context
-from .stream import MAX_TOKENS as STREAM_MAX_ROWS
-from .stream import NotStreamable, StepRecorder, StreamProgram, stream_blocks
+
+MAX_GRAPHS = 64      # captured steps kept; the one unused for longest goes first
 
 
 class DecodeRunner:
-    def __init__(self, engine, use_graphs: Optional[bool] = None, use_stream: Optional[bool] = None):
+    def __init__(self, engine, use_graphs: Optional[bool] = None):
         # the engine owns this runner: a weak reference back, so that dropping the engine frees
         # its weights and cache at once instead of when the cycle collector next runs
         self._engine = weakref.ref(engine)
         cuda = engine.device.type == "cuda"
         self.use_graphs = (cuda and engine.model.graph_safe) if use_graphs is None else use_graphs
-        self.stream_blocks = stream_blocks(engine.rt.k) if cuda else 0
-        self.can_stream = bool(cuda and engine.dtype == torch.bfloat16 and engine.model.kernels_only
-                               and self.stream_blocks > 0)
-        self.use_stream = bool(use_stream) and self.can_stream
         # Programmatic dependent launch between the step's kernels (a kernel's blocks may be
         # scheduled while the kernel before it drains; each waits before it reads what that one
         # wrote): None = for steps of up to 16 rows.  Measured against plain stream order:
@@ -53,13 +47,9 @@ class DecodeRunner:
         # batch 8: 5,940 -> 6,100, batch 1: 964 -> 1,028; at batch 64 (one block per SM with
         # nearly all its shared memory) 8,446 -> 8,475 and 16,450 -> 16,120: left off there.
         self.use_pdl: Optional[bool] = None
-        # blocks the decode attention cuts its work for: None lets each path take its own
-        # (what runs at a time: 3 per SM stand-alone, 1 per SM in the persistent kernel)
-        self.attention_blocks: Optional[int] = None
-        self.graphs: Dict[Tuple, torch.cuda.CUDAGraph] = {}
+        self.graphs: "OrderedDict[Tuple, torch.cuda.CUDAGraph]" = OrderedDict()
         self.graph_generation = -1
-        self.programs: Dict[Tuple, Optional[StreamProgram]] = {}
-        self.program_generation = None
+        self.replays = 0
         self.out = torch.zeros(engine.max_batch, dtype=torch.int32, device=engine.device)
         # where queued steps leave their tokens for the host: two buffers, so that a step can be
         # queued while the one before it is still being read
@@ -117,12 +107,10 @@ class DecodeRunner:
             e.stager.view("token_ids", R).copy_(self.out[:R])
         arrays.setdefault("token_ids", ar)   # make_context only needs the shapes
         ctx = make_context(e.stager, arrays, R, R, e.rt.ws)
-        ctx.attention_blocks = self.attention_blocks
-        if not (self.use_stream and R <= STREAM_MAX_ROWS and self._run_program(ctx, R, params)):
-            if self.use_graphs:
-                self._replay(ctx, R, params)
-            else:
-                self._device_work(ctx, R, params)
+        if self.use_graphs:
+            self._replay(ctx, R, params)
+        else:
+            self._device_work(ctx, R, params)
         e.cache.commit(growth)
         e.steps_run += 1
         return self.out[:R]
@@ -148,6 +136,10 @@ class DecodeRunner:
         done, buf, R = handle
         if done is not None:
             done.synchronize()
+        # the host has just waited for the step: what its kernels reported is there to be read
+        check = getattr(self.e.rt.k, "check_status", None)
+        if check is not None:
+            check()
         return buf[:R].tolist()
 
     # ------------------------------------------------------------------ device work
@@ -177,67 +169,18 @@ class DecodeRunner:
             e.rt.k.sample(self.out[:R], logits, params.temperature, params.top_k, params.top_p, params.seed,
                           e.stager.view("sample_request", R), e.stager.view("sample_position", R))
 
-    # ------------------------------------------------------------------ the persistent kernel
-    def _run_program(self, ctx, R: int, params: SamplingParams) -> bool:
-        """Runs the step as one launch of the persistent kernel and chooses the tokens; False
-        if this step cannot be a program (the caller then launches the kernels one by one)."""
-        before = self.e.rt.k.launches()
-        ok, logits = self.run_program(ctx, R, R)
-        if not ok:
-            return False
-        self.last_logits = logits
-        self._choose(logits, R, params)
-        self.launches_per_step = self.e.rt.k.launches() - before
-        return True
-
-    def run_program(self, ctx, R: int, wanted: int):
-        """The device work of a step of one token per row (``Engine.run_model``) as one launch
-        of the persistent kernel: (True, logits at the first ``wanted`` of the uploaded rows,
-        or None) or (False, None) if this step cannot be a program."""
-        if not (self.use_stream and ctx.is_decode and ctx.T == R and R <= STREAM_MAX_ROWS):
-            return False, None
-        if self.program_generation != self._generation():
-            self.programs.clear()
-        key = (R, wanted, ctx.len_bucket, ctx.attention_blocks)
-        if key not in self.programs:
-            self.programs[key] = self._record(ctx, wanted)
-            self.program_generation = self._generation()
-        entry = self.programs[key]
-        if entry is None:
-            return False, None
-        prog, logits = entry
-        prog.run()
-        return True, logits
-
-    def _record(self, ctx, wanted: int):
-        """One walk over the model with a recorder in the kernels' place.  Scratch buffers
-        that the walk itself creates or grows move; it is repeated until none did."""
-        e = self.e
-        k = e.rt.k
-        for _ in range(3):
-            gen = self._generation()
-            rec = StepRecorder(k, self.stream_blocks)
-            e.rt.k = rec
-            try:
-                logits = e.run_model(ctx, wanted)
-            except NotStreamable:
-                return None
-            finally:
-                e.rt.k = k
-            if gen == self._generation():
-                return StreamProgram(k, rec, e.device), logits
-        raise RuntimeError("scratch buffers kept moving while the decode program was recorded")
-
     def _generation(self):
         """Changes whenever a scratch buffer that a captured graph may point at has moved."""
         return (self.e.rt.ws.generation, getattr(self.e.rt.k, "scratch_generation", 0))
 
     def _replay(self, ctx, R: int, params: SamplingParams) -> None:
         e = self.e
-        key = (R, ctx.len_bucket, params, self._pdl(R))
+        key = (R, e.model.step_key(ctx), params, self._pdl(R))
         if self.graph_generation != self._generation():
             self.graphs.clear()
         g = self.graphs.get(key)
+        if g is not None:
+            self.graphs.move_to_end(key)
         if g is None:
             # a first eager run creates every scratch buffer the step needs; it also is
             # this step's result, so nothing is computed twice on replayed steps
@@ -266,6 +209,9 @@ class DecodeRunner:
                 raise RuntimeError("scratch buffers moved during graph capture")
             self.graph_generation = gen
             self.graphs[key] = g
+            while len(self.graphs) > MAX_GRAPHS:
+                self.graphs.popitem(last=False)
             # the capture did not run the kernels; the eager run above already did
             return
         g.replay()
+        self.replays += 1

@@ -62,6 +62,7 @@ class Engine:
         self.layout = MetaLayout(self.max_step_tokens, self.max_batch)
         self.stager = MetaStager(self.layout, self.device)
         self.steps_run = 0
+        self.last_logits: Optional[torch.Tensor] = None      # of the last prefill_sample / decode_sample
         from ..sampling import Sampler
         self.sampler = Sampler(self.rt)
         self._sample_meta = torch.zeros((2, self.max_batch), dtype=torch.int32, device=self.device)
@@ -95,6 +96,12 @@ class Engine:
             tensors[name] = random_tensor(name, p, seed, device, target_dtype(p, torch.float32, dt))
         return cls(config, tensors, dt, device, max_tokens, **kw)
 
+    def tensor(self, name: str) -> torch.Tensor:
+        """Read-back of a weight by its checkpoint name (``model.layers.0.self_attn.q_proj.weight``
+        ...), as the engine holds it: on the device, in the compute dtype.  The reference's
+        counterpart is its session's tensor view (src/runtime/session.zig:696-724)."""
+        return self.model.tensor(name)
+
     # ---- sequences ------------------------------------------------------------
     def new_sequence(self) -> int:
         """Takes a slot for a new sequence and returns it."""
@@ -107,21 +114,28 @@ class Engine:
     def length(self, slot: int) -> int:
         return self.cache.length(slot)
 
+    def check(self, sync: bool = False) -> None:
+        """Raises ``KernelError`` if a bounded wait inside a kernel has given up since the
+        last check (its results, and all after it, are then not valid).  The kernels report
+        into pinned host memory, so this reads a word and waits for nothing; it knows of
+        the steps the device has finished.  ``sync`` waits for the device first: call it so
+        before trusting logits that ``step`` returned."""
+        check = getattr(self.rt.k, "check_status", None)
+        if check is not None:
+            check(sync)
+
     # ---- the step ---------------------------------------------------------------
     def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
         """Runs the tokens of ``entries`` as one batch.  Returns fp32 logits
         [wanted, vocab] in the order of the entries and of their ``want`` (None if
         nothing is wanted).  The tensor is scratch: it is overwritten by the next step."""
+        self.check()              # what earlier steps reported, if they are done by now
         arrays, T, R, W = plan_step(entries, self.cache.lengths, self.spec.vocab_size, self.layout)
         growth = [(e.slot, len(e.tokens)) for e in entries]
         self.cache.reserve(growth)            # raises before anything is launched
         self.stager.upload(arrays, T, R)
         ctx = make_context(self.stager, arrays, T, R, self.rt.ws)
-        ctx.attention_blocks = self.decoder.attention_blocks
-        # one token per row: the persistent decode kernel, if the step can be its program
-        done, logits = self.decoder.run_program(ctx, R, W)
-        if not done:
-            logits = self.run_model(ctx, W)
+        logits = self.run_model(ctx, W)
         self.cache.commit(growth)
         self.steps_run += 1
         return logits
@@ -140,17 +154,23 @@ class Engine:
         """One step with every prompt whole; one token chosen per row at its prompt's
         end, back on the host."""
         logits = self.step([StepEntry(s, p, [len(p) - 1]) for s, p in zip(slots, prompts)])
+        self.last_logits = logits
         R = len(slots)
         meta = self._sample_meta[:, :R]
         if not params.greedy:
             # the token being chosen sits at position len(prompt)
             meta.copy_(torch.tensor([list(requests), [len(p) for p in prompts]], dtype=torch.int32))
-        return self.sampler.sample(logits, params, meta[0], meta[1]).tolist()
+        chosen = self.sampler.sample(logits, params, meta[0], meta[1]).tolist()
+        self.check()          # the host has just waited for the step
+        return chosen
 
     def decode_sample(self, slots: Sequence[int], tokens: Sequence[int], params,
                       requests: Sequence[int]) -> List[int]:
         """One decode step: feeds one token per row, returns the next ones on the host."""
-        return self.decoder.step(slots, tokens, params, requests).tolist()
+        chosen = self.decoder.step(slots, tokens, params, requests).tolist()
+        self.last_logits = self.decoder.last_logits
+        self.check()
+        return chosen
 
     def decode_launch(self, slots: Sequence[int], tokens: Optional[Sequence[int]], params,
                       requests: Sequence[int]):
@@ -165,7 +185,8 @@ class Engine:
 
     def generate(self, prompts: Sequence[Sequence[int]], max_tokens: int = 256, temperature: float = 0.0,
                  top_k: int = 0, top_p: float = 1.0, seed: int = 0,
-                 stop_token_ids: Optional[Sequence[int]] = None, include_stop: bool = False, on_token=None):
+                 stop_token_ids: Optional[Sequence[int]] = None, include_stop: bool = False, on_token=None,
+                 on_logits=None):
         """Token-id prompts in, generated token ids out (see ``generate.generate``).
         Option names and defaults are the reference's ``run`` command's
         (src/cli/commands/run.zig:116-120): max_tokens 256, temperature 0 (greedy),
@@ -173,4 +194,4 @@ class Engine:
         from ..sampling import SamplingParams
         from .generate import generate
         return generate(self, prompts, max_tokens, SamplingParams(temperature, top_k, top_p, seed),
-                        stop_token_ids, include_stop, on_token)
+                        stop_token_ids, include_stop, on_token, on_logits)

@@ -128,9 +128,15 @@ class BatchDecisions:
 def generate(engine, prompts: Sequence[Sequence[int]], max_tokens: int = 256,
              sampling: Optional[SamplingParams] = None, stop_token_ids: Optional[Sequence[int]] = None,
              include_stop: bool = False,
-             on_token: Optional[Callable[[int, int], None]] = None) -> GenerationResult:
+             on_token: Optional[Callable[[int, int], None]] = None,
+             on_logits: Optional[Callable] = None) -> GenerationResult:
     """Generates up to ``max_tokens`` tokens for every prompt.  ``on_token(request,
     token)`` is called for every emitted token as soon as its step is done.
+    ``on_logits(requests, positions, logits)`` is called after every step with the
+    step's rows: their request numbers, the position of the token each row is choosing,
+    and the fp32 logits [rows, vocab] it chooses from (``engine.last_logits``, still on
+    the device; the tensor is overwritten by the next step).  With it, steps run one at
+    a time: a queued step would overwrite the logits before the host has seen them.
 
     ``engine`` needs: config.eos_token_ids, max_tokens, max_batch, max_seq_len,
     new_sequence(), release(slot), prefill_sample(slots, prompts, params, requests)
@@ -165,6 +171,8 @@ def generate(engine, prompts: Sequence[Sequence[int]], max_tokens: int = 256,
             stats.prefill_ms += (time.perf_counter() - t0) * 1e3
             stats.prefill_steps += 1
             stats.prompt_tokens += sum(r.length for r in rows)
+            if on_logits is not None:
+                on_logits([r.request for r in rows], [r.length for r in rows], engine.last_logits)
             def settle(rows_, sampled_):
                 """Applies one step's tokens: emits, frees the rows that ended; returns the live rows."""
                 before = [len(r.out) for r in rows_]
@@ -180,7 +188,7 @@ def generate(engine, prompts: Sequence[Sequence[int]], max_tokens: int = 256,
                 return live
 
             rows = settle(rows, sampled)
-            launch = getattr(engine, "decode_launch", None)
+            launch = getattr(engine, "decode_launch", None) if on_logits is None else None
             if launch is None:
                 # one step at a time: feed, wait, decide
                 while rows:
@@ -191,6 +199,8 @@ def generate(engine, prompts: Sequence[Sequence[int]], max_tokens: int = 256,
                         r.length += 1
                     stats.decode_ms += (time.perf_counter() - t0) * 1e3
                     stats.decode_steps += 1
+                    if on_logits is not None:
+                        on_logits([r.request for r in rows], [r.length for r in rows], engine.last_logits)
                     rows = settle(rows, sampled)
             else:
                 # One step ahead: while the device runs a step, the next one is already queued with

@@ -32,17 +32,32 @@ def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     return torch.stack([gate.view(I // 8, 8, K), up.view(I // 8, 8, K)], dim=1).reshape(2 * I, K).contiguous()
 
 
-def decode_splits(rows: int, nkv: int, len_bucket: int, blocks: Optional[int] = None):
+def attention_len_bucket(max_len: int) -> int:
+    """The longest sequence of a step in pages, rounded up: powers of two up to 8, then
+    multiples of 8.  The decode attention sizes its grid by it, so a captured decode step
+    holds for every step with the same bucket."""
+    pages = (max_len + PAGE_TOKENS - 1) // PAGE_TOKENS
+    bucket = 1
+    while bucket < pages and bucket < 8:
+        bucket *= 2
+    if bucket < pages:
+        bucket = (pages + 7) // 8 * 8
+    return bucket
+
+
+DECODE_BLOCKS_PER_SM = 3      # blocks of the decode attention that an SM holds at a time
+
+
+def decode_splits(rows: int, nkv: int, len_bucket: int, blocks: int = 148 * DECODE_BLOCKS_PER_SM):
     """How the decode attention cuts a sequence's pages: (splits, pages per split).  A
     block's start (the query, its first pages) and end (merging its warps, writing its
     partial result) cost about as much as several pages, so the parts are as long as they
-    can be while every block that runs at a time (148 SMs x 3 for the stand-alone kernel)
+    can be while every block that runs at a time (``blocks``: the device's SMs x 3)
     still has one: one wave of blocks, two for large batches (measured at 2,100 tokens:
     batch 16 4.2 TB/s with one wave against 3.7 with two; batch 64 5.7 TB/s with two
     against 5.5 with four and 4.6 with sixteen), and at least two pages long.
     ``len_bucket`` is the longest sequence of the step in pages, rounded up, so that the
     choice (and a captured graph) holds for many steps."""
-    blocks = blocks or 444
     work = len_bucket * rows * nkv
     waves = 2 if work >= 16 * blocks else 1
     per = max(2, -(-work // (blocks * waves)))
@@ -61,8 +76,16 @@ def _dt(t: torch.Tensor) -> int:
         raise KernelError(f"unsupported dtype {t.dtype}") from None
 
 
-def _ptr(t: Optional[torch.Tensor]) -> int:
-    return 0 if t is None else t.data_ptr()
+def _span_bytes(t: torch.Tensor) -> int:
+    """Bytes from the tensor's first element to the end of its last one."""
+    if t.numel() == 0:
+        return 0
+    last = sum((n - 1) * st for n, st in zip(t.shape, t.stride()))
+    return (last + 1) * t.element_size()
+
+
+# what a status code's family byte stands for (tc_common.cuh: TC_FAMILY)
+_STATUS_FAMILY = {1: "tcgen05 product", 2: "tcgen05 prefill attention"}
 
 
 class CudaKernels:
@@ -80,6 +103,16 @@ class CudaKernels:
             raise KernelError("kernel library and Python disagree on the cache page size")
         if not torch.cuda.is_available():
             raise KernelError("zlm_b200 needs a CUDA GPU (sm_100a); none is visible and there is no CPU path")
+        # binds the status block (pinned host memory the kernels report to) for every part of
+        # the library; it copies to device symbols, so it happens here, outside any capture
+        if self.lib.zlm_runtime_init() != 0:
+            raise KernelError(self.lib.zlm_last_error().decode())
+        self.lib.zlm_bounds_first_address.restype = ctypes.c_ulonglong
+        self.bounds_check = bool(self.lib.zlm_bounds_check_build())
+        self._ranges = []
+        # blocks the decode attention cuts its work for; None: what the device holds at a time
+        self.decode_blocks: Optional[int] = None
+        self.sm_count = int(torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count)
         self._fn = {}
         self._scratch = {}
         self.scratch_generation = 0
@@ -106,14 +139,79 @@ class CudaKernels:
             fn = getattr(self.lib, name)
             fn.restype = c_int
             self._fn[name] = fn
+        if self.bounds_check:
+            self._register_ranges()
         rc = fn(*args)
         self._launches += 1
         if rc != 0:
             raise KernelError(self.lib.zlm_last_error().decode())
+        if self.bounds_check:
+            self.check_bounds(name)
+
+    def _p(self, t: Optional[torch.Tensor]) -> c_void_p:
+        """The tensor's address as a kernel argument.  In the bounds-check build the bytes it
+        spans are also noted as memory the next call may touch."""
+        if t is None:
+            return c_void_p(0)
+        if self.bounds_check:
+            self._ranges.append((t.data_ptr(), _span_bytes(t)))
+        return c_void_p(t.data_ptr())
+
+    def _register_ranges(self) -> None:
+        lib = self.lib
+        if lib.zlm_bounds_clear_ranges() != 0:
+            raise KernelError(lib.zlm_last_error().decode())
+        for base, n in self._ranges:
+            if n and lib.zlm_bounds_add_range(c_void_p(base), ctypes.c_ulonglong(n)) != 0:
+                raise KernelError(lib.zlm_last_error().decode())
+        self._ranges = []
+
+    def check_bounds(self, what: str = "") -> None:
+        """Bounds-check build: waits for the device and raises if a kernel asked for memory
+        outside the tensors it was given (the access itself was skipped)."""
+        torch.cuda.synchronize()
+        n = int(self.lib.zlm_bounds_violations())
+        if n:
+            site = int(self.lib.zlm_bounds_first_site())
+            addr = int(self.lib.zlm_bounds_first_address())
+            self.lib.zlm_bounds_reset()
+            raise KernelError(f"{what}: {n} accesses outside the tensors passed; the first at address "
+                              f"{addr:#x}, source file id {site >> 16} line {site & 0xffff}")
+
+    # -- the status word ----------------------------------------------------
+    def status(self, sync: bool = False) -> int:
+        """0, or the mark of the first bounded wait inside a kernel that gave up:
+        (kernel family << 8) | place of the wait.  The word lives in pinned host memory
+        that the GPU writes directly, so reading it costs nothing and waits for nothing;
+        it tells of the kernels that have finished (``sync`` waits for all of them first)."""
+        if sync:
+            torch.cuda.synchronize()
+        return int(self.lib.zlm_status())
+
+    def clear_status(self) -> None:
+        self.lib.zlm_status_clear()
+
+    def check_status(self, sync: bool = False) -> None:
+        """Raises if a kernel's bounded wait gave up: what that kernel computed, and
+        everything after it, is not to be trusted.  The word is cleared, so that the
+        caller may go on (the GPU and the library remain usable)."""
+        code = self.status(sync)
+        if code:
+            self.clear_status()
+            family = _STATUS_FAMILY.get(code >> 8, f"kernel family {code >> 8}")
+            raise KernelError(f"a bounded wait inside a {family} kernel gave up (place {code & 0xff}, "
+                              f"status {code:#x}): results since the last check are not valid")
 
     @staticmethod
     def _stream() -> c_void_p:
         return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def check_linear(self, what: str, w: torch.Tensor) -> None:
+        """Raises at once, with the weight's name, if no kernel takes a product with this
+        weight [N, K]: the bf16 kernels read 16 bytes (8 elements) of a row at a time."""
+        if w.dtype == torch.bfloat16 and w.shape[1] % 8 != 0:
+            raise KernelError(f"{what} [{w.shape[0]}, {w.shape[1]}]: the bfloat16 kernels need an inner size "
+                              f"that is a multiple of 8 (run this model with dtype float32)")
 
     # -- kernels ----------------------------------------------------------
     def embed(self, out: torch.Tensor, table: torch.Tensor, ids: torch.Tensor) -> None:
@@ -121,8 +219,8 @@ class CudaKernels:
         T, H = out.shape
         assert out.dtype == torch.float32 and ids.dtype == torch.int32 and table.shape[1] == H
         assert out.is_contiguous() and table.is_contiguous()
-        self._call("zlm_embed", c_void_p(out.data_ptr()), c_void_p(table.data_ptr()), c_int(_dt(table)),
-                   c_void_p(ids.data_ptr()), c_int(T), c_int(H), c_int(table.shape[0]), self._stream())
+        self._call("zlm_embed", self._p(out), self._p(table), c_int(_dt(table)),
+                   self._p(ids), c_int(T), c_int(H), c_int(table.shape[0]), self._stream())
 
     def rmsnorm(self, out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, eps: float,
                 rows: Optional[torch.Tensor] = None) -> None:
@@ -131,8 +229,8 @@ class CudaKernels:
         assert x.dtype == torch.float32 and x.shape[1] == H and w.shape == (H,)
         assert out.is_contiguous() and x.is_contiguous() and w.is_contiguous()
         assert rows is None or (rows.dtype == torch.int32 and rows.numel() >= R)
-        self._call("zlm_rmsnorm", c_void_p(out.data_ptr()), c_int(_dt(out)), c_void_p(x.data_ptr()),
-                   c_void_p(w.data_ptr()), c_int(_dt(w)), c_void_p(_ptr(rows)), c_int(R), c_int(H),
+        self._call("zlm_rmsnorm", self._p(out), c_int(_dt(out)), self._p(x),
+                   self._p(w), c_int(_dt(w)), self._p(rows), c_int(R), c_int(H),
                    c_float(eps), self._stream())
 
     def swiglu(self, out: torch.Tensor, gu: torch.Tensor) -> None:
@@ -140,7 +238,7 @@ class CudaKernels:
         T, I = out.shape
         assert gu.shape == (T, 2 * I) and gu.dtype == out.dtype
         assert out.is_contiguous() and gu.is_contiguous()
-        self._call("zlm_swiglu", c_void_p(out.data_ptr()), c_void_p(gu.data_ptr()), c_int(_dt(out)),
+        self._call("zlm_swiglu", self._p(out), self._p(gu), c_int(_dt(out)),
                    c_int(T), c_int(I), self._stream())
 
     def linear(self, out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, accumulate: bool = False,
@@ -159,8 +257,8 @@ class CudaKernels:
             assert out.dtype == torch.float32
         if x.dtype == torch.float32:
             assert out.dtype == torch.float32 and ldx == K
-            self._call("zlm_gemm_f32", c_void_p(out.data_ptr()), c_void_p(x.data_ptr()),
-                       c_void_p(w.data_ptr()), c_int(T), c_int(N), c_int(K), c_int(ldy),
+            self._call("zlm_gemm_f32", self._p(out), self._p(x),
+                       self._p(w), c_int(T), c_int(N), c_int(K), c_int(ldy),
                        c_int(1 if accumulate else 0), self._stream())
             return
         if x.dtype != torch.bfloat16:
@@ -182,12 +280,12 @@ class CudaKernels:
         if impl == "tc":
             ks = self.lib.zlm_gemm_tc_ksplit(T, N, K)
             scratch = self.scratch("gemm_tc.partials", ks * T * N, torch.float32, out.device) if ks > 1 else None
-            self._call("zlm_gemm_tc", c_void_p(out.data_ptr()), c_void_p(x.data_ptr()), c_void_p(w.data_ptr()),
-                       c_int(T), c_int(N), c_int(K), c_int(ldx), c_int(ldy), c_int(mode), c_void_p(_ptr(scratch)),
+            self._call("zlm_gemm_tc", self._p(out), self._p(x), self._p(w),
+                       c_int(T), c_int(N), c_int(K), c_int(ldx), c_int(ldy), c_int(mode), self._p(scratch),
                        self._stream())
             return
         name = {"gemv": "zlm_gemv_bf16", "mma": "zlm_gemm_bf16_mma"}[impl]
-        self._call(name, c_void_p(out.data_ptr()), c_void_p(x.data_ptr()), c_void_p(w.data_ptr()),
+        self._call(name, self._p(out), self._p(x), self._p(w),
                    c_int(T), c_int(N), c_int(K), c_int(ldx), c_int(ldy), c_int(mode), self._stream())
 
     def set_gemm_form(self, form: Optional[str] = None, width: int = 0) -> None:
@@ -239,61 +337,66 @@ class CudaKernels:
             assert pool is not None and pool.dtype == qkv.dtype and pool.is_contiguous()
             assert tuple(pool.shape[1:]) == (2, nkv, PAGE_TOKENS, hd)
             assert block_table is not None and block_table.dtype == torch.int32
-        self._call("zlm_qk_norm_rope_write", c_void_p(qkv.data_ptr()), c_int(_dt(qkv)), c_int(qkv.stride(0)),
-                   c_void_p(_ptr(q_w)), c_void_p(_ptr(k_w)), c_int(_dt(q_w) if has_norm else F32),
-                   c_int(1 if has_norm else 0), c_float(eps), c_void_p(_ptr(inv_freq)), c_int(n_rot),
-                   c_void_p(token_pos.data_ptr()), c_void_p(token_slot.data_ptr()),
-                   c_void_p(_ptr(block_table)), c_int(block_table.stride(0) if block_table is not None else 0),
-                   c_void_p(_ptr(pool)), c_int(nq), c_int(nkv), c_int(hd), c_int(1 if write else 0), c_int(T),
+        self._call("zlm_qk_norm_rope_write", self._p(qkv), c_int(_dt(qkv)), c_int(qkv.stride(0)),
+                   self._p(q_w), self._p(k_w), c_int(_dt(q_w) if has_norm else F32),
+                   c_int(1 if has_norm else 0), c_float(eps), self._p(inv_freq), c_int(n_rot),
+                   self._p(token_pos), self._p(token_slot),
+                   self._p(block_table), c_int(block_table.stride(0) if block_table is not None else 0),
+                   self._p(pool), c_int(nq), c_int(nkv), c_int(hd), c_int(1 if write else 0), c_int(T),
                    self._stream())
 
     def attention(self, out: torch.Tensor, q: torch.Tensor, pool: torch.Tensor, block_table: torch.Tensor,
                   token_pos: torch.Tensor, token_slot: torch.Tensor, nq: int, nkv: int, hd: int,
-                  scale: float, window: int, plan=None) -> None:
+                  scale: float, window: int, plan=None, len_bucket: Optional[int] = None) -> None:
         """out[t, h] = softmax(q[t, h] . K * scale) V over the keys [start, pos[t]] of the
-        token's slot; q may be a column view of the fused qkv buffer."""
+        token's slot; q may be a column view of the fused qkv buffer.  ``plan`` is the
+        step's context (one token per sequence: the split-KV kernel; whole prompts or
+        chunks: the flash kernels; none: the generic kernel); ``len_bucket`` is the longest
+        sequence in pages as ``attention_len_bucket`` rounds it (computed if absent)."""
         T = q.shape[0]
         assert out.shape == (T, nq * hd) and q.shape[1] == nq * hd and q.dtype == out.dtype == pool.dtype
         assert q.stride(1) == 1 and out.stride(1) == 1 and pool.is_contiguous()
         assert tuple(pool.shape[1:]) == (2, nkv, PAGE_TOKENS, hd)
         if (plan is not None and plan.is_decode and q.dtype == torch.bfloat16
                 and self.lib.zlm_attention_decode_supported(nq, nkv, hd)):
-            splits, per = decode_splits(T, nkv, plan.len_bucket, getattr(plan, "attention_blocks", None))
+            if len_bucket is None:
+                len_bucket = attention_len_bucket(plan.max_len)
+            splits, per = decode_splits(T, nkv, len_bucket, self.decode_blocks or self.sm_count * DECODE_BLOCKS_PER_SM)
             part_o = part_ml = None
             if splits > 1:
                 part_o = plan.scratch("attn.part_o", (T * nq * splits * hd,), torch.float32)
                 part_ml = plan.scratch("attn.part_ml", (T * nq * splits * 2,), torch.float32)
-            self._call("zlm_attention_decode", c_void_p(out.data_ptr()), c_int(out.stride(0)),
-                       c_void_p(q.data_ptr()), c_int(q.stride(0)), c_void_p(pool.data_ptr()),
-                       c_void_p(block_table.data_ptr()), c_int(block_table.stride(0)),
-                       c_void_p(token_pos.data_ptr()), c_void_p(token_slot.data_ptr()), c_int(T), c_int(nq),
+            self._call("zlm_attention_decode", self._p(out), c_int(out.stride(0)),
+                       self._p(q), c_int(q.stride(0)), self._p(pool),
+                       self._p(block_table), c_int(block_table.stride(0)),
+                       self._p(token_pos), self._p(token_slot), c_int(T), c_int(nq),
                        c_int(nkv), c_int(hd), c_float(scale), c_int(window), c_int(splits), c_int(per),
-                       c_void_p(_ptr(part_o)), c_void_p(_ptr(part_ml)), self._stream())
+                       self._p(part_o), self._p(part_ml), self._stream())
             return
         if (plan is not None and not plan.is_decode and q.dtype == torch.bfloat16
                 and getattr(plan, "cu_seqlens", None) is not None
                 and self.lib.zlm_attention_prefill_supported(nq, nkv, hd)):
             impl = getattr(plan, "attention_impl", None)
             if impl != "mma" and self.lib.zlm_attention_prefill_tc_supported(nq, nkv, hd, q.stride(0), out.stride(0)):
-                self._call("zlm_attention_prefill_tc", c_void_p(out.data_ptr()), c_int(out.stride(0)),
-                           c_void_p(q.data_ptr()), c_int(q.stride(0)), c_int(T), c_void_p(pool.data_ptr()),
-                           ctypes.c_longlong(pool.shape[0]), c_void_p(block_table.data_ptr()),
-                           c_int(block_table.stride(0)), c_void_p(plan.cu_seqlens.data_ptr()),
-                           c_void_p(plan.seq_slot.data_ptr()), c_void_p(plan.seq_start.data_ptr()), c_int(plan.R),
+                self._call("zlm_attention_prefill_tc", self._p(out), c_int(out.stride(0)),
+                           self._p(q), c_int(q.stride(0)), c_int(T), self._p(pool),
+                           ctypes.c_longlong(pool.shape[0]), self._p(block_table),
+                           c_int(block_table.stride(0)), self._p(plan.cu_seqlens),
+                           self._p(plan.seq_slot), self._p(plan.seq_start), c_int(plan.R),
                            c_int(plan.max_new), c_int(nq), c_int(nkv), c_int(hd), c_float(scale), c_int(window),
                            self._stream())
                 return
-            self._call("zlm_attention_prefill", c_void_p(out.data_ptr()), c_int(out.stride(0)),
-                       c_void_p(q.data_ptr()), c_int(q.stride(0)), c_void_p(pool.data_ptr()),
-                       c_void_p(block_table.data_ptr()), c_int(block_table.stride(0)),
-                       c_void_p(plan.cu_seqlens.data_ptr()), c_void_p(plan.seq_slot.data_ptr()),
-                       c_void_p(plan.seq_start.data_ptr()), c_int(plan.R), c_int(plan.max_new), c_int(nq),
+            self._call("zlm_attention_prefill", self._p(out), c_int(out.stride(0)),
+                       self._p(q), c_int(q.stride(0)), self._p(pool),
+                       self._p(block_table), c_int(block_table.stride(0)),
+                       self._p(plan.cu_seqlens), self._p(plan.seq_slot),
+                       self._p(plan.seq_start), c_int(plan.R), c_int(plan.max_new), c_int(nq),
                        c_int(nkv), c_int(hd), c_float(scale), c_int(window), self._stream())
             return
-        self._call("zlm_attention_generic", c_void_p(out.data_ptr()), c_int(out.stride(0)),
-                   c_void_p(q.data_ptr()), c_int(q.stride(0)), c_int(_dt(q)), c_void_p(pool.data_ptr()),
-                   c_void_p(block_table.data_ptr()), c_int(block_table.stride(0)),
-                   c_void_p(token_pos.data_ptr()), c_void_p(token_slot.data_ptr()), c_int(T), c_int(nq),
+        self._call("zlm_attention_generic", self._p(out), c_int(out.stride(0)),
+                   self._p(q), c_int(q.stride(0)), c_int(_dt(q)), self._p(pool),
+                   self._p(block_table), c_int(block_table.stride(0)),
+                   self._p(token_pos), self._p(token_slot), c_int(T), c_int(nq),
                    c_int(nkv), c_int(hd), c_float(scale), c_int(window), self._stream())
 
     def argmax(self, out: torch.Tensor, logits: torch.Tensor) -> None:
@@ -302,8 +405,8 @@ class CudaKernels:
         assert logits.dtype == torch.float32 and logits.stride(1) == 1 and out.dtype == torch.int32
         sv = self.scratch("argmax.values", R * 64, torch.float32, logits.device)
         si = self.scratch("argmax.indices", R * 64, torch.int32, logits.device)
-        self._call("zlm_argmax", c_void_p(out.data_ptr()), c_void_p(logits.data_ptr()), c_int(R), c_int(V),
-                   c_int(logits.stride(0)), c_void_p(sv.data_ptr()), c_void_p(si.data_ptr()), self._stream())
+        self._call("zlm_argmax", self._p(out), self._p(logits), c_int(R), c_int(V),
+                   c_int(logits.stride(0)), self._p(sv), self._p(si), self._stream())
 
     def set_pdl(self, on: bool) -> None:
         """Launch the decode-path kernels with programmatic dependent launch (a kernel's
@@ -312,14 +415,22 @@ class CudaKernels:
         self.lib.zlm_set_pdl(c_int(1 if on else 0))
 
     def gemm_tc_status(self) -> int:
-        """0 unless a bounded wait inside a tcgen05 kernel (product or attention) ever gave up
-        (synchronises)."""
-        return int(self.lib.zlm_gemm_tc_status()) or int(self.lib.zlm_attention_tc_status())
+        """0 unless a bounded wait inside a tcgen05 kernel (product or attention) gave up
+        since the status was last cleared (synchronises)."""
+        return self.status(sync=True)
 
-    def stream_status(self) -> int:
-        """0 unless a bounded wait inside the persistent decode kernel ever gave up
-        (synchronises)."""
-        return int(self.lib.zlm_stream_status())
+    def test_bounded_wait(self, limit_ns: int):
+        """Runs the tcgen05 kernels' give-up path on purpose, once, in a one-block kernel
+        made of the same helpers (a wait with the limit ``limit_ns`` on a barrier at which
+        nobody arrives), and returns (code it reported, other waits released by the abort
+        flag, nanoseconds the kernel took, its TMA copy had landed)."""
+        src = torch.zeros((128, 64), dtype=torch.bfloat16, device="cuda")
+        out = torch.zeros(4, dtype=torch.int32, device="cuda")
+        self._call("zlm_test_bounded_wait", self._p(src), self._p(out), ctypes.c_ulonglong(int(limit_ns)),
+                   self._stream())
+        torch.cuda.synchronize()
+        code, released, ns, landed = out.tolist()
+        return code, bool(released), ns, bool(landed)
 
     def sample(self, out: torch.Tensor, logits: torch.Tensor, temperature: float, top_k: int, top_p: float,
                seed: int, request: torch.Tensor, position: torch.Tensor, form: Optional[str] = None) -> None:
@@ -331,10 +442,10 @@ class CudaKernels:
         R, V = logits.shape
         assert logits.dtype == torch.float32 and logits.stride(1) == 1 and out.dtype == torch.int32
         assert request.dtype == torch.int32 and position.dtype == torch.int32
-        self._call("zlm_sample", c_void_p(out.data_ptr()), c_void_p(logits.data_ptr()), c_int(R), c_int(V),
+        self._call("zlm_sample", self._p(out), self._p(logits), c_int(R), c_int(V),
                    c_int(logits.stride(0)), c_float(temperature), c_int(top_k), c_float(top_p),
-                   ctypes.c_ulonglong(seed & 0xFFFFFFFFFFFFFFFF), c_void_p(request.data_ptr()),
-                   c_void_p(position.data_ptr()), c_int({None: 0, "block": 1, "cluster": 2}[form]), self._stream())
+                   ctypes.c_ulonglong(seed & 0xFFFFFFFFFFFFFFFF), self._p(request),
+                   self._p(position), c_int({None: 0, "block": 1, "cluster": 2}[form]), self._stream())
 
 
 _KERNELS: Optional[CudaKernels] = None

@@ -53,13 +53,17 @@ class GQAAttention(Mixer):
     def cache_request(self) -> Optional[CacheRequest]:
         return CacheRequest(self.nkv, self.hd, self.window)
 
-    @property
-    def kernels_only(self) -> bool:      # type: ignore[override]
-        return bool(getattr(self.position, "kernels_only", False))
-
     def attach(self, rt) -> None:
         super().attach(rt)
         self.position.attach(rt)
+
+    def step_key(self, ctx: StepContext):
+        # the decode kernel cuts the longest sequence's pages into parts: its grid, and with
+        # it a captured step, holds for one rounded length
+        if not ctx.is_decode:
+            return None
+        from ..kernels import attention_len_bucket
+        return ("gqa_attention", attention_len_bucket(ctx.max_len))
 
     def bind(self, params: Dict[str, torch.Tensor]) -> None:
         if self.kv_proj:
@@ -73,8 +77,20 @@ class GQAAttention(Mixer):
         self.w_o = params.pop("o_proj.weight")
         self.q_norm = params.pop("q_norm.weight", None)
         self.k_norm = params.pop("k_norm.weight", None)
+        self.check_products(q_proj=self.w_q, o_proj=self.w_o)
         if self.q_norm is not None and self.k_norm is not None and self.q_norm.dtype != self.k_norm.dtype:
             self.q_norm, self.k_norm = self.q_norm.float(), self.k_norm.float()
+
+    def tensors(self) -> Dict[str, torch.Tensor]:
+        out = {"q_proj.weight": self.w_q, "o_proj.weight": self.w_o}
+        if self.kv_proj:
+            out["k_proj.weight"] = self.w_qkv[self.Q: self.Q + self.KV]
+            out["v_proj.weight"] = self.w_qkv[self.Q + self.KV:]
+        if self.q_norm is not None:
+            out["q_norm.weight"] = self.q_norm
+        if self.k_norm is not None:
+            out["k_norm.weight"] = self.k_norm
+        return out
 
     # ---- the step -----------------------------------------------------------
     def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx: StepContext, io: LayerIO) -> None:
@@ -109,6 +125,8 @@ class GQAAttention(Mixer):
                 k.qk_norm_rope_write(qkv, None, None, self.eps, None, 0, ctx.token_pos, ctx.token_slot,
                                      tbl, pool, self.nq, nkv, self.hd)
         out = rt.ws.get("attn.out", (T, self.Q), rt.dtype)
+        key = self.step_key(ctx)
         k.attention(out, q, cache.pool, cache.block_table, ctx.token_pos, ctx.token_slot,
-                    self.nq, self.nkv, self.hd, self.scale, self.window, ctx)
+                    self.nq, self.nkv, self.hd, self.scale, self.window, ctx,
+                    len_bucket=key[1] if key else None)
         k.linear(residual, out, self.w_o, accumulate=True)

@@ -130,9 +130,7 @@ class StepContext:
     is_decode: bool = False
     max_new: int = 0
     max_len: int = 0          # longest sequence after this step
-    len_bucket: int = 1       # max_len in pages, rounded up (powers of two to 8, then multiples of 8)
     workspace: Any = None     # the runtime's Workspace
-    attention_blocks: Optional[int] = None    # blocks the decode attention sizes its splits for (None: its default)
     extras: Dict[str, Any] = field(default_factory=dict)
 
     def scratch(self, name: str, shape, dtype) -> torch.Tensor:
@@ -153,13 +151,38 @@ class Part:
     def bind(self, params: Dict[str, torch.Tensor]) -> None:
         """Takes the loaded tensors (by local name).  May fuse or re-lay them."""
 
+    def check_products(self, **weights: torch.Tensor) -> None:
+        """For ``bind``: refuses, when the model is built and not at its first step, a
+        weight whose sizes no product kernel takes."""
+        check = getattr(self.rt.k, "check_linear", None)
+        if check is not None:
+            for name, w in weights.items():
+                if w is not None:
+                    check(f"{type(self).__name__}.{name}", w)
+
+    def tensors(self) -> Dict[str, torch.Tensor]:
+        """The part's tensors by the local names of ``param_specs``, as they are used now:
+        the inverse of ``bind`` (a part that fused or re-laid tensors undoes it here).  The
+        default serves a part that keeps each tensor under an attribute of the name's
+        first component (``weight``, ``q_proj`` ...)."""
+        out = {}
+        for name in self.param_specs():
+            t = getattr(self, name.split(".")[0], None)
+            if isinstance(t, torch.Tensor):
+                out[name] = t
+        return out
+
     # a part whose forward launches only kernels (no host-side branching on
     # device data, no allocation) may be captured in a CUDA graph
     graph_safe = True
-    # a part whose forward does its device work through the methods of ``rt.k`` alone (no
-    # torch operation, no kernel of its own) can also be recorded as part of a program of
-    # the persistent decode kernel; a part has to say so itself
-    kernels_only = False
+
+    def step_key(self, ctx: "StepContext"):
+        """What about a step, beyond its numbers of tokens and sequences, changes the
+        launches this part makes (grid sizes, kernel choices): any hashable value, or
+        None if nothing does.  A captured decode step is replayed only for steps whose
+        keys are equal, so a part whose launches depend on, say, the longest sequence
+        returns that quantity here, rounded the way its launches round it."""
+        return None
 
 
 class Norm(Part):

@@ -30,9 +30,9 @@ class PreNormBlock(Part):
     def graph_safe(self) -> bool:      # type: ignore[override]
         return all(c.graph_safe for c in self.children().values())
 
-    @property
-    def kernels_only(self) -> bool:      # type: ignore[override]
-        return all(getattr(c, "kernels_only", False) for c in self.children().values())
+    def step_key(self, ctx: StepContext):
+        keys = tuple(k for k in (c.step_key(ctx) for c in self.children().values()) if k is not None)
+        return keys or None
 
     def forward(self, hidden: torch.Tensor, ctx: StepContext, io: LayerIO) -> None:
         rt = self.rt

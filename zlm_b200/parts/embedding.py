@@ -16,8 +16,6 @@ from .base import ParamSpec, Part
 
 @register_embedding("token_embedding")
 class TokenEmbedding(Part):
-    kernels_only = True
-
     def __init__(self, vocab_size: int, hidden_size: int):
         self.vocab, self.hidden = int(vocab_size), int(hidden_size)
         self.weight: Optional[torch.Tensor] = None
@@ -34,8 +32,6 @@ class TokenEmbedding(Part):
 
 @register_head("lm_head")
 class LMHead(Part):
-    kernels_only = True
-
     def __init__(self, vocab_size: int, hidden_size: int, tied: bool):
         self.vocab, self.hidden, self.tied = int(vocab_size), int(hidden_size), bool(tied)
         self.weight: Optional[torch.Tensor] = None
@@ -47,9 +43,11 @@ class LMHead(Part):
     def bind(self, params: Dict[str, torch.Tensor]) -> None:
         if not self.tied:
             self.weight = params["weight"]
+            self.check_products(weight=self.weight)
 
     def tie(self, table: torch.Tensor) -> None:
         self.weight = table
+        self.check_products(weight=self.weight)
 
     def forward(self, logits: torch.Tensor, x: torch.Tensor) -> None:
         """logits [R, vocab] fp32 = x [R, hidden] . W^T"""

@@ -16,8 +16,6 @@ from .base import FeedForward, ParamSpec, StepContext
 
 @register_feed_forward("swiglu")
 class SwiGLU(FeedForward):
-    kernels_only = True
-
     def __init__(self, hidden_size: int, intermediate_size: int):
         self.hidden = int(hidden_size)
         self.inter = int(intermediate_size)
@@ -39,6 +37,16 @@ class SwiGLU(FeedForward):
         else:
             self.w_gu = torch.cat([gate, up], dim=0).contiguous()
         self.w_down = params.pop("down_proj.weight")
+        self.check_products(gate_up_proj=self.w_gu, down_proj=self.w_down)
+
+    def tensors(self) -> Dict[str, torch.Tensor]:
+        I, K = self.inter, self.hidden
+        if self.fused:
+            gu = self.w_gu.view(I // 8, 2, 8, K)
+            gate, up = gu[:, 0].reshape(I, K), gu[:, 1].reshape(I, K)
+        else:
+            gate, up = self.w_gu[:I], self.w_gu[I:]
+        return {"gate_proj.weight": gate, "up_proj.weight": up, "down_proj.weight": self.w_down}
 
     def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx: StepContext) -> None:
         rt, k = self.rt, self.rt.k

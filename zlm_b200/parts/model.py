@@ -72,6 +72,22 @@ class DecoderModel:
         if getattr(self.head, "tied", False):
             self.head.tie(self.embedding.weight)
 
+    def tensor(self, name: str) -> torch.Tensor:
+        """The tensor that the checkpoint calls ``name``, as the model holds it now (the
+        compute dtype; fused projections are cut apart again)."""
+        for part, ps in self._owners:
+            for local in part.param_specs():
+                if ps.tensor_name(local) == name:
+                    got = part.tensors().get(local)
+                    if got is None and local == "weight" and getattr(part, "tied", False):
+                        got = getattr(part, "weight", None)
+                    if got is not None:
+                        return got
+        raise KeyError(f"the model has no tensor '{name}'")
+
+    def tensor_names(self) -> List[str]:
+        return sorted(self.param_specs())
+
     # ---- what the cache has to provide -----------------------------------
     def cache_requests(self) -> List[Optional[CacheRequest]]:
         """Per schedule entry."""
@@ -84,11 +100,15 @@ class DecoderModel:
     def graph_safe(self) -> bool:
         return all(b.graph_safe for b in self.blocks)
 
-    @property
-    def kernels_only(self) -> bool:
-        """Every part does its device work through the kernel object alone."""
-        parts = list(self.blocks) + [self.embedding, self.final_norm, self.head]
-        return all(getattr(p, "kernels_only", False) for p in parts)
+    def step_key(self, ctx: StepContext) -> Tuple:
+        """The parts' say on which steps make the same launches (``Part.step_key``): the
+        distinct keys of all parts, in the order of their first appearance."""
+        seen: List = []
+        for p in list(self.blocks) + [self.embedding, self.final_norm, self.head]:
+            k = p.step_key(ctx)
+            if k is not None and k not in seen:
+                seen.append(k)
+        return tuple(seen)
 
     # ---- the step -------------------------------------------------------------
     def forward(self, ctx: StepContext, ios: List[LayerIO]) -> torch.Tensor:

@@ -15,8 +15,6 @@ from .base import Norm, ParamSpec
 
 @register_norm("rms_norm")
 class RMSNorm(Norm):
-    kernels_only = True
-
     def __init__(self, size: int, eps: float):
         self.size = int(size)
         self.eps = float(eps)

@@ -18,8 +18,6 @@ from .base import PositionEncoding, StepContext
 
 @register_position_encoding("rope_half_split")
 class RotaryHalfSplit(PositionEncoding):
-    kernels_only = True
-
     fused = True      # applied inside the attention mixer's norm/rotate/write kernel
 
     def __init__(self, theta: float, head_dim: int, n_rot: Optional[int] = None):
@@ -39,8 +37,6 @@ class RotaryHalfSplit(PositionEncoding):
 
 @register_position_encoding("none")
 class NoPosition(PositionEncoding):
-    kernels_only = True
-
     fused = True
     inv_freq = None
     n_rot = 0
