@@ -94,3 +94,72 @@ def test_schedule_may_repeat_a_layer_and_share_a_cache():
     assert float((torch.cat(parts) - whole).abs().max()) < 1e-5
     # and it is not the plain two-layer model
     assert float((whole - plain_logits(t, cfg, p)).abs().max()) > 1e-3
+
+
+def test_a_place_named_twice_is_refused():
+    eng, cfg, _ = build("A", max_tokens=128, max_batch=2, max_step_tokens=4)
+    s = eng.new_sequence()
+    with pytest.raises(StepError, match="may be named once"):
+        eng.step([StepEntry(s, [1, 2], [0, 1, 1])])
+    assert eng.length(s) == 0
+
+
+class ReportingKernels(PlainKernels):
+    """Plain kernels with the CUDA library's status word: ``pending`` stands for a mark that
+    a kernel's bounded wait left there."""
+    pending = 0
+
+    def check_status(self, sync=False):
+        from zlm_b200.kernels import KernelError
+        if self.pending:
+            code, self.pending = self.pending, 0
+            raise KernelError(f"a bounded wait inside a kernel gave up (status {code:#x})")
+
+
+def test_a_reported_give_up_raises_where_the_host_waits_anyway():
+    from zlm_b200.kernels import KernelError
+    cfg = config_from_dict(TINY["A"])
+    t = random_tensors(DecoderModel(cfg.to_model_spec()).param_specs(), 2)
+    k = ReportingKernels()
+    eng = Engine(cfg, dict(t), torch.float32, "cpu", kernels=k, max_tokens=512)
+    assert len(eng.generate([[1, 2, 3], [4, 5]], max_tokens=3).tokens[0]) == 3
+    # reported during a prefill: generate raises, and gives its slots back
+    k.pending = 0x102
+    with pytest.raises(KernelError, match="gave up"):
+        eng.generate([[1, 2, 3], [4, 5]], max_tokens=3)
+    assert eng.cache.slots.held == 0
+    # reported during a decode step: the fetch of that step raises
+    s = eng.new_sequence()
+    eng.step([StepEntry(s, [1, 2, 3], [])])
+    k.pending = 0x203
+    from zlm_b200.sampling import SamplingParams
+    h = eng.decode_launch([s], [4], SamplingParams(), [0])
+    with pytest.raises(KernelError, match="0x203"):
+        eng.decode_fetch(h)
+    # reported by a step whose logits the caller has not read yet: the next step says so
+    k.pending = 0x101
+    with pytest.raises(KernelError, match="0x101"):
+        eng.step([StepEntry(s, [5], [0])])
+    assert eng.step([StepEntry(s, [5], [0])] ) is not None
+    eng.release(s)
+
+
+def test_tensors_can_be_read_back_by_their_checkpoint_names():
+    eng, cfg, t = build("B")
+    names = eng.model.tensor_names()
+    assert set(names) == set(t)
+    for n in names:
+        assert torch.equal(eng.tensor(n).float(), t[n].float()), n
+    with pytest.raises(KeyError, match="no tensor"):
+        eng.tensor("model.layers.99.mlp.up_proj.weight")
+    tied, cfg_a, ta = build("A")
+    assert torch.equal(tied.tensor("lm_head.weight"), ta["model.embed_tokens.weight"])
+
+
+def test_a_width_that_no_bf16_kernel_takes_is_refused_when_the_model_is_built():
+    from zlm_b200.kernels import CudaKernels, KernelError
+    w = torch.zeros((16, 36), dtype=torch.bfloat16)
+    with pytest.raises(KernelError, match=r"SwiGLU.down_proj \[16, 36\].*multiple of 8"):
+        CudaKernels.check_linear(None, "SwiGLU.down_proj", w)
+    CudaKernels.check_linear(None, "x", torch.zeros((16, 36)))            # 32-bit: any width
+    CudaKernels.check_linear(None, "x", torch.zeros((16, 40), dtype=torch.bfloat16))

@@ -78,3 +78,57 @@ def test_layer_sizes_of_the_benchmark(model, dtype):
         assert_close(eng.decoder.last_logits.clone(), ref[t:t + 1], dtype, f"layer sizes decode {t} {dtype}", TOL_8B[dtype])
     if dtype == "bfloat16":
         assert eng.rt.k.gemm_tc_status() == 0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_unequal_sequences_chunks_and_reused_slots_at_head_size_128(dtype):
+    """Three sequences of unequal lengths prefilled as one step, one of them continued by a
+    chunk while the others decode... (the tcgen05 flash attention with a cached prefix and
+    the split-KV decode attention at head size 128 inside one model), the shortest ending
+    early; then a second batch in the slots and pages the first gave back."""
+    from zlm_b200 import Engine, StepEntry
+    from zlm_b200.engine import parse_dtype
+    from zlm_b200.parts.model import DecoderModel
+    from zlm_b200.registry import config_from_dict
+    from zlm_b200.sampling import SamplingParams
+    from zlm_b200.weights import random_tensors
+    from zlm_b200.weights.loader import target_dtype
+    cfg = config_from_dict(dict(SIZES_8B, num_hidden_layers=1, vocab_size=2048))
+    tensors = random_tensors(DecoderModel(cfg.to_model_spec()).param_specs(), 6, "cpu", torch.float32)
+    ref_t = reference_tensors(tensors, dtype)
+    dt = parse_dtype(dtype)
+    specs = DecoderModel(cfg.to_model_spec()).param_specs()
+    dev = {n: t.to("cuda").to(target_dtype(specs[n], t.dtype, dt)) for n, t in tensors.items()}
+    eng = Engine(cfg, dev, dt, "cuda:0", max_tokens=64 * 12, max_batch=3)
+    tol = TOL_8B[dtype]
+    for b, lens in enumerate(([200, 77, 129], [64, 260, 1])):
+        full = random_prompts(cfg.vocab_size, [n + 8 for n in lens], seed=20 + b)
+        want = [plain_logits(ref_t, cfg, p) for p in full]
+        slots = [eng.new_sequence() for _ in full]
+        assert sorted(slots) == [0, 1, 2]
+        # unequal prompts as one step; the longest is cut: its first part now, the rest as a chunk
+        cut = [min(n, 130) for n in lens]
+        got = eng.step([StepEntry(s, p[:c], [c - 1]) for s, p, c in zip(slots, full, cut)]).clone()
+        for j in range(3):
+            assert_close(got[j], want[j][cut[j] - 1], dtype, f"batch {b} row {j} first part", tol)
+        j_long = max(range(3), key=lambda j: lens[j])
+        rest = list(range(cut[j_long], lens[j_long]))
+        got = eng.step([StepEntry(slots[j_long], [full[j_long][t] for t in rest], list(range(len(rest))))]).clone()
+        assert_close(got, want[j_long][rest[0]:rest[-1] + 1], dtype, f"batch {b} continued chunk", tol)
+        # decode: all three, then without the shortest (it ends early and gives its slot back)
+        j_short = min(range(3), key=lambda j: lens[j])
+        for step in range(8):
+            live = [j for j in range(3) if not (j == j_short and step >= 3)]
+            if step == 3:
+                eng.release(slots[j_short])
+            eng.decoder.step([slots[j] for j in live], [full[j][lens[j] + step] for j in live], SamplingParams())
+            got = eng.decoder.last_logits[:len(live)].clone()
+            for r, j in enumerate(live):
+                assert_close(got[r], want[j][lens[j] + step], dtype, f"batch {b} row {j} decode {step}", tol)
+        for j in range(3):
+            if j != j_short:
+                eng.release(slots[j])
+        eng.cache.check()
+    assert eng.cache.slots.held == 0
+    if dtype == "bfloat16":
+        assert eng.rt.k.gemm_tc_status() == 0

@@ -144,6 +144,8 @@ class DecodeRunner:
 
     # ------------------------------------------------------------------ device work
     def _pdl(self, R: int) -> bool:
+        if not hasattr(self.e.rt.k, "set_pdl"):
+            return False
         return self.use_pdl if self.use_pdl is not None else R <= 16
 
     def _device_work(self, ctx, R: int, params: SamplingParams) -> None:
@@ -178,10 +180,10 @@ class DecodeRunner:
         key = (R, e.model.step_key(ctx), params, self._pdl(R))
         if self.graph_generation != self._generation():
             self.graphs.clear()
-        g = self.graphs.get(key)
-        if g is not None:
+        entry = self.graphs.get(key)
+        if entry is not None:
             self.graphs.move_to_end(key)
-        if g is None:
+        if entry is None:
             # a first eager run creates every scratch buffer the step needs; it also is
             # this step's result, so nothing is computed twice on replayed steps
             self._device_work(ctx, R, params)
@@ -208,10 +210,11 @@ class DecodeRunner:
             if gen != self._generation():
                 raise RuntimeError("scratch buffers moved during graph capture")
             self.graph_generation = gen
-            self.graphs[key] = g
+            self.graphs[key] = (g, self.last_logits)
             while len(self.graphs) > MAX_GRAPHS:
                 self.graphs.popitem(last=False)
             # the capture did not run the kernels; the eager run above already did
             return
+        g, self.last_logits = entry          # the logits of these rows, where this graph leaves them
         g.replay()
         self.replays += 1
