@@ -27,6 +27,7 @@ __device__ __forceinline__ void attention_decode_item(
     const int g = lane >> 2, qd = lane & 3;
     const int G = nq / nkv;
     if (PDL) pdl_launch_dependents();
+    if (!ZLM_CHK(token_pos + t, 4) || !ZLM_CHK(token_slot + t, 4)) return;      // block-uniform
     const int pos = token_pos[t];
     const int slot = token_slot[t];
     const int seq = pos + 1;
@@ -44,6 +45,7 @@ __device__ __forceinline__ void attention_decode_item(
     if (PDL) pdl_wait();          // q and this step's keys and values come from the kernel before
     // the pages do not depend on q: start them now, they land while q is fetched
     auto load_page = [&](int p, int stage) {
+        if (!ZLM_CHK(pages + p, 4)) return;
         const __nv_bfloat16* kb = pool + (size_t)pages[p] * page_stride + (size_t)kvh * TILE;
         const __nv_bfloat16* vb = kb + v_off;
         __nv_bfloat16* ks_ = Ks + stage * TILE;
@@ -60,11 +62,12 @@ __device__ __forceinline__ void attention_decode_item(
     if (p_begin + 1 < p_end) load_page(p_begin + 1, 1);
     dec_commit();
     // Q fragments: row i of the 16-row tile is head kvh*G + i (zero beyond the group)
-    unsigned qf[KS][4];
+    unsigned qf[KS][4] = {};
     {
         const __nv_bfloat16* qt = q + (size_t)t * q_stride + (size_t)kvh * G * HD;
+        const bool q_ok = ZLM_CHK(qt, (size_t)G * HD * 2);
 #pragma unroll
-        for (int ks = 0; ks < KS; ++ks) {
+        for (int ks = 0; ks < KS && q_ok; ++ks) {
             const int c = ks * 16 + qd * 2;
             qf[ks][0] = g < G ? *(const unsigned*)(qt + (size_t)g * HD + c) : 0u;
             qf[ks][1] = g + 8 < G ? *(const unsigned*)(qt + (size_t)(g + 8) * HD + c) : 0u;
@@ -202,11 +205,12 @@ __device__ __forceinline__ void attention_decode_item(
         }
         const int head = kvh * G + row;
         if (splits == 1) {
-            out[(size_t)t * out_stride + (size_t)head * HD + d] = __float2bfloat16_rn(O / L);
+            if (ZLM_CHK(out + (size_t)t * out_stride + (size_t)head * HD + d, 2))
+                out[(size_t)t * out_stride + (size_t)head * HD + d] = __float2bfloat16_rn(O / L);
         } else {
             const size_t pi = ((size_t)t * nq + head) * splits + split;
-            part_o[pi * HD + d] = O;
-            if (d == 0) { part_ml[pi * 2] = M; part_ml[pi * 2 + 1] = L; }
+            if (ZLM_CHK(part_o + pi * HD + d, 4)) part_o[pi * HD + d] = O;
+            if (d == 0 && ZLM_CHK(part_ml + pi * 2, 8)) { part_ml[pi * 2] = M; part_ml[pi * 2 + 1] = L; }
         }
     }
 }
@@ -221,11 +225,15 @@ __device__ __forceinline__ void attention_decode_combine_item(
     float* fs, float* red, const int tid, const GroupSync gs, const int t, const int head, __nv_bfloat16* out,
     int out_stride, const float* part_o, const float* part_ml, const int* token_pos, int nq, int hd, int splits,
     int per, int window) {
+    if (!ZLM_CHK(token_pos + t, 4)) return;
     const int pos = token_pos[t];
     const int t_start = (window != 0 && pos + 1 > window) ? pos + 1 - window : 0;
     const int pages = pos / ZLM_PAGE + 1 - t_start / ZLM_PAGE;
     const int used = min(splits, (pages + per - 1) / per);
     const size_t base = ((size_t)t * nq + head) * splits;
+    if (!ZLM_CHK(part_ml + base * 2, (size_t)used * 8) || !ZLM_CHK(part_o + base * hd, (size_t)used * hd * 4) ||
+        !ZLM_CHK(out + (size_t)t * out_stride + (size_t)head * hd, (size_t)hd * 2))
+        return;
     float m = -INFINITY;
     for (int s = tid; s < used; s += COMB_THREADS) m = fmaxf(m, part_ml[(base + s) * 2]);
     const float M = group_max(m, red, tid, gs);

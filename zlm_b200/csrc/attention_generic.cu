@@ -29,6 +29,7 @@ attention_generic_kernel(TA* __restrict__ out, int out_stride, const TA* __restr
     const int t = blockIdx.x, h = blockIdx.y;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int kvh = h / (nq / nkv);
+    if (!ZLM_CHK(token_pos + t, 4) || !ZLM_CHK(token_slot + t, 4)) return;
     const int pos = token_pos[t];
     const int slot = token_slot[t];
     const int seq = pos + 1;
@@ -38,6 +39,9 @@ attention_generic_kernel(TA* __restrict__ out, int out_stride, const TA* __restr
     const size_t v_off = (size_t)nkv * ZLM_PAGE * hd;
 
     const TA* qp = q + (size_t)t * q_stride + (size_t)h * hd;
+    if (!ZLM_CHK(qp, (size_t)hd * sizeof(TA)) ||
+        !ZLM_CHK(out + (size_t)t * out_stride + (size_t)h * hd, (size_t)hd * sizeof(TA)))
+        return;
     for (int e = threadIdx.x; e < hd; e += blockDim.x) qs[e] = to_f32(qp[e]);
     __syncthreads();
 
@@ -51,8 +55,12 @@ attention_generic_kernel(TA* __restrict__ out, int out_stride, const TA* __restr
         // chunk c holds keys [32c, 32c+32); chunk c belongs to warp c % ATT_WARPS
         const int key = c * 32 + lane;
         const bool valid = key >= t_start && key <= pos;
+        if (!ZLM_CHK(pages + (c * 32) / ZLM_PAGE, 4)) continue;
         const int page = pages[(c * 32) / ZLM_PAGE];
         const TA* kbase = pool + (size_t)page * page_stride + (size_t)kvh * ZLM_PAGE * hd;
+        // this head's 64 keys and 64 values of the page
+        if (!ZLM_CHK(kbase, (size_t)ZLM_PAGE * hd * sizeof(TA)) || !ZLM_CHK(kbase + v_off, (size_t)ZLM_PAGE * hd * sizeof(TA)))
+            continue;
         float s = -INFINITY;
         if (valid) {
             const TA* kr = kbase + (size_t)(key % ZLM_PAGE) * hd;

@@ -33,6 +33,7 @@ attention_prefill_kernel(__nv_bfloat16* __restrict__ out, int out_stride, const 
 
     const int r = blockIdx.x / tiles_per_seq, b = blockIdx.x % tiles_per_seq;
     const int head = blockIdx.y;
+    if (!ZLM_CHK(cu_seqlens + r, 8) || !ZLM_CHK(seq_start + r, 4) || !ZLM_CHK(seq_slot + r, 4)) return;   // block-uniform
     const int tok0 = cu_seqlens[r], n_new = cu_seqlens[r + 1] - tok0;
     const int row0 = b * PRE_BM;
     if (row0 >= n_new) return;
@@ -47,7 +48,14 @@ attention_prefill_kernel(__nv_bfloat16* __restrict__ out, int out_stride, const 
 
     // positions of this thread's two rows; rows beyond the tile's tokens are idle
     const int i0 = warp * 16 + g, i1 = i0 + 8;
-    const bool ok0 = i0 < rows, ok1 = i1 < rows;
+    bool ok0 = i0 < rows, ok1 = i1 < rows;
+#ifdef ZLM_BOUNDS_CHECK
+    // a row whose query or output lies outside the tensors passed is treated as idle
+    ok0 = ok0 && ZLM_CHK(q + (size_t)(tok0 + row0 + i0) * q_stride + (size_t)head * HD, HD * 2) &&
+          ZLM_CHK(out + (size_t)(tok0 + row0 + i0) * out_stride + (size_t)head * HD, HD * 2);
+    ok1 = ok1 && ZLM_CHK(q + (size_t)(tok0 + row0 + i1) * q_stride + (size_t)head * HD, HD * 2) &&
+          ZLM_CHK(out + (size_t)(tok0 + row0 + i1) * out_stride + (size_t)head * HD, HD * 2);
+#endif
     const int pos0 = start + row0 + i0, pos1 = start + row0 + i1;
     const int lo0 = (window != 0 && pos0 + 1 > window) ? pos0 + 1 - window : 0;
     const int lo1 = (window != 0 && pos1 + 1 > window) ? pos1 + 1 - window : 0;
@@ -81,6 +89,7 @@ attention_prefill_kernel(__nv_bfloat16* __restrict__ out, int out_stride, const 
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
 
     auto load_page = [&](int p, int stage) {
+        if (!ZLM_CHK(pages + p, 4)) return;
         const __nv_bfloat16* kb = pool + (size_t)pages[p] * page_stride + (size_t)kvh * TILE;
         const __nv_bfloat16* vb = kb + v_off;
         __nv_bfloat16* ks_ = Ks + stage * TILE;

@@ -77,6 +77,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const int rank = blockIdx.x / n_hb;        // 0 = the last tile of a sequence
     const int b = tiles_per_seq - 1 - rank / R, r = rank % R;
     const int head0 = (blockIdx.x % n_hb) * HPC;   // the block's first query head; its heads share a kv head
+    if (!ZLM_CHK(cu_seqlens + r, 8) || !ZLM_CHK(seq_start + r, 4) || !ZLM_CHK(seq_slot + r, 4)) return;   // block-uniform
     const int tok0 = cu_seqlens[r], n_new = cu_seqlens[r + 1] - tok0;
     const int row0 = b * FA_BM;
     if (row0 >= n_new) return;
@@ -120,7 +121,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             for (int j = 0; j < NP; ++j) {
                 const int s = j % FA_STAGES;
                 if (!mbar_wait(&kv_empty[s], ((j / FA_STAGES) & 1) ^ 1, abort_flag, 1)) break;
-                const int page = pages[page_lo + j];
+                const int page = ZLM_CHK(pages + page_lo + j, 4) ? pages[page_lo + j] : 0;
                 const int krow = ((page * 2 + 0) * nkv + kvh) * ZLM_PAGE;
                 const int vrow = ((page * 2 + 1) * nkv + kvh) * ZLM_PAGE;
                 mbar_expect_tx(&kv_full[s], 2 * KV_BYTES);
@@ -295,7 +296,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             for (int c = 0; c < FA_HD; c += 16) {
                 float ov[16];
                 tc_ld16(tmem_o + lane_addr + c, ov);
-                if (row_ok) {
+                if (row_ok && ZLM_CHK(orow + c, 32)) {
                     uint4 a, bq;
                     a.x = fa_pack(ov[0] * inv, ov[1] * inv); a.y = fa_pack(ov[2] * inv, ov[3] * inv);
                     a.z = fa_pack(ov[4] * inv, ov[5] * inv); a.w = fa_pack(ov[6] * inv, ov[7] * inv);

@@ -5,6 +5,7 @@
 #include "common.cuh"
 
 __device__ __forceinline__ void dec_cp_async16(void* smem, const void* gmem) {
+    if (!ZLM_CHK(gmem, 16)) return;
     const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gmem));
 }

@@ -4,6 +4,13 @@ The library is plain CUDA behind ``extern "C"`` entry points (no torch headers),
 so a cold build is a handful of nvcc calls run in parallel.  It is rebuilt when
 a source changed (content hash), and a line is printed for every file so that a
 first call that has to compile shows progress.
+
+Two variants: the ordinary library, and ``variant="check"``, the bounds-check build
+(``-DZLM_BOUNDS_CHECK``, ``libzlm_b200_check.so``), in which every global-memory
+access of the hand-written kernels is first compared with the tensors the caller
+passed; an access outside them is counted, recorded and skipped (nothing traps).
+It stands where a memory checker would: ``python -m zlm_b200.csrc.build check``
+builds it, ``CudaKernels(variant="check")`` loads it.
 """
 from __future__ import annotations
 
@@ -22,7 +29,19 @@ LIB_NAME = "libzlm_b200.so"
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
     "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=default",
-] + os.environ.get("ZLM_B200_NVCC_FLAGS", "").split()      # extra flags, e.g. -DNAME, for experiments
+]
+# variant -> (library name, object folder, extra nvcc flags)
+VARIANTS = {
+    "": (LIB_NAME, "_build", []),
+    "check": ("libzlm_b200_check.so", "_build_check", ["-DZLM_BOUNDS_CHECK"]),
+}
+
+
+def _variant(variant: str):
+    try:
+        return VARIANTS[variant or ""]
+    except KeyError:
+        raise ValueError(f"unknown build variant {variant!r}; known: {sorted(VARIANTS)}") from None
 
 
 def _say(msg: str) -> None:
@@ -33,14 +52,14 @@ def sources() -> List[str]:
     return sorted(f for f in os.listdir(HERE) if f.endswith(".cu"))
 
 
-def source_hash() -> str:
+def source_hash(variant: str = "") -> str:
     h = hashlib.sha256()
     for f in sorted(os.listdir(HERE)):
         if f.endswith((".cu", ".cuh", ".h")):
             h.update(f.encode())
             with open(os.path.join(HERE, f), "rb") as fh:
                 h.update(fh.read())
-    h.update(" ".join(NVCC_FLAGS).encode())
+    h.update(" ".join(NVCC_FLAGS + _variant(variant)[2]).encode())
     return h.hexdigest()
 
 
@@ -65,10 +84,11 @@ def _writable(d: str) -> bool:
         return False
 
 
-def library_path(build_if_needed: bool = True, verbose: bool = True) -> str:
+def library_path(build_if_needed: bool = True, verbose: bool = True, variant: str = "") -> str:
     """Path of an up-to-date kernel library, building it first if needed."""
-    want = source_hash()
-    lib = os.path.join(HERE, LIB_NAME)
+    lib_name, obj_name, extra = _variant(variant)
+    want = source_hash(variant)
+    lib = os.path.join(HERE, lib_name)
     stamp = lib + ".hash"
     if os.path.isfile(lib) and os.path.isfile(stamp):
         with open(stamp) as f:
@@ -77,21 +97,21 @@ def library_path(build_if_needed: bool = True, verbose: bool = True) -> str:
     if not build_if_needed:
         raise RuntimeError(f"{lib} is missing or stale")
     out_dir = HERE
-    if not _writable(os.path.join(HERE, "_build")):
+    if not _writable(os.path.join(HERE, obj_name)):
         out_dir = os.path.join(tempfile.gettempdir(), f"zlm_b200_{os.getuid()}_{want[:16]}")
-        lib = os.path.join(out_dir, LIB_NAME)
+        lib = os.path.join(out_dir, lib_name)
         stamp = lib + ".hash"
         if os.path.isfile(lib) and os.path.isfile(stamp):
             return lib
-    build(out_dir, lib, verbose)
+    build(out_dir, lib, verbose, obj_name, extra)
     with open(stamp, "w") as f:
         f.write(want)
     return lib
 
 
-def build(out_dir: str, lib: str, verbose: bool = True) -> None:
+def build(out_dir: str, lib: str, verbose: bool = True, obj_name: str = "_build", extra_flags=()) -> None:
     nvcc = find_nvcc()
-    obj_dir = os.path.join(out_dir, "_build")
+    obj_dir = os.path.join(out_dir, obj_name)
     os.makedirs(obj_dir, exist_ok=True)
     srcs = sources()
     t0 = time.time()
@@ -100,7 +120,7 @@ def build(out_dir: str, lib: str, verbose: bool = True) -> None:
 
     def compile_one(src: str) -> str:
         obj = os.path.join(obj_dir, src[:-3] + ".o")
-        cmd = [nvcc, *NVCC_FLAGS, "-I", HERE, "-c", os.path.join(HERE, src), "-o", obj]
+        cmd = [nvcc, *NVCC_FLAGS, *extra_flags, "-I", HERE, "-c", os.path.join(HERE, src), "-o", obj]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError(f"nvcc failed on {src}:\n{r.stdout}\n{r.stderr}")
@@ -124,4 +144,4 @@ def build(out_dir: str, lib: str, verbose: bool = True) -> None:
 
 
 if __name__ == "__main__":
-    print(library_path())
+    print(library_path(variant=sys.argv[1] if len(sys.argv) > 1 else ""))

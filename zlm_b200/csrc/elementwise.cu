@@ -41,6 +41,7 @@ __global__ void embed_kernel(float* __restrict__ out, const TW* __restrict__ tab
     pdl_trigger();
     const int t = blockIdx.x;
     pdl_wait();                 // the ids may be what the previous step's sampler wrote
+    if (!ZLM_CHK(ids + t, 4) || !ZLM_CHK(out + (size_t)t * H, (size_t)H * 4)) return;
     embed_row(out + (size_t)t * H, table, ids[t], H, V, threadIdx.x, blockDim.x);
 }
 
@@ -69,8 +70,12 @@ __global__ void rmsnorm_kernel(TO* __restrict__ out, const float* __restrict__ x
     __shared__ float red[32];
     pdl_trigger();
     const int r = blockIdx.x;
+    if (rows && !ZLM_CHK(rows + r, 4)) return;
     const int src = rows ? rows[r] : r;
     pdl_wait();
+    if (!ZLM_CHK(x + (size_t)src * H, (size_t)H * 4) || !ZLM_CHK(out + (size_t)r * H, (size_t)H * sizeof(TO)) ||
+        !ZLM_CHK(w.p, (size_t)H * (w.dtype == ZLM_DTYPE_F32 ? 4 : 2)))
+        return;
     rmsnorm_row<TO, 1>(out + (size_t)r * H, x + (size_t)src * H, w, H, eps, red, threadIdx.x,
                        GroupSync{0, (int)blockDim.x}, blockDim.x);
 }
@@ -114,6 +119,9 @@ __global__ void swiglu_kernel(TA* __restrict__ out, const TA* __restrict__ gu, i
          e += (size_t)gridDim.x * blockDim.x) {
         const size_t t = e / I;
         const int i = (int)(e - t * I);
+        if (!ZLM_CHK(&gu[t * 2 * I + i], sizeof(TA)) || !ZLM_CHK(&gu[t * 2 * I + I + i], sizeof(TA)) ||
+            !ZLM_CHK(&out[e], sizeof(TA)))
+            continue;
         const float g = to_f32(gu[t * 2 * I + i]);
         const float u = to_f32(gu[t * 2 * I + I + i]);
         out[e] = from_f32<TA>((g / (1.0f + expf(-g))) * u);

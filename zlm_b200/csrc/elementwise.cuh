@@ -10,6 +10,7 @@ __device__ __forceinline__ void embed_row(float* o, const TW* table, int id, int
     // outside the table
     id = id < 0 ? 0 : (id >= V ? V - 1 : id);
     const TW* row = table + (size_t)id * H;
+    if (!ZLM_CHK(row, (size_t)H * sizeof(TW))) return;
     if (sizeof(TW) == 2 && H % 8 == 0) {
         // 16-byte loads, two 16-byte stores
         for (int c = tid; c < H / 8; c += nthreads) {

@@ -14,7 +14,7 @@
 
 __device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
     const unsigned s = (unsigned)__cvta_generic_to_shared(smem);
-    const int n = valid ? 16 : 0;
+    const int n = (valid && ZLM_CHK(gmem, 16)) ? 16 : 0;
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(s), "l"(gmem), "r"(n));
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
@@ -39,6 +39,7 @@ __device__ __forceinline__ void mma_bf16(float* c, const unsigned* a, unsigned b
 // MODE 0: Y bf16 = acc; MODE 1: Y fp32 += acc; MODE 2: Y fp32 = acc
 template <int MODE>
 __device__ __forceinline__ void store_out(void* Y, size_t idx, float v) {
+    if (!ZLM_CHK((char*)Y + idx * (MODE == 0 ? 2 : 4), MODE == 0 ? 2 : 4)) return;
     if (MODE == 0) ((__nv_bfloat16*)Y)[idx] = __float2bfloat16_rn(v);
     else if (MODE == 1) ((float*)Y)[idx] += v;
     else if (MODE == 2) ((float*)Y)[idx] = v;
@@ -141,8 +142,9 @@ gemm_bf16_mma_kernel(void* __restrict__ Y, const __nv_bfloat16* __restrict__ X,
 #pragma unroll
                     for (int e = 0; e < 2; ++e) {
                         const float gt = acc[i][j][half * 2 + e], up = acc[i][j + 1][half * 2 + e];
-                        ((__nv_bfloat16*)Y)[(size_t)m * ldy + n / 2 + q * 2 + e] =
-                            __float2bfloat16_rn((gt / (1.0f + expf(-gt))) * up);
+                        if (ZLM_CHK((__nv_bfloat16*)Y + (size_t)m * ldy + n / 2 + q * 2 + e, 2))
+                            ((__nv_bfloat16*)Y)[(size_t)m * ldy + n / 2 + q * 2 + e] =
+                                __float2bfloat16_rn((gt / (1.0f + expf(-gt))) * up);
                     }
                 }
             }

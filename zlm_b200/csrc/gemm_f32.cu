@@ -32,8 +32,8 @@ gemm_f32_kernel(float* __restrict__ Y, const float* __restrict__ X, const float*
         for (int p = 0; p < 4; ++p) {
             const int r = lr + 16 * p;
             const int gm = m0 + r, gn = n0 + r, gk = k0 + lk;
-            Xs[lk][r] = (gm < T && gk < K) ? X[(size_t)gm * K + gk] : 0.f;
-            Ws[lk][r] = (gn < N && gk < K) ? W[(size_t)gn * K + gk] : 0.f;
+            Xs[lk][r] = (gm < T && gk < K && ZLM_CHK(X + (size_t)gm * K + gk, 4)) ? X[(size_t)gm * K + gk] : 0.f;
+            Ws[lk][r] = (gn < N && gk < K && ZLM_CHK(W + (size_t)gn * K + gk, 4)) ? W[(size_t)gn * K + gk] : 0.f;
         }
         __syncthreads();
 #pragma unroll
@@ -57,7 +57,7 @@ gemm_f32_kernel(float* __restrict__ Y, const float* __restrict__ X, const float*
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int gn = n0 + tx * 4 + j;
-            if (gn >= N) continue;
+            if (gn >= N || !ZLM_CHK(Y + (size_t)gm * ldy + gn, 4)) continue;
             float* y = Y + (size_t)gm * ldy + gn;
             if (MODE == 0) *y = acc[i][j];
             else *y = *y + acc[i][j];

@@ -38,6 +38,15 @@ template <int MODE>
 __device__ __forceinline__ void store_row16(const float* v, void* Y, int row, int n, int T, int N, int ldy) {
     if (row >= T || n >= N) return;
     const bool whole = n + 16 <= N;
+#ifdef ZLM_BOUNDS_CHECK
+    {
+        const int cols = whole ? 16 : N - n;
+        const bool ok = MODE == 3 ? ZLM_CHK((__nv_bfloat16*)Y + (size_t)row * ldy + n / 2, 16)
+                      : MODE == 0 ? ZLM_CHK((__nv_bfloat16*)Y + (size_t)row * ldy + n, cols * 2)
+                                  : ZLM_CHK((float*)Y + (size_t)row * ldy + n, cols * 4);
+        if (!ok) return;
+    }
+#endif
     __nv_bfloat162 t;
 #define ZLM_PK(a, b) (t = __floats2bfloat162_rn(a, b), *(unsigned*)&t)
     if (MODE == 3) {
@@ -92,12 +101,17 @@ __device__ __forceinline__ void store_swapped16(const float* v, void* Y, int row
             const float u = __shfl_down_sync(0xffffffffu, v[i], 8);
             if ((lane & 8) == 0 && row < N && t0 + i < T) {
                 const int ch = (row >> 4) * 8 + (row & 7);
+                if (!ZLM_CHK((__nv_bfloat16*)Y + (size_t)(t0 + i) * ldy + ch, 2)) continue;
                 ((__nv_bfloat16*)Y)[(size_t)(t0 + i) * ldy + ch] = __float2bfloat16_rn(silu_mul(v[i], u));
             }
         }
         return;
     }
     if (row >= N) return;
+#ifdef ZLM_BOUNDS_CHECK
+    for (int i = 0; i < 16 && t0 + i < T; ++i)
+        if (!ZLM_CHK((char*)Y + ((size_t)(t0 + i) * ldy + row) * (MODE == 0 ? 2 : 4), MODE == 0 ? 2 : 4)) return;
+#endif
     if (MODE == 1) {
         float old[16];
 #pragma unroll
@@ -225,7 +239,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
                     if (arow < N) {
 #pragma unroll
                         for (int i = 0; i < 16; ++i)
-                            if (t0 + i < T) ((float*)Y)[((size_t)blockIdx.z * T + t0 + i) * N + arow] = v[i];
+                            if (t0 + i < T && ZLM_CHK((float*)Y + ((size_t)blockIdx.z * T + t0 + i) * N + arow, 4))
+                                ((float*)Y)[((size_t)blockIdx.z * T + t0 + i) * N + arow] = v[i];
                     }
                 } else {
                     store_swapped16<MODE>(v, Y, arow, t0, T, N, ldy, lane);
@@ -668,7 +683,8 @@ gemm_tc_few_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                     if (row < N) {
 #pragma unroll
                         for (int i = 0; i < 16; ++i)
-                            if (b0row + c + i < T) part[(size_t)z * TN + (size_t)(b0row + c + i) * N + row] = KB ? v[i] : 0.f;
+                            if (b0row + c + i < T && ZLM_CHK(part + (size_t)z * TN + (size_t)(b0row + c + i) * N + row, 4))
+                                part[(size_t)z * TN + (size_t)(b0row + c + i) * N + row] = KB ? v[i] : 0.f;
                     }
                 }
             }
@@ -704,14 +720,20 @@ __global__ void gemm_tc_reduce_kernel(void* __restrict__ Y, const float* __restr
             const int c = n_from / 2 + (int)(e - t * (width / 2));
             const size_t g = t * N + (size_t)(c >> 3) * 16 + (c & 7);
             float sg = 0.f, su = 0.f;
+            if (!ZLM_CHK(part + g, 4) || !ZLM_CHK(part + (splits - 1) * total + g + 8, 4) ||
+                !ZLM_CHK((__nv_bfloat16*)Y + t * ldy + c, 2))
+                continue;
             for (int s = 0; s < splits; ++s) { sg += part[s * total + g]; su += part[s * total + g + 8]; }
             ((__nv_bfloat16*)Y)[t * ldy + c] = __float2bfloat16_rn(silu_mul(sg, su));
         } else {
             const size_t t = e / width;
             const int n = n_from + (int)(e - t * width);
             float sum = 0.f;
-            for (int s = 0; s < splits; ++s) sum += part[s * total + t * N + n];
             const size_t off = t * ldy + n;
+            if (!ZLM_CHK(part + t * N + n, 4) || !ZLM_CHK(part + (splits - 1) * total + t * N + n, 4) ||
+                !ZLM_CHK((char*)Y + off * (MODE == 0 ? 2 : 4), MODE == 0 ? 2 : 4))
+                continue;
+            for (int s = 0; s < splits; ++s) sum += part[s * total + t * N + n];
             if (MODE == 0) ((__nv_bfloat16*)Y)[off] = __float2bfloat16_rn(sum);
             else if (MODE == 1) ((float*)Y)[off] += sum;
             else ((float*)Y)[off] = sum;

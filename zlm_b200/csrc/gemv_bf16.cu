@@ -28,10 +28,16 @@
 
 __device__ __forceinline__ uint4 ld_stream16(const void* p) {
     uint4 v;
+    if (!ZLM_CHK(p, 16)) return make_uint4(0, 0, 0, 0);
     asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
                  : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
                  : "l"(p));
     return v;
+}
+// 16 bytes of the activations (they stay in L1: every warp of the block reads them)
+__device__ __forceinline__ uint4 ld_act16(const __nv_bfloat16* p) {
+    if (!ZLM_CHK(p, 16)) return make_uint4(0, 0, 0, 0);
+    return __ldg((const uint4*)p);
 }
 __device__ __forceinline__ void gemv_mma(float* c, unsigned a0, unsigned a1, unsigned a2, unsigned a3,
                                          unsigned b0, unsigned b1) {
@@ -106,7 +112,7 @@ gemv_bf16_kernel(void* __restrict__ Y, const __nv_bfloat16* __restrict__ X,
             for (int u = 0; u < GEMV_UNROLL; ++u)
 #pragma unroll
                 for (int j = 0; j < NT; ++j)
-                    x[u][j] = xok[j] ? __ldg((const uint4*)(xr[j] + kb + u * 32)) : make_uint4(0, 0, 0, 0);
+                    x[u][j] = xok[j] ? ld_act16(xr[j] + kb + u * 32) : make_uint4(0, 0, 0, 0);
 #pragma unroll
             for (int u = 0; u < GEMV_UNROLL; ++u)      // kb - kc is a multiple of 128: block u has parity u & 1
 #pragma unroll
@@ -123,7 +129,7 @@ gemv_bf16_kernel(void* __restrict__ Y, const __nv_bfloat16* __restrict__ X,
             const uint4 b = in ? ld_stream16(w1 + kb) : z;
 #pragma unroll
             for (int j = 0; j < NT; ++j) {
-                const uint4 x = (in && xok[j]) ? __ldg((const uint4*)(xr[j] + kb)) : z;
+                const uint4 x = (in && xok[j]) ? ld_act16(xr[j] + kb) : z;
                 if (par == 0) {
                     gemv_mma(ch[j][0], a.x, b.x, a.y, b.y, x.x, x.y);
                     gemv_mma(ch[j][1], a.z, b.z, a.w, b.w, x.z, x.w);
@@ -159,7 +165,8 @@ gemv_bf16_kernel(void* __restrict__ Y, const __nv_bfloat16* __restrict__ X,
                 sg += red[w][j][row][tok & 7];
                 su += red[w][j][row + 8][tok & 7];
             }
-            ((__nv_bfloat16*)Y)[(size_t)tok * ldy + n0 / 2 + row] = __float2bfloat16_rn((sg / (1.0f + expf(-sg))) * su);
+            if (ZLM_CHK((__nv_bfloat16*)Y + (size_t)tok * ldy + n0 / 2 + row, 2))
+                ((__nv_bfloat16*)Y)[(size_t)tok * ldy + n0 / 2 + row] = __float2bfloat16_rn((sg / (1.0f + expf(-sg))) * su);
         }
     } else {
     for (int idx = tid; idx < NT * GEMV_ROWS * 8; idx += GEMV_THREADS) {
@@ -171,6 +178,7 @@ gemv_bf16_kernel(void* __restrict__ Y, const __nv_bfloat16* __restrict__ X,
 #pragma unroll
         for (int w = 0; w < GEMV_WARPS; ++w) s += red[w][j][row][tok & 7];
         const size_t o = (size_t)tok * ldy + n;
+        if (!ZLM_CHK((char*)Y + o * (MODE == 0 ? 2 : 4), MODE == 0 ? 2 : 4)) continue;
         if (MODE == 0) ((__nv_bfloat16*)Y)[o] = __float2bfloat16_rn(s);
         else if (MODE == 1) ((float*)Y)[o] += s;
         else ((float*)Y)[o] = s;

@@ -73,6 +73,10 @@ __device__ __forceinline__ void qk_norm_rope_write_item(
     float* bufs = sm + 2 * ang;           // [ROPE_WARPS][hd]
     const int lane = tid & 31, warp = tid >> 5;
     if (PDL) pdl_trigger();
+    // bounds-check build: the step's integers and tables first (the same answer in every thread)
+    if (!ZLM_CHK(token_pos + t, 4) || (ang > 0 && !ZLM_CHK(inv_freq, (size_t)ang * 4)) ||
+        (writes_kv && !ZLM_CHK(token_slot + t, 4)))
+        return;
     const int pos = token_pos[t];
     for (int i = tid; i < ang; i += ROPE_WARPS * 32) {
         float s, c;
@@ -84,7 +88,15 @@ __device__ __forceinline__ void qk_norm_rope_write_item(
     const int heads = nq + 2 * nkv;
     float* buf = bufs + warp * hd;
     int page = 0;
-    if (writes_kv) page = block_table[(size_t)token_slot[t] * table_stride + pos / ZLM_PAGE];
+    if (writes_kv) {
+        const int* entry = block_table + (size_t)token_slot[t] * table_stride + pos / ZLM_PAGE;
+        if (!ZLM_CHK(entry, 4)) return;
+        page = *entry;
+    }
+    if (has_norm && (!ZLM_CHK(qw.p, (size_t)hd * (qw.dtype == ZLM_DTYPE_F32 ? 4 : 2)) ||
+                     (nkv > 0 && !ZLM_CHK(kw.p, (size_t)hd * (kw.dtype == ZLM_DTYPE_F32 ? 4 : 2)))))
+        return;
+    if (!ZLM_CHK(qkv + (size_t)t * row_stride, (size_t)(nq + (writes_kv ? 2 : 1) * nkv) * hd * sizeof(TA))) return;
     if (PDL) pdl_wait();    // the table above is the step's own; qkv comes from the kernel before
     const int j_end = min(heads, (chunk + 1) * heads_per_block);
     if constexpr (VEC) {
@@ -147,7 +159,7 @@ __device__ __forceinline__ void qk_norm_rope_write_item(
                 dst = pool + (size_t)page * page_stride + (size_t)(kind - 1) * nkv * ZLM_PAGE * hd +
                       ((size_t)kvh * ZLM_PAGE + (pos % ZLM_PAGE)) * hd + lane * NPL;
             }
-            rope_store_vec<TA, NPL>(dst, v);
+            if (ZLM_CHK(dst, NPL * sizeof(TA))) rope_store_vec<TA, NPL>(dst, v);
         }
     } else {
     for (int j = chunk * heads_per_block + warp; j < j_end; j += ROPE_WARPS) {
@@ -206,7 +218,7 @@ __device__ __forceinline__ void qk_norm_rope_write_item(
 #pragma unroll
         for (int r = 0; r < NPL; ++r) {
             const int e = lane + 32 * r;
-            if (e < hd) dst[e] = from_f32<TA>(v[r]);
+            if (e < hd && ZLM_CHK(dst + e, sizeof(TA))) dst[e] = from_f32<TA>(v[r]);
         }
     }
     }

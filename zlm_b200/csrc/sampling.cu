@@ -17,6 +17,9 @@ argmax_partial_kernel(float* __restrict__ pv, int* __restrict__ pi, const float*
     pdl_launch_dependents();
     pdl_wait();
     const float* row = logits + (size_t)blockIdx.x * ld;
+    if (!ZLM_CHK(row, (size_t)V * 4) || !ZLM_CHK(pv + blockIdx.x * ARGMAX_CHUNKS + blockIdx.y, 4) ||
+        !ZLM_CHK(pi + blockIdx.x * ARGMAX_CHUNKS + blockIdx.y, 4))
+        return;                                                          // block-uniform
     const int per = (V + ARGMAX_CHUNKS - 1) / ARGMAX_CHUNKS;
     const int lo = blockIdx.y * per, hi = min(V, lo + per);
     float best = -INFINITY;
@@ -60,6 +63,9 @@ argmax_final_kernel(int* __restrict__ out, const float* __restrict__ pv, const i
     const int lane = threadIdx.x;
     float best = -INFINITY;
     int idx = 0x7fffffff;
+    if (!ZLM_CHK(pv + blockIdx.x * ARGMAX_CHUNKS, ARGMAX_CHUNKS * 4) || !ZLM_CHK(pi + blockIdx.x * ARGMAX_CHUNKS, ARGMAX_CHUNKS * 4) ||
+        !ZLM_CHK(out + blockIdx.x, 4))
+        return;
     for (int c = lane; c < ARGMAX_CHUNKS; c += 32) {
         const float v = pv[blockIdx.x * ARGMAX_CHUNKS + c];
         const int i = pi[blockIdx.x * ARGMAX_CHUNKS + c];
@@ -200,6 +206,8 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, int V, in
     pdl_wait();
     const int row = blockIdx.x, tid = threadIdx.x;
     const float* l = logits + (size_t)row * ld;
+    if (!ZLM_CHK(l, (size_t)V * 4) || !ZLM_CHK(out + row, 4) || !ZLM_CHK(request + row, 4) || !ZLM_CHK(position + row, 4))
+        return;                                                          // block-uniform
     const int seg = (V + SAMPLE_THREADS - 1) / SAMPLE_THREADS;     // contiguous segment per thread
     const int i0 = min(V, tid * seg), i1 = min(V, i0 + seg);
     const float invT = 1.0f / temperature;
@@ -441,6 +449,8 @@ sample_cluster_kernel(int* __restrict__ out, const float* __restrict__ logits, i
     pdl_launch_dependents();
     pdl_wait();
     const float* l = logits + (size_t)row * ld;
+    if (!ZLM_CHK(l, (size_t)V * 4) || !ZLM_CHK(out + row, 4) || !ZLM_CHK(request + row, 4) || !ZLM_CHK(position + row, 4))
+        return;                                                          // the same answer in every block of the cluster
     const int lo = min(V, rank * chunk), n = min(V, lo + chunk) - lo;             // global [lo, lo + n)
     // a thread's own contiguous part, for the walks in index order (an odd length: no bank conflicts)
     const int sseg = ((chunk + SAMPLE_THREADS - 1) / SAMPLE_THREADS) | 1;

@@ -94,9 +94,10 @@ class CudaKernels:
 
     name = "cuda"
 
-    def __init__(self, verbose_build: bool = True):
+    def __init__(self, verbose_build: bool = True, variant: str = ""):
         from .csrc.build import library_path
-        self.lib_path = library_path(verbose=verbose_build)
+        self.variant = variant
+        self.lib_path = library_path(verbose=verbose_build, variant=variant)
         self.lib = ctypes.CDLL(self.lib_path)
         self.lib.zlm_last_error.restype = ctypes.c_char_p
         if self.lib.zlm_page_tokens() != PAGE_TOKENS:
@@ -449,10 +450,20 @@ class CudaKernels:
 
 
 _KERNELS: Optional[CudaKernels] = None
+_VARIANT = ""
+
+
+def set_build_variant(variant: str) -> None:
+    """Which build of the library ``get_kernels`` loads: "" (the ordinary one) or "check"
+    (the bounds-check build).  To be called before the first ``get_kernels``."""
+    global _VARIANT, _KERNELS
+    if _KERNELS is not None and _KERNELS.variant != variant:
+        raise KernelError("the kernel library is loaded already; choose the build variant before first use")
+    _VARIANT = variant
 
 
 def get_kernels() -> CudaKernels:
     global _KERNELS
     if _KERNELS is None:
-        _KERNELS = CudaKernels()
+        _KERNELS = CudaKernels(variant=_VARIANT)
     return _KERNELS
