@@ -5,10 +5,17 @@ bf16 weights, one GPU.
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl reference]
 
 One JSON line on stdout.  ``value`` is decoded tokens per second at batch 8
-(device-timed, sampled tokens fed back on the device); ``e2e`` is the same
-through ``Engine.generate`` with host tokens in and out every step; ``prefill``
-is one 2,048-token prompt; ``roofline`` relates the decode step's mandatory HBM
-reads to the measured copy bandwidth; ``points`` holds decode at batch 1 and 64.
+(device-timed, sampled tokens fed back on the device), timed at contexts of 2,048,
+3,072 and 4,095 tokens and averaged: the run from 2,048-token prompts to the 4,096
+context; ``e2e`` is decode through ``Engine.generate`` with host tokens in and out
+every step; ``prefill`` is one 2,048-token prompt; ``roofline`` relates the decode
+step's mandatory HBM reads to the measured copy bandwidth; ``points`` holds, as flat
+numbers, each context of the headline, decode at batch 1 and 64, and the baseline's
+other configurations (Qwen3-0.6B sizes incl. the 64 unequal prompts through
+``generate``, Qwen3-32B sizes with a cache for 64 x 4,096 tokens); ``kernels`` gives
+every operation of a prefill and of a decode step by CUDA events with its fraction of
+the measured peak; ``cpu_baseline`` times the plain implementation on the two tiny
+configurations.
 """
 from __future__ import annotations
 
@@ -119,165 +126,301 @@ def model_numbers(cfg, layers: int):
     return per_layer, weight_bytes, kv_bytes_per_token
 
 
-def run(args) -> dict:
-    import torch
-    from zlm_b200 import Engine
-    from zlm_b200.registry import config_from_dict
-    from zlm_b200.sampling import SamplingParams
+CONTEXTS = (2048, 3072, 4095)      # where decode is timed: the start, the middle and the end of the run
 
-    pk = peaks()
-    d = dict(OTHER_SIZES.get(args.sizes, QWEN3_8B))
-    full_layers = d["num_hidden_layers"]
-    if args.layers is None:
-        args.layers = full_layers
-    d["num_hidden_layers"] = args.layers
-    cfg = config_from_dict(d)
-    B = args.batch
-    steps, warmup = args.steps, args.warmup
-    torch.cuda.set_device(0)
-    greedy = SamplingParams()
 
-    def make_engine(batch, tokens):
-        # the headline numbers come from an engine whose cache is sized for the headline
-        # configuration (batch x context); the batch-64 point gets an engine of its own
-        e = Engine.from_random(cfg, seed=0, dtype="bfloat16", device="cuda:0", max_tokens=tokens,
-                               max_batch=batch, max_seq_len=CONTEXT, max_step_tokens=max(B, 8) * PROMPT_LEN)
-        if args.pdl or args.no_pdl:
-            e.decoder.use_pdl = bool(args.pdl)
-        if args.decode == "stream":
-            e.decoder.use_stream = e.decoder.can_stream
+class Runner:
+    """One set of layer sizes: builds engines as the cases need them and times decode
+    (device-timed, tokens fed back on the device), the same through ``Engine.generate``,
+    prefill, and every operation of a step by CUDA events."""
+
+    def __init__(self, sizes: str, layers, args, pk):
+        import torch
+        from zlm_b200.registry import config_from_dict
+        from zlm_b200.sampling import SamplingParams
+        self.torch = torch
+        self.args, self.pk, self.sizes = args, pk, sizes
+        d = dict(OTHER_SIZES.get(sizes, QWEN3_8B))
+        self.full_layers = d["num_hidden_layers"]
+        self.layers = self.full_layers if layers is None else layers
+        d["num_hidden_layers"] = self.layers
+        self.cfg = config_from_dict(d)
+        self.per_layer, self.weight_bytes, self.kv_per_tok = model_numbers(self.cfg, self.layers)
+        self.greedy = SamplingParams()
+        self.g = torch.Generator().manual_seed(0)
+        self.eng = None
+        self.shape = None
+
+    # ---- engines ------------------------------------------------------------------
+    def engine(self, batch: int, tokens_per_seq: int):
+        """An engine whose cache holds ``batch`` sequences of ``tokens_per_seq`` tokens (kept
+        while it is large enough)."""
+        torch = self.torch
+        from zlm_b200 import Engine
+        need = (batch, batch * tokens_per_seq)
+        if self.eng is not None and self.shape[0] >= need[0] and self.shape[1] >= need[1]:
+            return self.eng
+        self.drop()
+        e = Engine.from_random(self.cfg, seed=0, dtype="bfloat16", device="cuda:0", max_tokens=need[1],
+                               max_batch=batch, max_seq_len=CONTEXT, max_step_tokens=8 * CONTEXT)
+        if self.args.pdl or self.args.no_pdl:
+            e.decoder.use_pdl = bool(self.args.pdl)
+        self.eng, self.shape = e, need
         return e
 
-    eng = make_engine(max(B, 1), B * CONTEXT)
-    g = torch.Generator().manual_seed(0)
-    per_layer, weight_bytes, kv_per_tok = model_numbers(cfg, args.layers)
-    k = eng.rt.k
+    def drop(self):
+        if self.eng is not None:
+            self.eng = None
+            gc.collect()
+            self.torch.cuda.empty_cache()
 
-    def prompts(n):
-        return [torch.randint(0, cfg.vocab_size, (PROMPT_LEN,), generator=g).tolist() for _ in range(n)]
+    def prompts(self, n: int, length: int):
+        return [self.torch.randint(0, self.cfg.vocab_size, (length,), generator=self.g).tolist() for _ in range(n)]
 
-    def prefill(ps, chunk=8):
+    def prefill(self, eng, ps, chunk_tokens=8 * 2048):
+        """Prompts into fresh slots, a few at a time; returns (slots, first sampled tokens)."""
         slots = [eng.new_sequence() for _ in ps]
+        per = max(1, chunk_tokens // max(len(p) for p in ps))
         first = []
-        for i in range(0, len(ps), chunk):
-            first += eng.prefill_sample(slots[i:i + chunk], ps[i:i + chunk], greedy, list(range(i, i + len(ps[i:i + chunk]))))
+        for i in range(0, len(ps), per):
+            first += eng.prefill_sample(slots[i:i + per], ps[i:i + per], self.greedy,
+                                        list(range(i, i + len(ps[i:i + per]))))
         return slots, first
 
-    def timed_decode(slots, first, n_warm, n_steps, clocks=None):
-        dec = eng.decoder
-        dec.step(slots, first, greedy)
-        for _ in range(max(0, n_warm - 1)):
-            dec.step(slots, None, greedy)
+    # ---- decode ---------------------------------------------------------------------
+    def decode_at(self, batch: int, context: int, steps: int, warmup: int, clocks=None) -> dict:
+        """``steps`` decode steps of ``batch`` sequences that hold about ``context`` tokens,
+        timed on the device around the whole run of steps."""
+        torch = self.torch
+        start = max(1, min(context, CONTEXT - warmup - steps))    # the timed steps end inside the context
+        eng = self.engine(batch, CONTEXT)
+        slots, first = self.prefill(eng, self.prompts(batch, start))
+        dec, k = eng.decoder, eng.rt.k
+        dec.step(slots, first, self.greedy)
+        for _ in range(max(0, warmup - 1)):
+            dec.step(slots, None, self.greedy)
         torch.cuda.synchronize()
-        l0 = k.launches()
         if clocks:
             clocks.start()
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         ctx0 = eng.length(slots[0])
         ev0.record()
-        for _ in range(n_steps):
-            dec.step(slots, None, greedy)
+        for _ in range(steps):
+            dec.step(slots, None, self.greedy)
         ev1.record()
         torch.cuda.synchronize()
-        ms = ev0.elapsed_time(ev1)
-        launches = dec.launches_per_step * n_steps if (dec.use_graphs or dec.use_stream) else k.launches() - l0
-        return ms, ctx0, launches
+        ms = ev0.elapsed_time(ev1) / steps
+        for sl in slots:
+            eng.release(sl)
+        eng.check(sync=True)
+        mean_ctx = ctx0 + (steps - 1) / 2.0
+        nbytes = self.weight_bytes + batch * self.cfg.hidden_size * 2 + batch * mean_ctx * self.kv_per_tok
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        return {"ms": ms, "tok_s": batch / ms * 1e3, "context": mean_ctx, "nominal": context, "gbs": gbs,
+                "frac": gbs / self.pk["hbm_gbs"], "launches": dec.launches_per_step, "steps": steps}
 
-    # ---- prefill of 2,048 tokens at batch 1 ------------------------------------------
-    p1 = prompts(1)
-    s, _ = prefill(p1)
-    eng.release(s[0])
-    torch.cuda.synchronize()
-    pre_ms = []
-    for _ in range(3):
-        s = [eng.new_sequence()]
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        torch.cuda.synchronize()
-        e0.record()
+    def decode_over_contexts(self, batch: int, steps: int, warmup: int, clocks=None) -> dict:
+        """Decode timed at three contexts of the run from 2,048 to 4,096 tokens; a step's time
+        grows linearly with the context, so the mean of the three is the run's time per step."""
+        runs = [self.decode_at(batch, c, steps, warmup, clocks if i == 0 else None) for i, c in enumerate(CONTEXTS)]
+        ms = sum(r["ms"] for r in runs) / len(runs)
+        ctx = sum(r["context"] for r in runs) / len(runs)
+        nbytes = self.weight_bytes + batch * self.cfg.hidden_size * 2 + batch * ctx * self.kv_per_tok
+        gbs = nbytes / (ms * 1e-3) / 1e9
+        return {"ms": ms, "tok_s": batch / ms * 1e3, "context": ctx, "gbs": gbs, "frac": gbs / self.pk["hbm_gbs"],
+                "runs": runs, "launches": runs[0]["launches"], "steps": runs[0]["steps"]}
+
+    def e2e(self, batch: int, steps: int) -> dict:
+        """The same decode through the Python entry point: host tokens in, host tokens out."""
+        eng = self.engine(batch, CONTEXT)
+        ps = self.prompts(batch, PROMPT_LEN)
+        # at least 128 steps: the first dozen steps after a prefill run at the clocks that the
+        # prefill's power draw left (measured: 5.0 instead of 3.8 ms a step for about 15 steps),
+        # which says nothing about the loop and would weigh a fifth in a run of 20 steps
+        n = max(steps, 128)
+        # once before, so that the decode graphs of every context length the run passes through
+        # exist before the timed call (a capture costs as much as several steps)
+        eng.generate(ps, max_tokens=n + 1, stop_token_ids=())
+        st = eng.generate(ps, max_tokens=n + 1, stop_token_ids=()).stats
+        return {"value": round(batch * st.decode_steps / st.decode_ms * 1e3, 1), "unit": "tokens/s",
+                "h2d_bytes_per_step": int(eng.stager.h2d_bytes), "d2h_bytes_per_step": 4 * batch,
+                "steps": st.decode_steps}
+
+    # ---- prefill ----------------------------------------------------------------------
+    def prefill_2048(self) -> dict:
+        torch = self.torch
         from zlm_b200 import StepEntry
-        eng.step([StepEntry(s[0], p1[0], [PROMPT_LEN - 1])])
-        e1.record()
-        torch.cuda.synchronize()
-        pre_ms.append(e0.elapsed_time(e1))
-        eng.release(s[0])
-    pms = min(pre_ms)
-    T = PROMPT_LEN
-    attn_flops = args.layers * 4 * cfg.num_attention_heads * cfg.head_dim * (T * (T + 1) // 2)
-    pre_flops = 2 * T * args.layers * per_layer + 2 * cfg.vocab_size * cfg.hidden_size + attn_flops
-    prefill_rec = {"value": round(T / pms * 1e3, 1), "tokens": T, "ms": round(pms, 3),
-                   "frac": round(pre_flops / (pms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4)}
+        eng = self.engine(1, CONTEXT)
+        (p,) = self.prompts(1, PROMPT_LEN)
+        times = []
+        for i in range(4):
+            s = eng.new_sequence()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            e0.record()
+            eng.step([StepEntry(s, p, [PROMPT_LEN - 1])])
+            e1.record()
+            torch.cuda.synchronize()
+            if i:
+                times.append(e0.elapsed_time(e1))
+            eng.release(s)
+        ms = min(times)
+        T, cfg = PROMPT_LEN, self.cfg
+        attn = self.layers * 4 * cfg.num_attention_heads * cfg.head_dim * (T * (T + 1) // 2)
+        flops = 2 * T * self.layers * self.per_layer + 2 * cfg.vocab_size * cfg.hidden_size + attn
+        return {"value": round(T / ms * 1e3, 1), "tokens": T, "ms": round(ms, 3),
+                "frac": round(flops / (ms * 1e-3) / (self.pk["bf16_tflops"] * 1e12), 4)}
 
-    # ---- decode at the headline batch ------------------------------------------------
+    # ---- every operation of a step -------------------------------------------------------
+    def kernels(self, batch: int, phase: str) -> dict:
+        """Per-operation CUDA-event times inside a real step (weights stream from HBM: the whole
+        model is larger than L2): microseconds per call, GB/s and TFLOP/s, and the larger of
+        their fractions of the measured peaks."""
+        from zlm_b200.profiling import profile_engine
+        eng = self.engine(batch, CONTEXT)
+        n = 1 if phase == "prefill" else batch
+        rows = profile_engine(eng, self.prompts(n, PROMPT_LEN), decode_steps=0 if phase == "prefill" else 6)
+        out = {}
+        for r in rows:
+            if r["phase"] != phase or r["op"] in ("argmax", "sample", "embed"):
+                continue
+            f_b = r["gb_s"] / self.pk["hbm_gbs"]
+            f_f = r["tflop_s"] / self.pk["bf16_tflops"]
+            out[r["op"]] = {"us": r["us_per_call"], "calls": r["calls"], "gb_s": r["gb_s"], "tflop_s": r["tflop_s"],
+                            "frac": round(max(f_b, f_f), 3), "bound": "hbm" if f_b >= f_f else "tensor"}
+        return out
+
+
+def cpu_baseline() -> dict:
+    """The two tiny configurations on the CPU with the plain implementation (no cache: every
+    token recomputes its whole sequence), the baseline's workloads: tokens a second."""
+    import torch
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import plain_qwen3 as P
+    from tiny_configs import TINY, plain_sizes
+    from zlm_b200.parts.model import DecoderModel
+    from zlm_b200.registry import config_from_dict
+    from zlm_b200.weights import random_tensors
+    out = {}
+    for name, lens, steps in (("A", [5, 9, 13], 8), ("B", [1, 7, 16, 31], 12)):
+        cfg = config_from_dict(TINY[name])
+        t = random_tensors(DecoderModel(cfg.to_model_spec()).param_specs(), 0, "cpu", torch.float32)
+        g = torch.Generator().manual_seed(1)
+        ps = [torch.randint(0, cfg.vocab_size, (n,), generator=g).tolist() for n in lens]
+        t0 = time.perf_counter()
+        n = sum(len(P.greedy_generate(t, plain_sizes(cfg), p, steps)) for p in ps)
+        dt = time.perf_counter() - t0
+        out[f"tiny_{name.lower()}_tok_s"] = round(n / dt, 1)
+    out["what"] = "tests/plain_qwen3.py, greedy, float32, torch on the host's cores"
+    return out
+
+
+def run(args) -> dict:
+    import torch
+    torch.cuda.set_device(0)
+    pk = peaks()
+    B, steps, warmup = args.batch, args.steps, args.warmup
+    R = Runner(args.sizes, args.layers, args, pk)
+    cfg = R.cfg
     clocks = ClockSampler()
-    slots, first = prefill(prompts(B))
-    ms, ctx0, launches = timed_decode(slots, first, warmup, steps, clocks)
+
+    prefill_rec = R.prefill_2048()
+    kern = {}
+    if not args.no_kernels:
+        kern["prefill_2048"] = R.kernels(1, "prefill")
+    head = R.decode_over_contexts(B, steps, warmup, clocks)
     clock_rec = clocks.stop()
-    value = B * steps / ms * 1e3
-    mean_ctx = ctx0 + (steps - 1) / 2.0
-    step_bytes = weight_bytes + B * cfg.hidden_size * 2 + B * mean_ctx * kv_per_tok
-    achieved = step_bytes / (ms / steps * 1e-3) / 1e9
-    for sl in slots:
-        eng.release(sl)
-
-    # ---- the same through the Python entry point ------------------------------------
-    ps = prompts(B)
-    n_e2e = min(steps, 128)
-    # warm-up: the same call once, so that the decode graphs of every context length the run
-    # passes through exist before the timed call (a capture costs as much as several steps)
-    eng.generate(ps, max_tokens=n_e2e + 1, stop_token_ids=())
-    res = eng.generate(ps, max_tokens=n_e2e + 1, stop_token_ids=())
-    st = res.stats
-    e2e = {"value": round(st.new_tokens and (B * st.decode_steps) / st.decode_ms * 1e3, 1), "unit": "tokens/s",
-           "h2d_bytes_per_step": int(eng.stager.h2d_bytes), "d2h_bytes_per_step": 4 * B,
-           "steps": st.decode_steps}
-
-    # ---- decode at batch 1 and 64 ------------------------------------------------------
+    e2e = R.e2e(B, steps)
+    if not args.no_kernels:
+        kern[f"decode_b{B}"] = R.kernels(B, "decode")
     points = {}
+    for r in head["runs"]:
+        points[f"decode_b{B}_ctx{r['nominal']}"] = round(r["tok_s"], 1)
     if not args.no_points:
         for b in (1, 64):
-            if b > eng.max_batch or b * (PROMPT_LEN + args.point_steps + warmup + 64) > eng.max_tokens:
-                del eng, k
-                gc.collect()                 # the engine and its decode runner refer to each other
-                torch.cuda.empty_cache()
-                eng = make_engine(b, b * (PROMPT_LEN + args.point_steps + warmup + 64))
-                k = eng.rt.k
-            slots, first = prefill(prompts(b))
-            pm, _, _ = timed_decode(slots, first, warmup, args.point_steps)
-            points[f"decode_b{b}"] = round(b * args.point_steps / pm * 1e3, 1)
-            for sl in slots:
-                eng.release(sl)
+            if b == B:
+                continue
+            r = R.decode_over_contexts(b, args.point_steps, warmup)
+            points[f"decode_b{b}"] = round(r["tok_s"], 1)
+            points[f"decode_b{b}_frac"] = round(r["frac"], 4)
+            points[f"decode_b{b}_ctx2048"] = round(r["runs"][0]["tok_s"], 1)
+            if not args.no_kernels and b == 64:
+                kern["decode_b64"] = {k: v for k, v in R.kernels(64, "decode").items() if k.startswith("attention")}
+    R.drop()
+    others = {}
+    if not (args.no_points or args.no_other_sizes) and args.sizes == "8b":
+        others = other_sizes(args, pk, warmup)
+        for name, rec in others.items():
+            for k, v in rec.items():
+                points[f"{name}_{k}"] = v
 
     return {
         "metric": f"decode tokens/s (Qwen3-{args.sizes.upper()} sizes, bf16, batch {B}, 2048-token prompts, context 4096)",
-        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
-        "ms_per_step": round(ms / steps, 4), "higher_is_better": True, "scaling": "weak",
+        "value": round(head["tok_s"], 1), "unit": "tokens/s", "n_gpus": 1, "steps": head["steps"], "warmup": warmup,
+        "ms_per_step": round(head["ms"], 4), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic (random weights, uniform random token ids)",
         "impl": "zlm_b200",
-        "config": {"model": f"qwen3-{args.sizes}-sizes", "layers": args.layers, "layers_full": full_layers,
+        "config": {"model": f"qwen3-{args.sizes}-sizes", "layers": R.layers, "layers_full": R.full_layers,
                    "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads,
                    "kv_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim,
                    "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size, "global_batch": B,
-                   "prompt_len": PROMPT_LEN, "seq_len": CONTEXT, "context_at_timing": int(mean_ctx),
+                   "prompt_len": PROMPT_LEN, "seq_len": CONTEXT, "context_at_timing": int(head["context"]),
+                   "timed": f"{head['steps']} steps at each of contexts 2048, 3072 and 4095; their mean",
                    "parallelism": "single-gpu", "l2": "inputs larger than L2 (weights read every step)",
                    "peaks": pk["source"]},
-        "e2e": e2e, "gpu_launches": int(launches), "clocks": clock_rec,
+        "e2e": e2e, "gpu_launches": int(head["launches"] * head["steps"] * len(CONTEXTS)),
+        "launches_per_step": int(head["launches"]), "clocks": clock_rec,
         "prefill": prefill_rec,
-        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
-                     "frac": round(achieved / pk["hbm_gbs"], 4)},
-        "points": points,
+        "roofline": {"bound": "hbm", "achieved": round(head["gbs"], 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(head["frac"], 4)},
+        "points": points, "kernels": kern, "cpu_baseline": cpu_baseline(),
     }
 
 
-def unequal(args) -> int:
-    """The baseline's small-model scenario: 64 prompts of unequal lengths (uniform in
-    [16, 2048]) prefilled as one batch, then 256 decode steps, through ``Engine.generate``
-    (host tokens in and out).  The call is made twice; the second is reported."""
+def other_sizes(args, pk, warmup: int) -> dict:
+    """The baseline's other configurations, each as flat numbers: Qwen3-0.6B sizes (decode at
+    batch 1 / 8 / 64 at a 2,048-token context, and 64 prompts of unequal lengths with 256
+    decode steps through ``generate``) and Qwen3-32B sizes (prefill of 2,048 tokens, decode at
+    batch 1 / 8 / 64, the cache sized for 64 x 4,096 tokens)."""
+    out = {}
+    R = Runner("0.6b", None, args, pk)
+    rec = {}
+    for b in (1, 8, 64):
+        r = R.decode_at(b, PROMPT_LEN, args.point_steps, warmup)
+        rec[f"decode_b{b}"] = round(r["tok_s"], 1)
+        rec[f"decode_b{b}_frac"] = round(r["frac"], 4)
+        if b == 8:
+            rec["launches_per_step"] = int(r["launches"])
+            rec["e2e_b8"] = R.e2e(8, 64)["value"]
+    rec["prefill_2048_tok_s"] = R.prefill_2048()["value"]
+    R.drop()
+    rec.update(unequal_numbers(args, "0.6b"))
+    out["q06b"] = rec
+    R = Runner("32b", None, args, pk)
+    rec = {}
+    R.engine(64, CONTEXT)                     # the cache the configuration names: 64 x 4,096 tokens
+    p = R.prefill_2048()
+    rec["prefill_2048_tok_s"], rec["prefill_frac"] = p["value"], p["frac"]
+    for b in (1, 8, 64):
+        r = R.decode_at(b, PROMPT_LEN, max(8, args.point_steps // 2), warmup)
+        rec[f"decode_b{b}"] = round(r["tok_s"], 1)
+        rec[f"decode_b{b}_frac"] = round(r["frac"], 4)
+    rec["cache_tokens"] = 64 * CONTEXT
+    R.drop()
+    out["q32b"] = rec
+    return out
+
+
+def unequal_numbers(args, sizes: str, layers=None) -> dict:
+    """64 prompts of unequal lengths (uniform in [16, 2048]) prefilled as one batch, then 256
+    decode steps, through ``Engine.generate`` (host tokens in and out).  The call is made
+    twice; the second is reported."""
     import torch
     from zlm_b200 import Engine
     from zlm_b200.registry import config_from_dict
-    d = dict(OTHER_SIZES.get(args.sizes, QWEN3_8B))
-    full_layers = d["num_hidden_layers"]
-    d["num_hidden_layers"] = args.layers if args.layers is not None else full_layers
+    d = dict(OTHER_SIZES.get(sizes, QWEN3_8B))
+    if layers is not None:
+        d["num_hidden_layers"] = layers
     cfg = config_from_dict(d)
     g = torch.Generator().manual_seed(0)
     lens = torch.randint(16, 2049, (64,), generator=g).tolist()
@@ -285,15 +428,24 @@ def unequal(args) -> int:
     eng = Engine.from_random(cfg, seed=0, dtype="bfloat16", device="cuda:0", max_tokens=64 * 2368, max_batch=64,
                              max_seq_len=CONTEXT)
     for _ in range(2):
-        res = eng.generate(ps, max_tokens=256, stop_token_ids=())
-    st = res.stats
-    print(json.dumps({
-        "scenario": f"64 unequal prompts (16..2048 tokens) and 256 decode steps, Qwen3-{args.sizes.upper()} sizes, bf16",
-        "layers": d["num_hidden_layers"], "layers_full": full_layers, "prompt_tokens": st.prompt_tokens,
-        "prefill_ms": round(st.prefill_ms, 2), "prefill_tokens_per_s": round(st.prompt_tokens / st.prefill_ms * 1e3, 1),
-        "decode_steps": st.decode_steps, "decode_ms_per_step": round(st.decode_ms / st.decode_steps, 4),
-        "decode_tokens_per_s": round(64 * st.decode_steps / st.decode_ms * 1e3, 1), "batches": st.batches,
-        "bounded_waits_given_up": eng.rt.k.gemm_tc_status()}))
+        st = eng.generate(ps, max_tokens=256, stop_token_ids=()).stats
+    eng.check(sync=True)
+    del eng
+    gc.collect()
+    torch.cuda.empty_cache()
+    return {"unequal64_prompt_tokens": st.prompt_tokens,
+            "unequal64_prefill_tok_s": round(st.prompt_tokens / st.prefill_ms * 1e3, 1),
+            "unequal64_decode_tok_s": round(64 * st.decode_steps / st.decode_ms * 1e3, 1),
+            "unequal64_decode_ms_per_step": round(st.decode_ms / st.decode_steps, 4)}
+
+
+def unequal(args) -> int:
+    d = dict(OTHER_SIZES.get(args.sizes, QWEN3_8B))
+    rec = unequal_numbers(args, args.sizes, args.layers)
+    print(json.dumps({"scenario": f"64 unequal prompts (16..2048 tokens) and 256 decode steps through generate, "
+                                  f"Qwen3-{args.sizes.upper()} sizes, bf16",
+                      "layers": args.layers if args.layers is not None else d["num_hidden_layers"],
+                      "layers_full": d["num_hidden_layers"], **rec}))
     return 0
 
 
@@ -312,8 +464,6 @@ def profile(args) -> int:
     eng = Engine.from_random(cfg, seed=0, dtype="bfloat16", device="cuda:0", max_tokens=B * (L + 256),
                              max_batch=B, max_seq_len=L + 256, max_step_tokens=min(B, 8) * L)
     eng.decoder.use_graphs = False
-    if args.decode == "stream":
-        eng.decoder.use_stream = eng.decoder.can_stream
     g = torch.Generator().manual_seed(0)
     ps = [torch.randint(0, cfg.vocab_size, (L,), generator=g).tolist() for _ in range(B)]
     slots = [eng.new_sequence() for _ in ps]
@@ -365,8 +515,9 @@ def main() -> int:
     ap.add_argument("--no-pdl", action="store_true", help="decode kernels in plain stream order")
     ap.add_argument("--sample", action="store_true",
                     help="with --profile decode: temperature 0.8, top-k 40, top-p 0.9 instead of greedy")
-    ap.add_argument("--decode", choices=["graph", "stream"], default="graph",
-                    help="graph: a CUDA graph of one kernel per operation; stream: the persistent decode kernel where it applies")
+    ap.add_argument("--no-kernels", action="store_true", help="leave out the per-operation times")
+    ap.add_argument("--no-other-sizes", action="store_true",
+                    help="leave out the Qwen3-0.6B and Qwen3-32B sizes that the default run adds under points")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":

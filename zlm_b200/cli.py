@@ -10,7 +10,7 @@ alias, and prompts are token ids because tokenizing happens before this library.
     python -m zlm_b200 run MODEL_DIR -p "1 2 3" --profile --dump-logits logits.f32
     python -m zlm_b200 random-model --config config.json --seed 0 --out DIR
 
-``--profile`` prints, for one prefill step and a few decode steps of the given prompts,
+``--profile`` prints, for one prefill step and one decode step of the given prompts,
 every operation's time by CUDA events with the bytes it moves and GB/s (the reference's
 per-op profile with weight bytes per token and matvec GB/s: src/cli/commands/run.zig:233-299).
 ``--dump-logits FILE`` writes the fp32 logits every generated token was chosen from, one
@@ -55,8 +55,8 @@ def _parser() -> argparse.ArgumentParser:
     run.add_argument("--no-stream", dest="stream", action="store_false")
     run.add_argument("--metrics", nargs="?", const="", default=None, help="print timings (=full for phases)")
     run.add_argument("--verbose", nargs="?", const="min", default=None)
-    run.add_argument("--profile", nargs="?", type=int, const=8, default=None, metavar="STEPS",
-                     help="time every operation of one prefill and STEPS decode steps (default 8), then generate")
+    run.add_argument("--profile", action="store_true",
+                     help="time every operation of one prefill step and of one decode step, then generate")
     run.add_argument("--dump-logits", metavar="FILE",
                      help="write the logits every generated token was chosen from (float32 rows) and FILE.json")
     run.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
@@ -99,10 +99,10 @@ def _run(a) -> int:
     def on_token(req: int, tok: int) -> None:
         print(f"{req}\t{tok}", flush=True)
 
-    if a.profile is not None:
+    if a.profile:
         from .profiling import format_table, profile_engine
         batch = prompts[: eng.max_batch]
-        print(format_table(profile_engine(eng, batch, a.profile)), file=sys.stderr)
+        print(format_table(profile_engine(eng, batch, 1)), file=sys.stderr)
 
     dump, index = None, []
     on_logits = None

@@ -10,6 +10,14 @@ eagerly (no graph) while it is in place.  So that the times are the kernels' and
 host's launch gaps, a profiled step begins with a short device-side wait that lets the
 host queue the step's launches ahead.
 
+Events around every launch are right for the long kernels of a prefill.  The kernels of a
+decode step take a few microseconds each, as long as an event and the launch gap beside it;
+for them ``mode="graph"`` only notes the calls of one step, and ``table`` then captures, for
+each operation, all its calls of the step (one per layer, each with that layer's own
+weights, which together are far larger than L2) as one CUDA graph, replays it, and divides
+its time by the number of calls: the operation as it runs inside a captured step, weights
+streaming from HBM.
+
 ``profile_engine`` runs one prefill and some decode steps this way and returns a table.
 """
 from __future__ import annotations
@@ -27,6 +35,7 @@ class OpRecord:
     bytes: float = 0.0
     flops: float = 0.0
     events: List[Tuple[torch.cuda.Event, torch.cuda.Event]] = field(default_factory=list)
+    noted: List = field(default_factory=list)       # graph mode: the calls, to be replayed
     ms: float = 0.0
 
     def settle(self) -> None:
@@ -44,9 +53,12 @@ class ProfilingKernels:
 
     name = "profiling"
 
-    def __init__(self, kernels, weight_names: Optional[Dict[int, str]] = None):
+    def __init__(self, kernels, weight_names: Optional[Dict[int, str]] = None, mode: str = "events",
+                 pdl: bool = False):
         self.k = kernels
         self.weight_names = weight_names or {}
+        self.mode = mode
+        self.pdl = pdl          # graph mode: capture with programmatic dependent launch, as the decode runner does
         self.phase = "step"
         self.records: "OrderedDict[Tuple[str, str], OpRecord]" = OrderedDict()
 
@@ -57,6 +69,12 @@ class ProfilingKernels:
     # ------------------------------------------------------------------ bookkeeping
     def _timed(self, op: str, nbytes: float, flops: float, fn, *args, **kw):
         rec = self.records.setdefault((self.phase, op), OpRecord())
+        if self.mode == "graph":
+            rec.calls += 1
+            rec.bytes += nbytes
+            rec.flops += flops
+            rec.noted.append((fn, args, kw))
+            return fn(*args, **kw)
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         out = fn(*args, **kw)
@@ -73,10 +91,39 @@ class ProfilingKernels:
         if sleep is not None:
             sleep(int(microseconds * 1900))         # cycles at about 1.9 GHz
 
+    def _replay_noted(self, rec: OpRecord, repeats: int = 5) -> None:
+        """All noted calls of one operation as one graph; the best of a few replays."""
+        import gc
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        gc.collect()
+        if self.pdl:
+            self.k.set_pdl(True)
+        try:
+            with torch.cuda.graph(g):
+                for fn, args, kw in rec.noted:
+                    fn(*args, **kw)
+        finally:
+            if self.pdl:
+                self.k.set_pdl(False)
+        best = None
+        for _ in range(repeats + 1):
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            g.replay()
+            e1.record()
+            torch.cuda.synchronize()
+            t = e0.elapsed_time(e1)
+            best = t if best is None else min(best, t)
+        rec.ms = best
+        rec.noted = []
+
     def table(self) -> List[dict]:
         torch.cuda.synchronize()
         rows = []
         for (phase, op), r in self.records.items():
+            if r.noted:
+                self._replay_noted(r)
             r.settle()
             us = r.ms * 1e3 / max(1, r.calls)
             sec = r.ms * 1e-3
@@ -161,7 +208,8 @@ def weight_names(model) -> Dict[int, str]:
     return names
 
 
-def profile_engine(engine, prompts: Sequence[Sequence[int]], decode_steps: int = 8, sampling=None) -> List[dict]:
+def profile_engine(engine, prompts: Sequence[Sequence[int]], decode_steps: int = 8, sampling=None,
+                   decode_mode: str = "graph") -> List[dict]:
     """One prefill step with every prompt whole and ``decode_steps`` decode steps of all
     rows, each operation timed by CUDA events; returns ``ProfilingKernels.table()``.  The
     sequences are released again."""
@@ -169,31 +217,49 @@ def profile_engine(engine, prompts: Sequence[Sequence[int]], decode_steps: int =
     sampling = sampling or SamplingParams()
     real = engine.rt.k
     prof = ProfilingKernels(real, weight_names(engine.model))
+    if decode_mode == "graph":
+        decode_steps = min(decode_steps, 1)        # one step's calls are noted and replayed per operation
     graphs = engine.decoder.use_graphs
     slots = [engine.new_sequence() for _ in prompts]
+    # as many prompts per prefill step as the engine's step takes
+    per = max(1, engine.max_step_tokens // max(len(p) for p in prompts))
+
+    def prefill():
+        toks = []
+        for i in range(0, len(prompts), per):
+            prof.run_ahead()
+            toks += engine.prefill_sample(slots[i:i + per], prompts[i:i + per], sampling,
+                                          list(range(i, i + len(prompts[i:i + per]))))
+        return toks
+
     try:
         # once unprofiled, so that no first-call set-up (scratch buffers, attributes) is timed
-        toks = engine.prefill_sample(slots, prompts, sampling, list(range(len(prompts))))
+        toks = prefill()
         for s in slots:
             engine.release(s)
         slots = [engine.new_sequence() for _ in prompts]
         engine.rt.k = prof
         engine.decoder.use_graphs = False
         prof.phase = "prefill"
-        prof.run_ahead()
-        toks = engine.prefill_sample(slots, prompts, sampling, list(range(len(prompts))))
+        toks = prefill()
         prof.phase = "decode"
+        if decode_steps:
+            toks = engine.decode_sample(slots, toks, sampling, list(range(len(prompts))))     # first-call set-up, untimed
+            prof.records = OrderedDict((k, v) for k, v in prof.records.items() if k[0] != "decode")
+            prof.mode = decode_mode
+            prof.pdl = len(prompts) <= 16 and hasattr(real, "set_pdl")
         for _ in range(decode_steps):
             if any(engine.length(s) + 1 > engine.max_seq_len for s in slots):
                 break
             prof.run_ahead()
             toks = engine.decode_sample(slots, toks, sampling, list(range(len(prompts))))
+        rows = prof.table()          # graph mode replays the noted calls: the sequences must still be held
     finally:
         engine.rt.k = real
         engine.decoder.use_graphs = graphs
         for s in slots:
             engine.release(s)
-    return prof.table()
+    return rows
 
 
 def format_table(rows: List[dict]) -> str:
