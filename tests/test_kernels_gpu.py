@@ -478,3 +478,60 @@ def test_linear_bf16_tcgen05_few_tokens(K, T):
     K.linear(lg, x.cuda(), w.cuda(), impl="tc")
     close(lg, want, torch.float32, atol=1e-3, rtol=1e-3)
     assert K.gemm_tc_status() == 0
+
+
+@pytest.mark.parametrize("T,nq,nkv,hd,Kin,norm,rope,width", [
+    (500, 4, 2, 128, 256, True, True, 0), (700, 6, 3, 64, 192, True, True, 0), (390, 8, 0, 128, 128, True, True, 0),
+    (450, 3, 1, 32, 96, False, True, 0), (600, 4, 4, 128, 320, True, False, 0), (1100, 5, 1, 128, 512, True, True, 128),
+    (513, 16, 8, 128, 1024, True, True, 256)])
+def test_projection_with_norm_rotation_and_cache_write_in_its_epilogue(K, T, nq, nkv, hd, Kin, norm, rope, width):
+    """The fused q/k/v projection (norm, rotation and cache write in the tcgen05 product's
+    epilogue) against the plain product followed by the plain norm / rotation / write: q, and
+    every key and value where the tokens' positions put them in the paged pool; pages that
+    no token of the step writes must keep their content.  Two sequences with a cached prefix
+    each, so that positions do not start at zero and slots differ."""
+    dt = torch.bfloat16
+    N = (nq + 2 * nkv) * hd
+    x = rnd((T, Kin), dt, 70)
+    w = rnd((N, Kin), dt, 71, scale=0.3)
+    q_w = (1.0 + rnd((hd,), torch.float32, 72, scale=0.1)) if norm else None
+    k_w = (1.0 + rnd((hd,), torch.float32, 73, scale=0.1)) if (norm and nkv) else None
+    half = hd // 2
+    inv = torch.pow(torch.tensor(10000.0, dtype=torch.float64), -2.0 * torch.arange(half, dtype=torch.float64) / hd).float()
+    starts, news = [70, 3], [T - T // 3, T // 3]
+    lens = [s + n for s, n in zip(starts, news)]
+    pool, table, slots = make_paged(max(nkv, 1), hd, lens, dt, 74, n_pages=sum((n + PAGE - 1) // PAGE for n in lens) + 4)
+    pos = torch.cat([torch.arange(s, s + n) for s, n in zip(starts, news)]).to(torch.int32)
+    slot = torch.cat([torch.full((n,), sl) for sl, n in zip(slots, news)]).to(torch.int32)
+    if not K.qkv_rope_supported(x.cuda(), w.cuda(), nq, nkv, hd, hd if rope else 0):
+        pytest.fail("the fused projection refuses a shape it is documented to take")
+    # plain: product (rounded to bf16 as the unfused path stores it), then norm / rotation / write
+    P = PlainKernels()
+    qkv = torch.empty((T, N), dtype=dt)
+    P.linear(qkv, x, w)
+    want_pool = pool.clone()
+    P.qk_norm_rope_write(qkv, q_w, k_w, 1e-6, inv if rope else None, hd if rope else 0, pos, slot,
+                         table if nkv else None, want_pool if nkv else None, nq, nkv, hd)
+    got_pool = pool.clone().cuda()
+    q = torch.empty((T, nq * hd), dtype=dt, device="cuda")
+    cs = None
+    if rope:
+        cs = torch.empty((2, T, half), dtype=torch.float32, device="cuda")
+        K.rope_table(cs, inv.cuda(), hd, pos.cuda())
+        a = pos.float()[:, None] * inv[None, :]
+        torch.testing.assert_close(cs.cpu(), torch.stack([torch.cos(a), torch.sin(a)]), atol=2e-6, rtol=1e-5)
+    K.set_gemm_form("pair" if width else None, width)
+    try:
+        K.linear_qkv_rope(q, x.cuda(), w.cuda(), None if q_w is None else q_w.cuda(), None if k_w is None else k_w.cuda(),
+                          1e-6, cs, pos.cuda(), slot.cuda(), table.cuda() if nkv else None, got_pool if nkv else None,
+                          nq, nkv, hd)
+    finally:
+        K.set_gemm_form(None, 0)
+    assert K.gemm_tc_status() == 0
+    close(q, qkv[:, : nq * hd], dt, atol=3e-2, rtol=3e-2)
+    if nkv:
+        close(got_pool, want_pool, dt, atol=3e-2, rtol=3e-2)
+        written = torch.zeros(pool.shape[0], dtype=torch.bool)
+        for p_, s_ in zip(pos.tolist(), slot.tolist()):
+            written[int(table[s_, p_ // PAGE])] = True
+        assert torch.equal(got_pool.cpu()[~written], pool[~written]), "a page that no token writes was touched"

@@ -132,3 +132,48 @@ def test_unequal_sequences_chunks_and_reused_slots_at_head_size_128(dtype):
     assert eng.cache.slots.held == 0
     if dtype == "bfloat16":
         assert eng.rt.k.gemm_tc_status() == 0
+
+
+@pytest.mark.parametrize("sizes", ["8B", "0.6B"])
+def test_many_token_steps_through_the_fused_projection(sizes):
+    """Steps of more than 384 tokens, where the q/k/v projection carries norm, rotation and
+    cache write in its epilogue: a whole prompt, then two sequences of unequal lengths as
+    one step on top of cached prefixes, then decode steps that read what those epilogues
+    wrote into the cache."""
+    from zlm_b200 import Engine, StepEntry
+    from zlm_b200.parts.model import DecoderModel
+    from zlm_b200.registry import config_from_dict
+    from zlm_b200.sampling import SamplingParams
+    from zlm_b200.weights import random_tensors
+    from zlm_b200.weights.loader import target_dtype
+    dtype = "bfloat16"
+    cfg = config_from_dict(dict(SIZES[sizes], num_hidden_layers=1, vocab_size=2048))
+    tensors = random_tensors(DecoderModel(cfg.to_model_spec()).param_specs(), 8, "cpu", torch.float32)
+    ref_t = reference_tensors(tensors, dtype)
+    specs = DecoderModel(cfg.to_model_spec()).param_specs()
+    dev = {n: t.to("cuda").to(target_dtype(specs[n], t.dtype, torch.bfloat16)) for n, t in tensors.items()}
+    eng = Engine(cfg, dev, torch.bfloat16, "cuda:0", max_tokens=64 * 24, max_batch=3)
+    fused = []
+    real = eng.rt.k.linear_qkv_rope
+    eng.rt.k.linear_qkv_rope = lambda *a, **kw: (fused.append(a[1].shape[0]), real(*a, **kw))[1]
+    try:
+        tol = TOL_8B[dtype]
+        full = random_prompts(cfg.vocab_size, [460, 330, 270], seed=33)
+        want = [plain_logits(ref_t, cfg, p) for p in full]
+        s0 = eng.new_sequence()
+        got = eng.step([StepEntry(s0, full[0][:450], [0, 200, 449])]).clone()
+        assert_close(got, want[0][[0, 200, 449]], dtype, "whole prompt of 450 tokens", tol)
+        s1, s2 = eng.new_sequence(), eng.new_sequence()
+        eng.step([StepEntry(s1, full[1][:20], []), StepEntry(s2, full[2][:7], [])])
+        got = eng.step([StepEntry(s1, full[1][20:320], [299]), StepEntry(s2, full[2][7:260], [0, 252])]).clone()
+        assert_close(got[0], want[1][319], dtype, "second sequence, end of its chunk", tol)
+        assert_close(got[1:], want[2][[7, 259]], dtype, "third sequence, first and last of its chunk", tol)
+        assert fused == [450, 553], f"the fused projection ran for steps of {fused} tokens"
+        for step in range(4):
+            eng.decoder.step([s0, s1, s2], [full[0][450 + step], full[1][320 + step], full[2][260 + step]], SamplingParams())
+            got = eng.decoder.last_logits[:3].clone()
+            for r, (j, base) in enumerate(((0, 450), (1, 320), (2, 260))):
+                assert_close(got[r], want[j][base + step], dtype, f"decode {step} of sequence {j}", tol)
+        assert eng.rt.k.gemm_tc_status() == 0
+    finally:
+        eng.rt.k.linear_qkv_rope = real

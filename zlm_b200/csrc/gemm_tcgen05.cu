@@ -405,6 +405,141 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
 }
 
 // ---------------------------------------------------------------------------
+// MODE 5: the q/k/v projection with what follows it folded into the epilogue: per-head
+// RMSNorm of q and k, the rotation of q and k by the token's position, and the write of k
+// and v into the paged cache; only q goes to Y.  The separate pass over the projection's
+// output (read 25 MB, write 25 MB per layer at 2,048 tokens) disappears, and the norm sees
+// the fp32 sums instead of their bf16 roundings.  An epilogue thread owns one token row of
+// the tile and walks its columns, so a head (head_dim columns, a divisor of the tile's
+// width) is all in one thread: the sum of squares is a first walk over the head's tensor
+// memory columns, the second walk norms, rotates the halves against each other (columns c
+// and c + head_dim/2 of the same thread) and stores.  cos and sin come from a table
+// [2][T][head_dim/2] that is computed once per step for all layers (zlm_rope_table).
+// Order and arithmetic as the stand-alone kernel (rope_kv.cuh): norm, then rotation, then
+// the cache write; v as it is (src/architectures/impl/qwen3/block.zig:26-30,
+// src/kernels/transformer/norm.zig:128-166, src/kernels/transformer/rope.zig:161-206).
+// ---------------------------------------------------------------------------
+struct QkvEpilogue {
+    const void* q_w;            // [hd] norm weights (null: no norm)
+    const void* k_w;
+    int w_dtype;
+    float eps;
+    const float* cos_sin;       // [2][T][hd/2] (null: no rotation)
+    const int* token_pos;       // [T]
+    const int* token_slot;      // [T]
+    const int* block_table;
+    int table_stride;
+    __nv_bfloat16* pool;        // [pages][2][nkv][ZLM_PAGE][hd]
+    int nq, nkv, hd;
+};
+
+__device__ __forceinline__ void qkv_store16(__nv_bfloat16* dst, const float* v) {
+    if (!ZLM_CHK(dst, 32)) return;
+    __nv_bfloat162 t;
+    uint4 a, b;
+#define ZLM_PK2(x, y) (t = __floats2bfloat162_rn(x, y), *(unsigned*)&t)
+    a.x = ZLM_PK2(v[0], v[1]); a.y = ZLM_PK2(v[2], v[3]); a.z = ZLM_PK2(v[4], v[5]); a.w = ZLM_PK2(v[6], v[7]);
+    b.x = ZLM_PK2(v[8], v[9]); b.y = ZLM_PK2(v[10], v[11]); b.z = ZLM_PK2(v[12], v[13]); b.w = ZLM_PK2(v[14], v[15]);
+#undef ZLM_PK2
+    *(uint4*)dst = a;
+    *(uint4*)(dst + 8) = b;
+}
+
+// one token row (this thread's lane of tensor memory at `taddr`, tile columns [n0, n0 + BN))
+template <int BN>
+__device__ __forceinline__ void qkv_epilogue_row(const QkvEpilogue& ep, unsigned taddr, __nv_bfloat16* Y, int row, int n0,
+                                                 int T, int N, int ldy) {
+    const int hd = ep.hd, half = hd >> 1;
+    int pos = 0, page = 0;
+    // a row beyond the step's tokens (or, in the bounds-check build, one whose integers lie outside
+    // the tensors passed) still walks tensor memory with its warp, and stores nothing
+    bool live = row < T && ZLM_CHK(ep.token_pos + row, 4);
+    if (live) {
+        pos = ep.token_pos[row];
+        if (ep.nkv > 0) {
+            live = ZLM_CHK(ep.token_slot + row, 4);
+            if (live) {
+                const int* entry = ep.block_table + (size_t)ep.token_slot[row] * ep.table_stride + pos / ZLM_PAGE;
+                live = ZLM_CHK(entry, 4);
+                if (live) page = *entry;
+            }
+        }
+    }
+    const VecW qw{ep.q_w, ep.w_dtype}, kw{ep.k_w, ep.w_dtype};
+    const float* cs_row = ep.cos_sin ? ep.cos_sin + (size_t)row * half : nullptr;
+    const float* sn_row = ep.cos_sin ? ep.cos_sin + ((size_t)T + row) * half : nullptr;
+    for (int c0 = 0; c0 < BN; c0 += hd) {                 // the tile's heads; warp-uniform
+        const int n = n0 + c0;
+        if (n >= N) break;
+        const int j = n / hd;                             // head among q heads, then k heads, then v heads
+        const int kind = j < ep.nq ? 0 : (j < ep.nq + ep.nkv ? 1 : 2);
+        __nv_bfloat16* dst;
+        if (kind == 0) {
+            dst = Y + (size_t)row * ldy + n;
+        } else {
+            const int kvh = kind == 1 ? j - ep.nq : j - ep.nq - ep.nkv;
+            dst = ep.pool + ((((size_t)page * 2 + (kind - 1)) * ep.nkv + kvh) * ZLM_PAGE + (pos % ZLM_PAGE)) * hd;
+        }
+        if (kind == 2) {
+#pragma unroll 1
+            for (int c = 0; c < hd; c += 16) {
+                float v[16];
+                tc_ld16(taddr + (unsigned)(c0 + c), v);
+                if (live) qkv_store16(dst + c, v);
+            }
+            continue;
+        }
+        const VecW& w = kind == 0 ? qw : kw;
+        float inv = 1.f;
+        if (w.p) {
+            float ss = 0.f;
+#pragma unroll 1
+            for (int c = 0; c < hd; c += 16) {
+                float v[16];
+                tc_ld16(taddr + (unsigned)(c0 + c), v);
+#pragma unroll
+                for (int i = 0; i < 16; ++i) ss = fmaf(v[i], v[i], ss);
+            }
+            inv = 1.0f / sqrtf(ss / (float)hd + ep.eps);
+        }
+#pragma unroll 1
+        for (int c = 0; c < half; c += 16) {
+            float lo[16], hi[16];
+            tc_ld16_nowait(taddr + (unsigned)(c0 + c), lo);
+            tc_ld16_nowait(taddr + (unsigned)(c0 + half + c), hi);
+            tc_wait_ld();
+            if (w.p) {
+#pragma unroll
+                for (int i = 0; i < 16; i += 4) {
+                    const float4 wl = w.load4(c + i), wh = w.load4(half + c + i);
+                    lo[i] = (lo[i] * inv) * wl.x; lo[i + 1] = (lo[i + 1] * inv) * wl.y;
+                    lo[i + 2] = (lo[i + 2] * inv) * wl.z; lo[i + 3] = (lo[i + 3] * inv) * wl.w;
+                    hi[i] = (hi[i] * inv) * wh.x; hi[i + 1] = (hi[i + 1] * inv) * wh.y;
+                    hi[i + 2] = (hi[i + 2] * inv) * wh.z; hi[i + 3] = (hi[i + 3] * inv) * wh.w;
+                }
+            }
+            if (cs_row && live) {
+#pragma unroll
+                for (int i = 0; i < 16; i += 4) {
+                    const float4 cv = *(const float4*)(cs_row + c + i), sv = *(const float4*)(sn_row + c + i);
+                    const float cc[4] = {cv.x, cv.y, cv.z, cv.w}, sn[4] = {sv.x, sv.y, sv.z, sv.w};
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const float x0 = lo[i + e], x1 = hi[i + e];
+                        lo[i + e] = x0 * cc[e] - x1 * sn[e];
+                        hi[i + e] = x0 * sn[e] + x1 * cc[e];
+                    }
+                }
+            }
+            if (live) {
+                qkv_store16(dst + c, lo);
+                qkv_store16(dst + half + c, hi);
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
 // The persistent kernel on pairs of blocks (tcgen05 with cta_group::2): a cluster of two
 // blocks, on neighbouring SMs, walks tiles of 256 tokens x BN outputs.  Each block loads its
 // 128 tokens and its half of the BN rows of W; rank 0 issues 256 x BN x 16 products that read
@@ -420,7 +555,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
 template <int BN, int STAGES, int MODE>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
-                    void* __restrict__ Y, int T, int N, int K, int ldy, int gm) {
+                    void* __restrict__ Y, int T, int N, int K, int ldy, int gm, const QkvEpilogue ep) {
     constexpr unsigned A_BYTES = TC_BM * TC_BK * 2, B_BYTES = (BN / 2) * TC_BK * 2;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -522,11 +657,16 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             tc_fence_after();
             if (!ok || *abort_flag) break;
             const int arow = a0row + lg * 32 + lane;
+            if constexpr (MODE == 5) {
+                qkv_epilogue_row<BN>(ep, tmem_base + ((unsigned)(lg * 32) << 16) + buf * TCP_ACC, (__nv_bfloat16*)Y, arow,
+                                     b0row, T, N, ldy);
+            } else {
 #pragma unroll 1
-            for (int c = 0; c < BN; c += 16) {
-                float v[16];
-                tc_ld16(tmem_base + ((unsigned)(lg * 32) << 16) + buf * TCP_ACC + (unsigned)c, v);
-                store_row16<MODE>(v, Y, arow, b0row + c, T, N, ldy);
+                for (int c = 0; c < BN; c += 16) {
+                    float v[16];
+                    tc_ld16(tmem_base + ((unsigned)(lg * 32) << 16) + buf * TCP_ACC + (unsigned)c, v);
+                    store_row16<MODE>(v, Y, arow, b0row + c, T, N, ldy);
+                }
             }
             tc_fence_before();
             __syncwarp();
@@ -876,7 +1016,8 @@ static int launch_tc_persistent(void* Y, const void* X, const void* W, int T, in
 
 template <int BN, int STAGES>
 static int launch_tc_pair(void* Y, const void* X, const void* W, int T, int N, int K, int ldx, int ldy, int mode,
-                          cudaStream_t st) {
+                          cudaStream_t st, const QkvEpilogue* qkv = nullptr) {
+    const QkvEpilogue ep = qkv ? *qkv : QkvEpilogue{};
     CUtensorMap mx, mw;
     int rc = make_map(&mx, X, T, K, ldx, TC_BM);
     if (rc) return rc;
@@ -897,11 +1038,14 @@ static int launch_tc_pair(void* Y, const void* X, const void* W, int T, int N, i
             }                                                                                              \
             attr_set = true;                                                                               \
         }                                                                                                  \
-        zlm_launch(kern, dim3(2 * pairs), dim3(TC_THREADS), smem, st, mx, mw, Y, T, N, K, ldy, tile_group(TCQ_BM, K)); \
+        zlm_launch(kern, dim3(2 * pairs), dim3(TC_THREADS), smem, st, mx, mw, Y, T, N, K, ldy, tile_group(TCQ_BM, K), ep); \
     }
     if (mode == 0) ZLM_TCQ_LAUNCH(0)
     else if (mode == 1) ZLM_TCQ_LAUNCH(1)
     else if (mode == 2) ZLM_TCQ_LAUNCH(2)
+    else if (mode == 5) {
+        if constexpr (BN == 256 || BN == 128) ZLM_TCQ_LAUNCH(5)
+    }
     else ZLM_TCQ_LAUNCH(3)
 #undef ZLM_TCQ_LAUNCH
     return zlm_check_launch("gemm_tc_pair");
@@ -1051,6 +1195,64 @@ extern "C" int zlm_gemm_tc(void* Y, const void* X, const void* W, int T, int N, 
 
 // 0 if no bounded wait of the kernel ever gave up; else 1 (producer), 2 (product issuer) or 3 (epilogue).
 // Synchronises the device.
+// 1 if the q/k/v projection of T tokens can carry norm, rotation and cache write in its epilogue:
+// the many-token form on pairs of blocks, heads that divide a tile of 256 or 128 columns, the
+// whole head rotated (or none of it).
+extern "C" int zlm_gemm_tc_qkv_supported(int T, int N, int K, int ldx, int nq, int nkv, int hd, int n_rot) {
+    if (!zlm_gemm_tc_supported(T, N, K, ldx) || T <= 384 || g_tc_form == 1) return 0;
+    if (hd < 32 || hd % 32 != 0 || 256 % hd != 0 || N != (nq + 2 * nkv) * hd) return 0;
+    if (n_rot != 0 && n_rot != hd) return 0;
+    if (g_tc_width != 0 && g_tc_width != 256 && g_tc_width != 128) return 0;
+    return 1;
+}
+
+// q [T, nq*hd] bf16 (row stride ldy) = norm+rotate(X Wq^T); k (normed, rotated) and v go to the
+// tokens' places in the paged pool.  cos_sin: [2][T][hd/2] from zlm_rope_table, or null.
+extern "C" int zlm_gemm_tc_qkv(void* Y, const void* X, const void* W, int T, int N, int K, int ldx, int ldy,
+                               const void* q_w, const void* k_w, int w_dtype, float eps, const float* cos_sin,
+                               const int* token_pos, const int* token_slot, const int* block_table, int table_stride,
+                               void* pool, int nq, int nkv, int hd, cudaStream_t st) {
+    if (T == 0) return ZLM_OK;
+    ZLM_REQUIRE(zlm_gemm_tc_qkv_supported(T, N, K, ldx, nq, nkv, hd, cos_sin ? hd : 0),
+                "gemm_tc_qkv: T=%d N=%d K=%d with %d+2x%d heads of %d is not a shape the fused projection takes",
+                T, N, K, nq, nkv, hd);
+    ZLM_REQUIRE(((uintptr_t)X % 16 == 0) && ((uintptr_t)W % 16 == 0) && ((uintptr_t)Y % 16 == 0) && ldy % 8 == 0 &&
+                ((uintptr_t)pool % 16 == 0), "gemm_tc_qkv: operands must be 16-byte aligned");
+    ZLM_REQUIRE((q_w == nullptr) == (k_w == nullptr) || nkv == 0, "gemm_tc_qkv: one norm weight without the other");
+    ZLM_REQUIRE(nkv == 0 || (pool && block_table && token_slot), "gemm_tc_qkv: the cache is missing");
+    QkvEpilogue ep{q_w, k_w, w_dtype, eps, cos_sin, token_pos, token_slot, block_table, table_stride,
+                   (__nv_bfloat16*)pool, nq, nkv, hd};
+    // tiles of whole heads: 256 columns, or 128 where 256 would leave pairs of SMs idle
+    int width = g_tc_width ? g_tc_width : zlm_gemm_tc_tile_width(T, N, K);
+    if (width != 128 || 128 % hd != 0) width = 256;
+    if (width == 128) return launch_tc_pair<128, 8>(Y, X, W, T, N, K, ldx, ldy, 5, st, &ep);
+    return launch_tc_pair<256, 6>(Y, X, W, T, N, K, ldx, ldy, 5, st, &ep);
+}
+
+// cos and sin of pos[t] * inv_freq[i] for the step's tokens: out[0][t][i] = cos, out[1][t][i] = sin.
+// The angle and its sine and cosine are computed in fp32, as the stand-alone rotation kernel does.
+__global__ void rope_table_kernel(float* __restrict__ out, const float* __restrict__ inv_freq,
+                                  const int* __restrict__ token_pos, int T, int half) {
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= T * half) return;
+    const int t = idx / half, i = idx - t * half;
+    if (!ZLM_CHK(token_pos + t, 4) || !ZLM_CHK(inv_freq + i, 4) || !ZLM_CHK(out + idx, 4) ||
+        !ZLM_CHK(out + (size_t)T * half + idx, 4))
+        return;
+    float sn, cs;
+    sincosf((float)token_pos[t] * inv_freq[i], &sn, &cs);
+    out[idx] = cs;
+    out[(size_t)T * half + idx] = sn;
+}
+extern "C" int zlm_rope_table(float* out, const float* inv_freq, int n_rot, const int* token_pos, int T, cudaStream_t st) {
+    if (T == 0 || n_rot == 0) return ZLM_OK;
+    ZLM_REQUIRE(n_rot > 0 && n_rot % 2 == 0 && T > 0, "rope_table: n_rot=%d T=%d", n_rot, T);
+    const int half = n_rot / 2;
+    const long long n = (long long)T * half;
+    zlm_launch(rope_table_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, out, inv_freq, token_pos, T, half);
+    return zlm_check_launch("rope_table");
+}
+
 // ---------------------------------------------------------------------------------------
 // The give-up path on purpose.  One block with the roles of the product kernels, built from
 // the same helpers: the producer loads one tile of `src` by TMA; the issuer allocates tensor

@@ -313,6 +313,48 @@ class CudaKernels:
         assert out.shape == (T, N // 2) and x.stride(1) == 1 and out.stride(1) == 1 and w.is_contiguous()
         self._bf16_product(out, x, w, T, N, K, x.stride(0), out.stride(0), SWIGLU, impl)
 
+    def rope_table(self, out: torch.Tensor, inv_freq: torch.Tensor, n_rot: int, token_pos: torch.Tensor) -> None:
+        """out [2, T, n_rot/2] fp32: cos and sin of token_pos[t] * inv_freq[i], the step's rotation
+        table (the same for every layer with the same frequencies)."""
+        T = token_pos.shape[0]
+        assert out.dtype == torch.float32 and out.is_contiguous() and out.numel() == T * n_rot
+        assert inv_freq.dtype == torch.float32 and inv_freq.numel() * 2 == n_rot and token_pos.dtype == torch.int32
+        self._call("zlm_rope_table", self._p(out), self._p(inv_freq), c_int(n_rot), self._p(token_pos), c_int(T),
+                   self._stream())
+
+    def qkv_rope_supported(self, x: torch.Tensor, w: torch.Tensor, nq: int, nkv: int, hd: int, n_rot: int) -> bool:
+        """Whether ``linear_qkv_rope`` takes this step: bf16, many tokens, heads that divide a tile."""
+        if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+            return False
+        return bool(self.lib.zlm_gemm_tc_qkv_supported(c_int(x.shape[0]), c_int(w.shape[0]), c_int(w.shape[1]),
+                                                       c_int(x.stride(0)), c_int(nq), c_int(nkv), c_int(hd), c_int(n_rot)))
+
+    def linear_qkv_rope(self, q_out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, q_w: Optional[torch.Tensor],
+                        k_w: Optional[torch.Tensor], eps: float, cos_sin: Optional[torch.Tensor],
+                        token_pos: torch.Tensor, token_slot: torch.Tensor, block_table: Optional[torch.Tensor],
+                        pool: Optional[torch.Tensor], nq: int, nkv: int, hd: int) -> None:
+        """The fused q/k/v projection x @ w.T (w rows [q | k | v]) with its epilogue doing what
+        ``qk_norm_rope_write`` does: per-head RMSNorm of q and k, rotation by ``cos_sin`` (from
+        ``rope_table``), k and v into the paged pool; q_out [T, nq*hd] receives q.  With nkv == 0
+        w holds q rows only."""
+        T, K = x.shape
+        N = w.shape[0]
+        assert q_out.shape == (T, nq * hd) and q_out.dtype == torch.bfloat16 and q_out.stride(1) == 1
+        assert w.shape == ((nq + 2 * nkv) * hd, K) and w.is_contiguous() and x.stride(1) == 1
+        if nkv:
+            assert pool is not None and pool.dtype == torch.bfloat16 and pool.is_contiguous()
+            assert tuple(pool.shape[1:]) == (2, nkv, PAGE_TOKENS, hd) and block_table.dtype == torch.int32
+        if q_w is not None:
+            assert q_w.shape == (hd,) and (nkv == 0 or (k_w is not None and k_w.dtype == q_w.dtype))
+        if cos_sin is not None:
+            assert cos_sin.dtype == torch.float32 and cos_sin.numel() == T * hd and cos_sin.is_contiguous()
+        self._call("zlm_gemm_tc_qkv", self._p(q_out), self._p(x), self._p(w), c_int(T), c_int(N), c_int(K),
+                   c_int(x.stride(0)), c_int(q_out.stride(0)), self._p(q_w), self._p(k_w),
+                   c_int(_dt(q_w) if q_w is not None else F32), c_float(eps), self._p(cos_sin),
+                   self._p(token_pos), self._p(token_slot), self._p(block_table),
+                   c_int(block_table.stride(0) if block_table is not None else 0), self._p(pool), c_int(nq), c_int(nkv),
+                   c_int(hd), self._stream())
+
     def qk_norm_rope_write(self, qkv: torch.Tensor, q_w: Optional[torch.Tensor],
                            k_w: Optional[torch.Tensor], eps: float,
                            inv_freq: Optional[torch.Tensor], n_rot: int, token_pos: torch.Tensor,

@@ -99,6 +99,19 @@ class GQAAttention(Mixer):
         cache = io.cache
         writes = cache.writes and self.kv_proj
         fused_pos = getattr(self.position, "fused", False)
+        tbl = cache.block_table if writes else None
+        pool = cache.pool if writes else None
+        # many tokens: norm, rotation and cache write ride in the projection's epilogue
+        w_in = self.w_qkv if writes else self.w_q
+        n_rot = getattr(self.position, "n_rot", 0) if fused_pos else -1
+        if (fused_pos and hasattr(k, "qkv_rope_supported") and (n_rot == 0 or hasattr(self.position, "table"))
+                and k.qkv_rope_supported(x, w_in, self.nq, self.nkv if writes else 0, self.hd, n_rot)):
+            q = rt.ws.get("attn.q", (T, self.Q), rt.dtype)
+            k.linear_qkv_rope(q, x, w_in, self.q_norm, self.k_norm if writes else None, self.eps,
+                              self.position.table(ctx) if n_rot else None, ctx.token_pos, ctx.token_slot, tbl, pool,
+                              self.nq, self.nkv if writes else 0, self.hd)
+            self._attend(q, residual, ctx, cache)
+            return
         if writes:
             qkv = rt.ws.get("attn.qkv", (T, self.Q + 2 * self.KV), rt.dtype)
             k.linear(qkv, x, self.w_qkv)
@@ -108,8 +121,6 @@ class GQAAttention(Mixer):
             k.linear(qkv, x, self.w_q)
             nkv = 0
         q = qkv[:, : self.Q]
-        tbl = cache.block_table if writes else None
-        pool = cache.pool if writes else None
         if fused_pos:
             k.qk_norm_rope_write(qkv, self.q_norm, self.k_norm, self.eps, self.position.inv_freq,
                                  self.position.n_rot, ctx.token_pos, ctx.token_slot, tbl, pool,
@@ -124,7 +135,11 @@ class GQAAttention(Mixer):
             if writes:
                 k.qk_norm_rope_write(qkv, None, None, self.eps, None, 0, ctx.token_pos, ctx.token_slot,
                                      tbl, pool, self.nq, nkv, self.hd)
-        out = rt.ws.get("attn.out", (T, self.Q), rt.dtype)
+        self._attend(q, residual, ctx, cache)
+
+    def _attend(self, q: torch.Tensor, residual: torch.Tensor, ctx: StepContext, cache) -> None:
+        rt, k = self.rt, self.rt.k
+        out = rt.ws.get("attn.out", (q.shape[0], self.Q), rt.dtype)
         key = self.step_key(ctx)
         k.attention(out, q, cache.pool, cache.block_table, ctx.token_pos, ctx.token_slot,
                     self.nq, self.nkv, self.hd, self.scale, self.window, ctx,

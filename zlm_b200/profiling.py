@@ -162,6 +162,16 @@ class ProfilingKernels:
         return self._timed(self._linear_name(w, "linear+swiglu"), n, 2.0 * T * N * K, self.k.linear_swiglu, out, x, w,
                            impl=impl)
 
+    def rope_table(self, out, inv_freq, n_rot, token_pos):
+        return self._timed("rope_table", _nbytes(out), 0, self.k.rope_table, out, inv_freq, n_rot, token_pos)
+
+    def linear_qkv_rope(self, q_out, x, w, *args, **kw):
+        T, K = x.shape
+        N = w.shape[0]
+        n = _nbytes(w) + T * K * x.element_size() + T * N * q_out.element_size()
+        return self._timed(self._linear_name(w, "linear+qk_norm+rope+cache_write"), n, 2.0 * T * N * K,
+                           self.k.linear_qkv_rope, q_out, x, w, *args, **kw)
+
     def qk_norm_rope_write(self, qkv, q_w, k_w, eps, inv_freq, n_rot, token_pos, token_slot, block_table, pool,
                            nq, nkv, hd, write=True):
         T, el = qkv.shape[0], qkv.element_size()
