@@ -220,7 +220,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     } else {
         // epilogue: warp w may touch tensor-memory lanes 32 (w % 4) .. + 31; a lane is a row of the tile
         const int lg = warp & 3;
-        const bool ok = mbar_wait(acc_full, 0, abort_flag, 3);
+        const bool ok = mbar_wait_warp(acc_full, 0, abort_flag, 3);
         tc_fence_after();
         const int arow = a0row + lg * 32 + lane;
         if (ok && !*abort_flag) {
@@ -380,7 +380,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
             int tm, tn;
             tile_of(tile, m_tiles, n_tiles, gm, tm, tn);
             const int a0row = tm * TC_BM, b0row = tn * BN;
-            const bool ok = mbar_wait(&acc_full[buf], (local >> 1) & 1, abort_flag, 3);
+            const bool ok = mbar_wait_warp(&acc_full[buf], (local >> 1) & 1, abort_flag, 3);
             tc_fence_after();
             if (!ok || *abort_flag) break;
             const int arow = a0row + lg * 32 + lane;
@@ -653,7 +653,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             int tm, tn;
             tile_of(tile, m_tiles, n_tiles, gm, tm, tn);
             const int a0row = tm * TCQ_BM + rank * TC_BM, b0row = tn * BN;
-            const bool ok = mbar_wait(&acc_full[buf], (local >> 1) & 1, abort_flag, 3);
+            const bool ok = mbar_wait_warp(&acc_full[buf], (local >> 1) & 1, abort_flag, 3);
             tc_fence_after();
             if (!ok || *abort_flag) break;
             const int arow = a0row + lg * 32 + lane;
@@ -802,7 +802,7 @@ gemm_tc_few_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         for (int item = blockIdx.x; item < items; item += gridDim.x, ++local) {
             ZLM_ITEM(item)
             const unsigned buf = local & 1;
-            const bool ok = mbar_wait(&acc_full[buf], (local >> 1) & 1, abort_flag, 3);
+            const bool ok = mbar_wait_warp(&acc_full[buf], (local >> 1) & 1, abort_flag, 3);
             tc_fence_after();
             if (!ok || *abort_flag) break;
             const int row = a0row + lg * 32 + lane;

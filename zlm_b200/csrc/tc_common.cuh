@@ -44,12 +44,23 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, unsigned parity, volati
     const unsigned long long t0 = tc_now_ns();
     for (unsigned it = 1;; ++it) {
         if (mbar_try(bar, parity)) return true;
-        if (*abort_flag) return false;
+        // the flag and the clock are looked at every few polls only: each look at the flag is a read of
+        // shared memory, and a block's waiting threads would otherwise fill the pipe that the tensor
+        // cores read their operands through
+        if ((it & 7) == 0 && *abort_flag) return false;
         if ((it & 63) == 0 && tc_now_ns() - t0 > limit_ns) break;
     }
     *abort_flag = where;
     zlm_report_status((TC_FAMILY << 8) | where);
     return false;
+}
+// the same for a whole warp: one lane polls, all lanes get the answer (and, through the warp's
+// barrier, see what the arriving threads wrote before)
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, unsigned parity, volatile int* abort_flag, int where) {
+    int ok = 0;
+    if ((threadIdx.x & 31) == 0) ok = mbar_wait(bar, parity, abort_flag, where) ? 1 : 0;
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    return ok != 0;
 }
 // after a wait gave up: lets copies that are still in flight land (at most 10 ms each)
 __device__ __forceinline__ void mbar_drain(uint64_t* bar, unsigned parity) {
