@@ -154,3 +154,26 @@ def test_random_traffic_keeps_the_books():
         c.free_slot(s)
     c.check()
     assert all(g.pages.held == 0 for g in c.groups) and c.slots.held == 0
+
+
+def test_a_request_with_a_record_of_its_own_gets_its_own_paged_pool():
+    """A mixer may keep something other than keys and values per token: the pool then has the
+    record's shape and element type, in a group of its own, paged and freed like the others."""
+    from zlm_b200.parts.base import CacheRequest
+    sched = [ScheduleEntry(0), ScheduleEntry(1), ScheduleEntry(2)]
+    reqs = [CacheRequest(2, 16), CacheRequest(1, 24, token_shape=(24,), dtype=torch.float32),
+            CacheRequest(1, 24, token_shape=(24,), dtype=torch.float32)]
+    c = KVCache(sched, reqs, [None] * 3, 64 * 6, 3, 256, torch.bfloat16, "cpu")
+    assert len(c.groups) == 2
+    kv, latent = c.ios[0].cache, c.ios[1].cache
+    assert tuple(kv.pool.shape) == (6, 2, 2, 64, 16) and kv.pool.dtype == torch.bfloat16
+    assert tuple(latent.pool.shape) == (6, 64, 24) and latent.pool.dtype == torch.float32
+    assert c.ios[2].cache.block_table is latent.block_table and c.ios[2].cache.pool is not latent.pool
+    assert c.bytes_per_token() == 2 * 2 * 16 * 2 + 2 * 24 * 4
+    s = c.alloc_slot()
+    c.reserve([(s, 130)])
+    c.commit([(s, 130)])
+    assert all(g.pages.held == 3 for g in c.groups)
+    c.free_slot(s)
+    c.check()
+    assert all(g.pages.held == 0 for g in c.groups)

@@ -360,3 +360,142 @@ def test_toy_routed_feed_forward_in_one_layer_of_two():
         got = eng.step([StepEntry(sl, [s[i]], [0]) for sl, s in zip(slots, seqs)]).cpu()
         torch.testing.assert_close(got[0], want[0][i], atol=2e-5, rtol=1e-4)
         torch.testing.assert_close(got[1], want[1][i], atol=2e-5, rtol=1e-4)
+
+
+def test_toy_mixer_with_a_cache_record_of_its_own_and_a_step_key():
+    """A mixer that caches a small fp32 latent per token instead of keys and values (its pool
+    has the record's shape and element type, whatever the compute dtype), attends over the
+    latents of its sequence through the block table, and contributes a step key of its own
+    to what a captured decode step is keyed by.  Defined here; no file of the package
+    changes.  (A toy: it is no model of anyone's.)"""
+    from zlm_b200 import Engine, StepEntry
+    from zlm_b200.config import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
+    from zlm_b200.kernels import PAGE_TOKENS
+    from zlm_b200.parts.base import CacheRequest, Mixer, ParamSpec
+    from zlm_b200.parts.model import DecoderModel
+    from zlm_b200.registry import ARCHITECTURES, MIXERS, register_architecture, register_mixer
+    from zlm_b200.weights import random_tensors
+
+    D = 12
+    if "toy_latent" not in MIXERS:
+        @register_mixer("toy_latent")
+        class LatentMixer(Mixer):
+            """c_t = Wc x_t is cached; y_t = Wo sum_s softmax_s(c_t . c_s) c_s over s <= t."""
+            graph_safe = False
+
+            def __init__(self, hidden_size, latent):
+                self.h, self.d = hidden_size, latent
+
+            def param_specs(self):
+                return {"down.weight": ParamSpec((self.d, self.h)), "up.weight": ParamSpec((self.h, self.d))}
+
+            def cache_request(self):
+                return CacheRequest(1, self.d, token_shape=(self.d,), dtype=torch.float32)
+
+            def step_key(self, ctx):
+                return ("toy_latent", ctx.max_len // 16)
+
+            def bind(self, params):
+                self.wc, self.wo = params["down.weight"].float(), params["up.weight"].float()
+
+            def forward(self, x, residual, ctx, io):
+                pool, table = io.cache.pool, io.cache.block_table
+                assert pool.dtype == torch.float32 and tuple(pool.shape[1:]) == (PAGE_TOKENS, self.d)
+                c = x.float() @ self.wc.t()
+                t = 0
+                for slot, start, n in zip(ctx.h_seq_slot, ctx.h_seq_start, ctx.h_seq_new):
+                    pos = torch.arange(start, start + n, device=x.device)
+                    pages = table[slot, (pos // PAGE_TOKENS).long()].long()
+                    pool[pages, pos % PAGE_TOKENS] = c[t:t + n]
+                    allpos = torch.arange(0, start + n, device=x.device)
+                    hist = pool[table[slot, (allpos // PAGE_TOKENS).long()].long(), allpos % PAGE_TOKENS]   # [start+n, d]
+                    s = c[t:t + n] @ hist.t()
+                    s = s.masked_fill(allpos[None, :] > pos[:, None], float("-inf"))
+                    residual[t:t + n] += (torch.softmax(s, -1) @ hist) @ self.wo.t()
+                    t += n
+
+    if "ToyLatentForCausalLM" not in ARCHITECTURES:
+        @register_architecture("ToyLatentForCausalLM")
+        @dataclass(frozen=True)
+        class ToyLatentConfig:
+            eos_token_ids: tuple = ()
+
+            @classmethod
+            def from_dict(cls, d):
+                return cls()
+
+            def to_dict(self):
+                return {"architectures": ["ToyLatentForCausalLM"]}
+
+            def to_model_spec(self):
+                norm = lambda p: PartSpec("rms_norm", {"eps": 1e-5}, prefix=p)
+                l0 = LayerSpec("pre_norm", PartSpec("toy_latent", {"latent": D}, prefix="l0.mix."),
+                               PartSpec("swiglu", {"intermediate_size": 40}, prefix="l0.ffn."), norm("l0.n1."), norm("l0.n2."))
+                l1 = LayerSpec("pre_norm", PartSpec("gqa_attention", {
+                    "num_heads": 2, "num_kv_heads": 1, "head_dim": 16, "qk_norm": True,
+                    "position": {"kind": "rope_half_split", "theta": 1000.0, "head_dim": 16, "n_rot": 16}}, prefix="l1.att."),
+                    PartSpec("swiglu", {"intermediate_size": 40}, prefix="l1.ffn."), norm("l1.n1."), norm("l1.n2."))
+                return ModelSpec("ToyLatentForCausalLM", 32, 70, 512, (l0, l1), (ScheduleEntry(0), ScheduleEntry(1)),
+                                 PartSpec("token_embedding", {}, prefix="emb."), norm("out_norm."),
+                                 PartSpec("lm_head", {"tied": False}, prefix="head."))
+
+    cfg = ARCHITECTURES["ToyLatentForCausalLM"]()
+    t = random_tensors(DecoderModel(cfg.to_model_spec()).param_specs(), 9)
+    for n in t:
+        if "l0.mix" in n:
+            t[n] = t[n] * 20            # the latents matter, and their softmax is peaked
+    dtype = torch.bfloat16
+    dev = {n: (v.to(dtype) if v.dim() == 2 else v).cuda() for n, v in t.items()}
+    ref = {n: (v.to(dtype).float() if v.dim() == 2 else v) for n, v in t.items()}
+    eng = Engine(cfg, dev, dtype, "cuda:0", max_tokens=512, max_batch=2)
+    assert len(eng.cache.groups) == 2 and {g.pool.dtype for g in eng.cache.groups} == {torch.float32, torch.bfloat16}
+
+    def reference(ids):
+        T = len(ids)
+        h = P.embed(ref["emb.weight"], ids)
+        pos = torch.arange(T)
+        x = P.rms_norm(h, ref["l0.n1.weight"], 1e-5).to(dtype).float()
+        c = x @ ref["l0.mix.down.weight"].t()
+        s = (c @ c.t()).masked_fill(pos[None, :] > pos[:, None], float("-inf"))
+        h = h + (torch.softmax(s, -1) @ c) @ ref["l0.mix.up.weight"].t()
+        for l, mix in (("l0", False), ("l1", True)):
+            if mix:
+                x = P.rms_norm(h, ref["l1.n1.weight"], 1e-5)
+                q = P.head_rms_norm(P.linear(x, ref["l1.att.q_proj.weight"]).reshape(T, 2, 16), ref["l1.att.q_norm.weight"], 1e-6)
+                k = P.head_rms_norm(P.linear(x, ref["l1.att.k_proj.weight"]).reshape(T, 1, 16), ref["l1.att.k_norm.weight"], 1e-6)
+                v = P.linear(x, ref["l1.att.v_proj.weight"]).reshape(T, 1, 16)
+                q, k = P.rope_half_split(q, pos, 1000.0, 16), P.rope_half_split(k, pos, 1000.0, 16)
+                h = h + P.linear(P.causal_attention(q, k, v).reshape(T, 32), ref["l1.att.o_proj.weight"])
+            x = P.rms_norm(h, ref[f"{l}.n2.weight"], 1e-5)
+            h = h + P.linear(P.swiglu(P.linear(x, ref[f"{l}.ffn.gate_proj.weight"]), P.linear(x, ref[f"{l}.ffn.up_proj.weight"])),
+                             ref[f"{l}.ffn.down_proj.weight"])
+        return P.linear(P.rms_norm(h, ref["out_norm.weight"], 1e-5), ref["head.weight"])
+
+    g = torch.Generator().manual_seed(10)
+    seqs = [torch.randint(0, 70, (n,), generator=g).tolist() for n in (80, 21)]
+    want = [reference(s) for s in seqs]
+    tol = dict(atol=4e-2, rtol=4e-2)
+    for round_ in range(2):                                    # the second round takes the slots and pages of the first
+        slots = [eng.new_sequence() for _ in seqs]
+        got = eng.step([StepEntry(sl, s[:15], list(range(15))) for sl, s in zip(slots, seqs)]).float().cpu()
+        torch.testing.assert_close(got[:15], want[0][:15], **tol)
+        torch.testing.assert_close(got[15:], want[1][:15], **tol)
+        keys = set()
+        for i in range(15, 80):
+            ents = [StepEntry(slots[0], [seqs[0][i]], [0])]
+            if i < 21:
+                ents.append(StepEntry(slots[1], [seqs[1][i]], [0]))
+            got = eng.step(ents).float().cpu()
+            torch.testing.assert_close(got[0], want[0][i], **tol)
+            if i < 21:
+                torch.testing.assert_close(got[1], want[1][i], **tol)
+        for sl in slots:
+            eng.release(sl)
+        eng.cache.check()
+    # the toy's key is part of what a captured decode step would be keyed by, beside the attention's
+    from zlm_b200.engine.batch import make_context, plan_step
+    s = eng.new_sequence()
+    arrays, T_, R_, _ = plan_step([StepEntry(s, [1], [0])], eng.cache.lengths, 70, eng.layout)
+    key = eng.model.step_key(make_context(eng.stager, arrays, T_, R_, eng.rt.ws))
+    assert ("toy_latent", 0) in key and any(k[0] == "gqa_attention" for k in key)
+    eng.release(s)

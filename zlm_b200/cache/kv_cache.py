@@ -91,8 +91,11 @@ class CacheGroup:
         self.entries = entries
         self.num_pages = num_pages
         self.pages = FreeList(num_pages, "page")
-        self.pool = torch.zeros((len(entries), num_pages, 2, request.num_kv_heads, PAGE_TOKENS,
-                                 request.head_dim), dtype=dtype, device=device)
+        if request.token_shape is not None:
+            shape = (PAGE_TOKENS, *request.token_shape)            # the mixer's own record per token
+        else:
+            shape = (2, request.num_kv_heads, PAGE_TOKENS, request.head_dim)
+        self.pool = torch.zeros((len(entries), num_pages, *shape), dtype=request.dtype or dtype, device=device)
         self.block_table = torch.zeros((num_slots, max_pages_per_slot), dtype=torch.int32, device=device)
         # logical page -> pool page (or -1 once given back by the window) per slot
         self.slot_pages: Dict[int, List[int]] = {}
@@ -188,7 +191,8 @@ class KVCache:
                 if src not in where:
                     raise ValueError(f"schedule[{i}] reads the cache of entry {src}, which keeps none")
                 g, j = where[src]
-                if e.cache_of is not None and (g.request.num_kv_heads, g.request.head_dim) != (r.num_kv_heads, r.head_dim):
+                if e.cache_of is not None and (g.request.num_kv_heads, g.request.head_dim, g.request.token_shape,
+                                               g.request.dtype) != (r.num_kv_heads, r.head_dim, r.token_shape, r.dtype):
                     raise ValueError(f"schedule[{i}] cannot read the cache of entry {src}: different head layout")
                 view = CacheView(pool=g.pool[j], block_table=g.block_table, writes=e.cache_of is None, group=g)
             st = None
@@ -261,5 +265,4 @@ class KVCache:
         return max((g.pages.held for g in self.groups), default=0) * PAGE_TOKENS
 
     def bytes_per_token(self) -> int:
-        el = torch.empty((), dtype=self.dtype).element_size()
-        return sum(2 * g.request.num_kv_heads * g.request.head_dim * el * len(g.entries) for g in self.groups)
+        return sum(g.pool[0, 0].numel() // PAGE_TOKENS * g.pool.element_size() * len(g.entries) for g in self.groups)

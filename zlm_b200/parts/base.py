@@ -45,10 +45,20 @@ class ParamSpec:
 class CacheRequest:
     """What a mixer wants to keep per token: keys and values for ``num_kv_heads``
     heads of ``head_dim``, either all of them (window == 0) or the last
-    ``window``."""
+    ``window``.  The pool is then [pages, 2, kv_heads, PAGE_TOKENS, head_dim] in the
+    compute dtype, the layout the library's attention kernels read.
+
+    A mixer that keeps something else per token (a compressed latent, keys and values of
+    different widths, another element type) names the shape of one token's record in
+    ``token_shape`` and, if it is not the compute dtype, its ``dtype``: the pool is then
+    [pages, PAGE_TOKENS, *token_shape], paged, sized, trimmed by the window and given back
+    like any other, and read by the mixer's own code (``num_kv_heads`` and ``head_dim``
+    are then only part of what tells one group of layers from another)."""
     num_kv_heads: int
     head_dim: int
     window: int = 0
+    token_shape: Optional[Tuple[int, ...]] = None
+    dtype: Optional[torch.dtype] = None
 
 
 @dataclass(frozen=True)
@@ -92,7 +102,8 @@ class Runtime:
 @dataclass
 class CacheView:
     """One schedule entry's share of a cache group: ``pool`` is
-    [pages, 2, kv_heads, PAGE_TOKENS, head_dim]; ``block_table`` [slots, max_pages]
+    [pages, 2, kv_heads, PAGE_TOKENS, head_dim] (or [pages, PAGE_TOKENS, *token_shape] for a
+    request with a record of its own); ``block_table`` [slots, max_pages]
     maps a slot's logical page to a pool page; ``writes`` is False for an entry
     that reads another entry's cache."""
     pool: torch.Tensor

@@ -104,7 +104,11 @@ class DecoderModel:
         """The parts' say on which steps make the same launches (``Part.step_key``): the
         distinct keys of all parts, in the order of their first appearance."""
         seen: List = []
-        for p in list(self.blocks) + [self.embedding, self.final_norm, self.head]:
+        leaves: List[Part] = [self.embedding, self.final_norm, self.head]
+        for b in self.blocks:
+            children = getattr(b, "children", None)
+            leaves += list(children().values()) if children else [b]
+        for p in leaves:
             k = p.step_key(ctx)
             if k is not None and k not in seen:
                 seen.append(k)
