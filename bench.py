@@ -394,7 +394,8 @@ def other_sizes(args, pk, warmup: int) -> dict:
         rec[f"decode_b{b}_frac"] = round(r["frac"], 4)
         if b == 8:
             rec["launches_per_step"] = int(r["launches"])
-            rec["e2e_b8"] = R.e2e(8, 64)["value"]
+        if b in (1, 8):
+            rec[f"e2e_b{b}"] = R.e2e(b, 64)["value"]
     rec["prefill_2048_tok_s"] = R.prefill_2048()["value"]
     R.drop()
     rec.update(unequal_numbers(args, "0.6b"))
