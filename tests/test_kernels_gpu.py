@@ -535,3 +535,19 @@ def test_projection_with_norm_rotation_and_cache_write_in_its_epilogue(K, T, nq,
         for p_, s_ in zip(pos.tolist(), slot.tolist()):
             written[int(table[s_, p_ // PAGE])] = True
         assert torch.equal(got_pool.cpu()[~written], pool[~written]), "a page that no token writes was touched"
+
+
+@pytest.mark.parametrize("R,H,w_dtype", [(512, 64, "float32"), (700, 1000, "bfloat16"), (1500, 4096, "float32"),
+                                         (600, 5120, "float32"), (2100, 8192, "bfloat16"), (513, 2052, "float32")])
+def test_rmsnorm_of_many_rows(K, R, H, w_dtype):
+    """Steps of 512 rows and more with bf16 output run the row-walking kernel (a block takes rows
+    r, r + blocks, ...; more rows than blocks here, and a last round that is not full); rows of
+    very different sizes, so that a row normed with another row's sum shows."""
+    x = rnd((R, H), torch.float32, 90) * (0.01 + torch.arange(R, dtype=torch.float32)[:, None] % 37)
+    w = (1 + rnd((H,), torch.float32, 91, 0.1)).to(DT[w_dtype])
+    assert K.lib.zlm_rmsnorm_walks_rows(1, R, H, 0) == 1
+    want = torch.empty(R, H, dtype=torch.bfloat16)
+    PlainKernels().rmsnorm(want, x, w, 1e-6)
+    got = torch.empty(R, H, dtype=torch.bfloat16, device="cuda")
+    K.rmsnorm(got, x.cuda(), w.cuda(), 1e-6)
+    close(got, want, torch.bfloat16, atol=2e-2, rtol=1e-2)
