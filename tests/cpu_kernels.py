@@ -91,7 +91,7 @@ class PlainKernels:
                 w = torch.softmax(s, 0)
                 out[t, h * hd:(h + 1) * hd] = (w @ V[:, h // group, :]).to(out.dtype)
 
-    def argmax(self, out, logits):
+    def argmax(self, out, logits, fresh=False):
         R, V = logits.shape
         for r in range(R):
             row = logits[r]

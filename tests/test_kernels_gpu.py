@@ -551,3 +551,29 @@ def test_rmsnorm_of_many_rows(K, R, H, w_dtype):
     got = torch.empty(R, H, dtype=torch.bfloat16, device="cuda")
     K.rmsnorm(got, x.cuda(), w.cuda(), 1e-6)
     close(got, want, torch.bfloat16, atol=2e-2, rtol=1e-2)
+
+
+@pytest.mark.parametrize("T,V,Kin", [(1, 1000, 64), (8, 151936, 128), (5, 50021, 72), (3, 40, 200)])
+def test_argmax_from_the_candidates_the_head_product_leaves(K, T, V, Kin):
+    """The few-token product with fp32 output leaves every block's best (value, index) per token;
+    ``argmax(..., fresh=True)`` picks among them.  Ties (equal rows of the weight) must go to the
+    lowest index, in one block and across blocks; a later write into the same tensor by another
+    path must not be answered from stale candidates."""
+    x = rnd((T, Kin), torch.bfloat16, 95)
+    w = rnd((V, Kin), torch.bfloat16, 96, scale=0.3)
+    w[V - 3] = w[7] = w[min(V - 1, 16 + 7)] = w[2] * 3.0           # a tie of four; which row wins differs by token
+    logits = torch.empty((T, V), dtype=torch.float32, device="cuda")
+    K.linear(logits, x.cuda(), w.cuda())
+    got = torch.empty(T, dtype=torch.int32, device="cuda")
+    K.argmax(got, logits, fresh=True)
+    plain = torch.empty(T, dtype=torch.int32, device="cuda")
+    K.argmax(plain, logits)                                        # the two-kernel path over the logits themselves
+    want = torch.empty(T, dtype=torch.int32)
+    PlainKernels().argmax(want, logits.cpu())
+    assert got.cpu().tolist() == plain.cpu().tolist() == want.tolist()
+    # the tensor is written again by something else: fresh candidates there are none
+    logits.copy_(torch.flip(logits, dims=[1]))
+    K.linear(logits, x.cuda(), w.cuda(), impl="mma")
+    logits[:, V // 2] = 1e9
+    K.argmax(got, logits, fresh=True)
+    assert got.cpu().tolist() == [V // 2] * T

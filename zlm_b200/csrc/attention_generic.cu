@@ -130,6 +130,7 @@ extern "C" int zlm_attention_generic(void* out, int out_stride, const void* q, i
     ZLM_REQUIRE(nq <= 65535, "attention: more than 65535 query heads");
     dim3 grid(T, nq);
     const size_t smem = (size_t)(1 + ATT_WARPS) * hd * sizeof(float);
+    zlm_count_launch();
     if (dtype == ZLM_DTYPE_F32)
         attention_generic_kernel<float><<<grid, ATT_WARPS * 32, smem, st>>>(
             (float*)out, out_stride, (const float*)q, q_stride, (const float*)pool, block_table,

@@ -243,6 +243,7 @@ __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.lau
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;\n" ::: "memory"); }
 
 int zlm_pdl_enabled();
+void zlm_count_launch();          // every kernel launch of the library is counted (zlm_launch_count)
 
 template <typename... KArgs, typename... Args>
 static inline void zlm_launch(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
@@ -257,5 +258,6 @@ static inline void zlm_launch(void (*kern)(KArgs...), dim3 grid, dim3 block, siz
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = zlm_pdl_enabled() ? 1 : 0;
+    zlm_count_launch();
     cudaLaunchKernelEx(&cfg, kern, KArgs(args)...);     // errors surface in zlm_check_launch
 }

@@ -31,6 +31,10 @@ int zlm_pdl_enabled() { return g_pdl; }
 // 1: launch the decode-path kernels with programmatic dependent launch; 0: plain stream order
 extern "C" void zlm_set_pdl(int on) { g_pdl = on ? 1 : 0; }
 
+static long long g_launches = 0;
+void zlm_count_launch() { ++g_launches; }
+// kernels launched by the library so far (also those captured into a graph: they are counted when captured)
+extern "C" long long zlm_launch_count() { return g_launches; }
 extern "C" const char* zlm_last_error() { return g_err; }
 extern "C" int zlm_page_tokens() { return ZLM_PAGE; }
 

@@ -71,6 +71,7 @@ extern "C" int zlm_gemm_f32(float* Y, const float* X, const float* W, int T, int
     ZLM_REQUIRE(T > 0 && N > 0 && K > 0 && ldy >= N, "gemm_f32: bad sizes T=%d N=%d K=%d ldy=%d", T, N, K, ldy);
     dim3 grid((N + F32_BN - 1) / F32_BN, (T + F32_BM - 1) / F32_BM);
     ZLM_REQUIRE(grid.y <= 65535, "gemm_f32: more than %d tokens in one step", 65535 * F32_BM);
+    zlm_count_launch();
     if (accumulate) gemm_f32_kernel<1><<<grid, 256, 0, st>>>(Y, X, W, T, N, K, ldy);
     else gemm_f32_kernel<0><<<grid, 256, 0, st>>>(Y, X, W, T, N, K, ldy);
     return zlm_check_launch("gemm_f32");

@@ -52,7 +52,8 @@ __device__ __forceinline__ void gemv_mma(float* c, unsigned a0, unsigned a1, uns
 template <int NT, int MODE>
 __global__ void __launch_bounds__(GEMV_THREADS, GEMV_MINBLOCKS)
 gemv_bf16_kernel(void* __restrict__ Y, const __nv_bfloat16* __restrict__ X,
-                 const __nv_bfloat16* __restrict__ W, int T, int N, int K, int ldx, int ldy, int SEG) {
+                 const __nv_bfloat16* __restrict__ W, int T, int N, int K, int ldx, int ldy, int SEG,
+                 float* __restrict__ best_v, int* __restrict__ best_i) {
     __shared__ float red[GEMV_WARPS][NT][GEMV_ROWS][8];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, q = lane & 3;
@@ -173,15 +174,36 @@ gemv_bf16_kernel(void* __restrict__ Y, const __nv_bfloat16* __restrict__ X,
         const int j = idx / (GEMV_ROWS * 8), rem = idx % (GEMV_ROWS * 8);
         const int tok = j * 8 + rem / GEMV_ROWS, row = rem % GEMV_ROWS;   // rows fastest: coalesced stores
         const int n = n0 + row;
-        if (tok >= T || n >= N) continue;
+        const bool live = tok < T && n < N;
         float s = 0.f;
+        if (live) {
 #pragma unroll
-        for (int w = 0; w < GEMV_WARPS; ++w) s += red[w][j][row][tok & 7];
-        const size_t o = (size_t)tok * ldy + n;
-        if (!ZLM_CHK((char*)Y + o * (MODE == 0 ? 2 : 4), MODE == 0 ? 2 : 4)) continue;
-        if (MODE == 0) ((__nv_bfloat16*)Y)[o] = __float2bfloat16_rn(s);
-        else if (MODE == 1) ((float*)Y)[o] += s;
-        else ((float*)Y)[o] = s;
+            for (int w = 0; w < GEMV_WARPS; ++w) s += red[w][j][row][tok & 7];
+            const size_t o = (size_t)tok * ldy + n;
+            if (ZLM_CHK((char*)Y + o * (MODE == 0 ? 2 : 4), MODE == 0 ? 2 : 4)) {
+                if (MODE == 0) ((__nv_bfloat16*)Y)[o] = __float2bfloat16_rn(s);
+                else if (MODE == 1) ((float*)Y)[o] += s;
+                else ((float*)Y)[o] = s;
+            }
+        }
+        if (MODE == 2 && best_v) {
+            // The logits' argmax starts here: the best of this block's 16 outputs for every token
+            // (16 neighbouring lanes hold a token's 16 rows; every iteration of this loop is taken
+            // by whole warps), ties to the lower index; a second kernel picks among the blocks'
+            // candidates instead of reading the logits again (src/runtime/sampler.zig:14-21).
+            float bv = live ? s : -INFINITY;
+            int bi = live ? n : 0x7fffffff;
+#pragma unroll
+            for (int o2 = 8; o2 > 0; o2 >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, bv, o2);
+                const int oi = __shfl_xor_sync(0xffffffffu, bi, o2);
+                if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+            }
+            if (row == 0 && tok < T) {
+                const size_t c = (size_t)tok * gridDim.x + blockIdx.x;
+                if (ZLM_CHK(best_v + c, 4) && ZLM_CHK(best_i + c, 4)) { best_v[c] = bv; best_i[c] = bi; }
+            }
+        }
     }
     }
 }
@@ -200,20 +222,24 @@ extern "C" int zlm_gemv_segment(int K) {
 
 template <int NT>
 static int launch_gemv(void* Y, const __nv_bfloat16* X, const __nv_bfloat16* W, int T, int N, int K,
-                       int ldx, int ldy, int mode, cudaStream_t st) {
+                       int ldx, int ldy, int mode, float* best_v, int* best_i, cudaStream_t st) {
     const int blocks = (N + GEMV_ROWS - 1) / GEMV_ROWS;
     const int seg = zlm_gemv_segment(K);
-    if (mode == 0) zlm_launch(gemv_bf16_kernel<NT, 0>, blocks, GEMV_THREADS, 0, st, Y, X, W, T, N, K, ldx, ldy, seg);
-    else if (mode == 1) zlm_launch(gemv_bf16_kernel<NT, 1>, blocks, GEMV_THREADS, 0, st, Y, X, W, T, N, K, ldx, ldy, seg);
-    else if (mode == 2) zlm_launch(gemv_bf16_kernel<NT, 2>, blocks, GEMV_THREADS, 0, st, Y, X, W, T, N, K, ldx, ldy, seg);
-    else zlm_launch(gemv_bf16_kernel<NT, 3>, blocks, GEMV_THREADS, 0, st, Y, X, W, T, N, K, ldx, ldy, seg);
+    float* bv = mode == 2 ? best_v : nullptr;
+    int* bi = mode == 2 ? best_i : nullptr;
+    if (mode == 0) zlm_launch(gemv_bf16_kernel<NT, 0>, blocks, GEMV_THREADS, 0, st, Y, X, W, T, N, K, ldx, ldy, seg, bv, bi);
+    else if (mode == 1) zlm_launch(gemv_bf16_kernel<NT, 1>, blocks, GEMV_THREADS, 0, st, Y, X, W, T, N, K, ldx, ldy, seg, bv, bi);
+    else if (mode == 2) zlm_launch(gemv_bf16_kernel<NT, 2>, blocks, GEMV_THREADS, 0, st, Y, X, W, T, N, K, ldx, ldy, seg, bv, bi);
+    else zlm_launch(gemv_bf16_kernel<NT, 3>, blocks, GEMV_THREADS, 0, st, Y, X, W, T, N, K, ldx, ldy, seg, bv, bi);
     return zlm_check_launch("gemv_bf16");
 }
 
 extern "C" int zlm_gemv_max_tokens() { return 16; }
 
-extern "C" int zlm_gemv_bf16(void* Y, const void* X, const void* W, int T, int N, int K, int ldx,
-                             int ldy, int mode, cudaStream_t st) {
+extern "C" int zlm_gemv_blocks(int N) { return (N + GEMV_ROWS - 1) / GEMV_ROWS; }
+
+static int gemv_entry(void* Y, const void* X, const void* W, int T, int N, int K, int ldx, int ldy, int mode,
+                      float* best_v, int* best_i, cudaStream_t st) {
     if (T == 0 || N == 0) return ZLM_OK;
     ZLM_REQUIRE(T > 0 && T <= 16, "gemv_bf16: takes 1 to 16 tokens, got %d", T);
     ZLM_REQUIRE(N > 0 && K > 0, "gemv_bf16: bad sizes N=%d K=%d", N, K);
@@ -224,8 +250,21 @@ extern "C" int zlm_gemv_bf16(void* Y, const void* X, const void* W, int T, int N
     ZLM_REQUIRE(mode != 3 || N % 16 == 0, "gemv_bf16: the fused gate/up product needs N=%d to be a multiple of 16", N);
     const __nv_bfloat16* x = (const __nv_bfloat16*)X;
     const __nv_bfloat16* w = (const __nv_bfloat16*)W;
-    if (T <= 8) return launch_gemv<1>(Y, x, w, T, N, K, ldx, ldy, mode, st);
-    return launch_gemv<2>(Y, x, w, T, N, K, ldx, ldy, mode, st);
+    if (T <= 8) return launch_gemv<1>(Y, x, w, T, N, K, ldx, ldy, mode, best_v, best_i, st);
+    return launch_gemv<2>(Y, x, w, T, N, K, ldx, ldy, mode, best_v, best_i, st);
+}
+
+extern "C" int zlm_gemv_bf16(void* Y, const void* X, const void* W, int T, int N, int K, int ldx,
+                             int ldy, int mode, cudaStream_t st) {
+    return gemv_entry(Y, X, W, T, N, K, ldx, ldy, mode, nullptr, nullptr, st);
+}
+
+// Y fp32 [T, N] = X W^T, and for every token the best (value, index) of each block's 16 outputs:
+// best_v / best_i [T][zlm_gemv_blocks(N)], what zlm_argmax_candidates picks the row's argmax from.
+extern "C" int zlm_gemv_bf16_best(void* Y, const void* X, const void* W, int T, int N, int K, int ldx, int ldy,
+                                  float* best_v, int* best_i, cudaStream_t st) {
+    ZLM_REQUIRE(best_v && best_i, "gemv_bf16_best: the candidates' arrays are missing");
+    return gemv_entry(Y, X, W, T, N, K, ldx, ldy, 2, best_v, best_i, st);
 }
 
 ZLM_TRANSLATION_UNIT(gemv_bf16)

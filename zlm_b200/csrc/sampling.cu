@@ -94,6 +94,49 @@ extern "C" int zlm_argmax(int* out, const float* logits, int R, int V, int ld, f
     return zlm_check_launch("argmax_final");
 }
 
+// the row's argmax from `n` candidates (value, index) that the product of the logits left
+// (one per block of 16 outputs): one block per row, the same tie rule
+__global__ void __launch_bounds__(ARGMAX_THREADS)
+argmax_candidates_kernel(int* __restrict__ out, const float* __restrict__ cv, const int* __restrict__ ci, int n) {
+    __shared__ float bv[32];
+    __shared__ int bi[32];
+    pdl_launch_dependents();
+    pdl_wait();
+    const float* v = cv + (size_t)blockIdx.x * n;
+    const int* ix = ci + (size_t)blockIdx.x * n;
+    if (!ZLM_CHK(v, (size_t)n * 4) || !ZLM_CHK(ix, (size_t)n * 4) || !ZLM_CHK(out + blockIdx.x, 4)) return;
+    float best = -INFINITY;
+    int idx = 0x7fffffff;
+    for (int c = threadIdx.x; c < n; c += ARGMAX_THREADS)
+        if (argmax_better(v[c], ix[c], best, idx)) { best = v[c]; idx = ix[c]; }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+        if (argmax_better(ov, oi, best, idx)) { best = ov; idx = oi; }
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) { bv[warp] = best; bi[warp] = idx; }
+    __syncthreads();
+    if (warp == 0) {
+        best = lane < ARGMAX_THREADS / 32 ? bv[lane] : -INFINITY;
+        idx = lane < ARGMAX_THREADS / 32 ? bi[lane] : 0x7fffffff;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+            if (argmax_better(ov, oi, best, idx)) { best = ov; idx = oi; }
+        }
+        if (lane == 0) out[blockIdx.x] = idx == 0x7fffffff ? 0 : idx;
+    }
+}
+extern "C" int zlm_argmax_candidates(int* out, const float* cand_v, const int* cand_i, int R, int n, cudaStream_t st) {
+    if (R == 0) return ZLM_OK;
+    ZLM_REQUIRE(R > 0 && n > 0 && cand_v && cand_i, "argmax_candidates: bad sizes R=%d n=%d", R, n);
+    zlm_launch(argmax_candidates_kernel, dim3(R), dim3(ARGMAX_THREADS), 0, st, out, cand_v, cand_i, n);
+    return zlm_check_launch("argmax_candidates");
+}
+
 // ---------------------------------------------------------------------------
 // Temperature / top-k / top-p sampling, one block per row.
 //

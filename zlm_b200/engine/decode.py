@@ -166,7 +166,7 @@ class DecodeRunner:
     def _choose(self, logits: torch.Tensor, R: int, params: SamplingParams) -> None:
         e = self.e
         if params.greedy:
-            e.rt.k.argmax(self.out[:R], logits)
+            e.rt.k.argmax(self.out[:R], logits, fresh=True)      # straight from the model's head
         else:
             e.rt.k.sample(self.out[:R], logits, params.temperature, params.top_k, params.top_p, params.seed,
                           e.stager.view("sample_request", R), e.stager.view("sample_position", R))

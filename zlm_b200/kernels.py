@@ -100,6 +100,7 @@ class CudaKernels:
         self.lib_path = library_path(verbose=verbose_build, variant=variant)
         self.lib = ctypes.CDLL(self.lib_path)
         self.lib.zlm_last_error.restype = ctypes.c_char_p
+        self.lib.zlm_launch_count.restype = ctypes.c_longlong
         if self.lib.zlm_page_tokens() != PAGE_TOKENS:
             raise KernelError("kernel library and Python disagree on the cache page size")
         if not torch.cuda.is_available():
@@ -115,6 +116,7 @@ class CudaKernels:
         self.decode_blocks: Optional[int] = None
         self.sm_count = int(torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count)
         self._fn = {}
+        self._candidates = None        # (address of the last logits a few-token product wrote, rows, width, blocks, values, indices)
         self._scratch = {}
         self.scratch_generation = 0
         self._launches = 0
@@ -130,8 +132,9 @@ class CudaKernels:
         return buf
 
     def launches(self) -> int:
-        """Kernel launches issued through this object so far."""
-        return self._launches
+        """Kernels that the library has launched so far (those captured into a graph are counted
+        once, when they are captured)."""
+        return int(self.lib.zlm_launch_count())
 
     # -- plumbing ---------------------------------------------------------
     def _call(self, name: str, *args):
@@ -251,6 +254,8 @@ class CudaKernels:
         ``impl`` forces one (tests)."""
         T, K = x.shape
         N = w.shape[0]
+        if self._candidates is not None and self._candidates[0] == out.data_ptr():
+            self._candidates = None         # whatever writes this tensor now, the old candidates are not its
         assert w.shape[1] == K and out.shape == (T, N) and w.dtype == x.dtype
         assert x.stride(1) == 1 and out.stride(1) == 1 and w.is_contiguous()
         ldx, ldy = x.stride(0), out.stride(0)
@@ -284,6 +289,17 @@ class CudaKernels:
             self._call("zlm_gemm_tc", self._p(out), self._p(x), self._p(w),
                        c_int(T), c_int(N), c_int(K), c_int(ldx), c_int(ldy), c_int(mode), self._p(scratch),
                        self._stream())
+            return
+        if impl == "gemv" and mode == STORE_F32 and out.is_contiguous():
+            # fp32 outputs of a few-token product are logits: the product also leaves, for every
+            # token, the best of each block's 16 outputs, and ``argmax`` of the same tensor picks
+            # among those candidates instead of reading the logits again
+            nb = int(self.lib.zlm_gemv_blocks(c_int(N)))
+            cv = self.scratch("gemv.best_values", T * nb, torch.float32, out.device)
+            ci = self.scratch("gemv.best_indices", T * nb, torch.int32, out.device)
+            self._call("zlm_gemv_bf16_best", self._p(out), self._p(x), self._p(w), c_int(T), c_int(N), c_int(K),
+                       c_int(ldx), c_int(ldy), self._p(cv), self._p(ci), self._stream())
+            self._candidates = (out.data_ptr(), T, N, nb, cv, ci)
             return
         name = {"gemv": "zlm_gemv_bf16", "mma": "zlm_gemm_bf16_mma"}[impl]
         self._call(name, self._p(out), self._p(x), self._p(w),
@@ -442,10 +458,19 @@ class CudaKernels:
                    self._p(token_pos), self._p(token_slot), c_int(T), c_int(nq),
                    c_int(nkv), c_int(hd), c_float(scale), c_int(window), self._stream())
 
-    def argmax(self, out: torch.Tensor, logits: torch.Tensor) -> None:
-        """out[r] = index of the highest logit of row r, ties to the lowest index."""
+    def argmax(self, out: torch.Tensor, logits: torch.Tensor, fresh: bool = False) -> None:
+        """out[r] = index of the highest logit of row r, ties to the lowest index.  ``fresh``: the
+        caller vouches that ``logits`` is what ``linear`` wrote last into this tensor and nothing
+        has written it since (the engine's logits on their way to the sampler); the few-token
+        product then has left every block's best candidates, and the logits are not read again."""
         R, V = logits.shape
         assert logits.dtype == torch.float32 and logits.stride(1) == 1 and out.dtype == torch.int32
+        cand = self._candidates if fresh else None
+        if cand is not None and cand[0] == logits.data_ptr() and cand[1] >= R and cand[2] == V and logits.is_contiguous():
+            # these logits came from the few-token product just before: it left the candidates
+            _, _, _, nb, cv, ci = cand
+            self._call("zlm_argmax_candidates", self._p(out), self._p(cv), self._p(ci), c_int(R), c_int(nb), self._stream())
+            return
         sv = self.scratch("argmax.values", R * 64, torch.float32, logits.device)
         si = self.scratch("argmax.indices", R * 64, torch.int32, logits.device)
         self._call("zlm_argmax", self._p(out), self._p(logits), c_int(R), c_int(V),

@@ -195,8 +195,8 @@ class ProfilingKernels:
         return self._timed(kind, n, 4.0 * nq * hd * pairs, self.k.attention, out, q, pool, block_table, token_pos,
                            token_slot, nq, nkv, hd, scale, window, plan, len_bucket=len_bucket)
 
-    def argmax(self, out, logits):
-        return self._timed("argmax", _nbytes(logits), 0, self.k.argmax, out, logits)
+    def argmax(self, out, logits, fresh=False):
+        return self._timed("argmax", _nbytes(logits), 0, self.k.argmax, out, logits, fresh=fresh)
 
     def sample(self, out, logits, *args, **kw):
         return self._timed("sample", _nbytes(logits), 0, self.k.sample, out, logits, *args, **kw)

@@ -64,7 +64,7 @@ class Sampler:
         R = logits.shape[0]
         out = self.rt.ws.get("sampler.out", (R,), torch.int32)
         if params.greedy:
-            self.rt.k.argmax(out, logits)
+            self.rt.k.argmax(out, logits, fresh=True)      # straight from the model's head
         else:
             self.rt.k.sample(out, logits, params.temperature, params.top_k, params.top_p, params.seed,
                              request, position)
