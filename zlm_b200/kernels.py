@@ -274,14 +274,22 @@ class CudaKernels:
             assert out.dtype == torch.bfloat16
         self._bf16_product(out, x, w, T, N, K, ldx, ldy, mode, impl)
 
+    # outputs from which a product counts as "as wide as a vocabulary" (see streams_weights)
+    WIDE_PRODUCT = 65536
+
+    def streams_weights(self, tokens: int, N: int) -> bool:
+        """Whether a bf16 product of this many tokens and N outputs runs as the register-fragment
+        streaming product (else a tcgen05 form).  Measured at Qwen3-8B sizes: it wins up to 16
+        tokens (a layer's four products at 9 / 16 tokens: 78 / 84 us against 88 / 90 us), except
+        for products as wide as a vocabulary, whose thousand tiles the persistent tcgen05 form
+        streams faster from 9 tokens on (191 against 197 to 216 us)."""
+        return tokens <= 8 or (tokens <= 16 and N < self.WIDE_PRODUCT)
+
     def _bf16_product(self, out, x, w, T, N, K, ldx, ldy, mode, impl) -> None:
         if impl is None:
-            # measured at Qwen3-8B sizes: the register-fragment GEMV wins up to 16 tokens (a layer's
-            # four products at 9 / 16 tokens: 78 / 84 us against 88 / 90 us), except for the head,
-            # whose 1,187 tiles the persistent tcgen05 form streams faster from 9 tokens on
-            # (191 against 197 to 216 us); from 17 tokens on the tcgen05 forms
+            # few tokens: the streaming product; from 17 tokens on the tcgen05 forms
             tc_ok = self.lib.zlm_gemm_tc_supported(T, N, K, ldx)
-            small = T <= 8 or (T <= 16 and N < 65536)
+            small = self.streams_weights(T, N)
             impl = "gemv" if (small or (T <= 16 and not tc_ok)) else ("tc" if tc_ok else "mma")
         if impl == "tc":
             ks = self.lib.zlm_gemm_tc_ksplit(T, N, K)
