@@ -516,9 +516,9 @@ def test_projection_with_norm_rotation_and_cache_write_in_its_epilogue(K, T, nq,
     q = torch.empty((T, nq * hd), dtype=dt, device="cuda")
     cs = None
     if rope:
-        cs = torch.empty((2, T, half), dtype=torch.float32, device="cuda")
+        cs = torch.empty((2, half, T), dtype=torch.float32, device="cuda")
         K.rope_table(cs, inv.cuda(), hd, pos.cuda())
-        a = pos.float()[:, None] * inv[None, :]
+        a = inv[:, None] * pos.float()[None, :]
         torch.testing.assert_close(cs.cpu(), torch.stack([torch.cos(a), torch.sin(a)]), atol=2e-6, rtol=1e-5)
     K.set_gemm_form("pair" if width else None, width)
     try:

@@ -414,7 +414,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __gri
 // width) is all in one thread: the sum of squares is a first walk over the head's tensor
 // memory columns, the second walk norms, rotates the halves against each other (columns c
 // and c + head_dim/2 of the same thread) and stores.  cos and sin come from a table
-// [2][T][head_dim/2] that is computed once per step for all layers (zlm_rope_table).
+// [2][head_dim/2][T] that is computed once per step for all layers (zlm_rope_table).
 // Order and arithmetic as the stand-alone kernel (rope_kv.cuh): norm, then rotation, then
 // the cache write; v as it is (src/architectures/impl/qwen3/block.zig:26-30,
 // src/kernels/transformer/norm.zig:128-166, src/kernels/transformer/rope.zig:161-206).
@@ -424,7 +424,7 @@ struct QkvEpilogue {
     const void* k_w;
     int w_dtype;
     float eps;
-    const float* cos_sin;       // [2][T][hd/2] (null: no rotation)
+    const float* cos_sin;       // [2][hd/2][T] (null: no rotation)
     const int* token_pos;       // [T]
     const int* token_slot;      // [T]
     const int* block_table;
@@ -466,8 +466,9 @@ __device__ __forceinline__ void qkv_epilogue_row(const QkvEpilogue& ep, unsigned
         }
     }
     const VecW qw{ep.q_w, ep.w_dtype}, kw{ep.k_w, ep.w_dtype};
-    const float* cs_row = ep.cos_sin ? ep.cos_sin + (size_t)row * half : nullptr;
-    const float* sn_row = ep.cos_sin ? ep.cos_sin + ((size_t)T + row) * half : nullptr;
+    // the table is [2][hd/2][T]: the warp's 32 rows read 32 neighbouring floats of one angle
+    const float* cs_row = ep.cos_sin ? ep.cos_sin + min(row, T - 1) : nullptr;
+    const float* sn_row = ep.cos_sin ? ep.cos_sin + (size_t)half * T + min(row, T - 1) : nullptr;
     for (int c0 = 0; c0 < BN; c0 += hd) {                 // the tile's heads; warp-uniform
         const int n = n0 + c0;
         if (n >= N) break;
@@ -519,16 +520,17 @@ __device__ __forceinline__ void qkv_epilogue_row(const QkvEpilogue& ep, unsigned
                 }
             }
             if (cs_row && live) {
+                float cc[16], sn[16];
 #pragma unroll
-                for (int i = 0; i < 16; i += 4) {
-                    const float4 cv = *(const float4*)(cs_row + c + i), sv = *(const float4*)(sn_row + c + i);
-                    const float cc[4] = {cv.x, cv.y, cv.z, cv.w}, sn[4] = {sv.x, sv.y, sv.z, sv.w};
+                for (int e = 0; e < 16; ++e) {
+                    cc[e] = __ldg(cs_row + (size_t)(c + e) * T);
+                    sn[e] = __ldg(sn_row + (size_t)(c + e) * T);
+                }
 #pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const float x0 = lo[i + e], x1 = hi[i + e];
-                        lo[i + e] = x0 * cc[e] - x1 * sn[e];
-                        hi[i + e] = x0 * sn[e] + x1 * cc[e];
-                    }
+                for (int e = 0; e < 16; ++e) {
+                    const float x0 = lo[e], x1 = hi[e];
+                    lo[e] = x0 * cc[e] - x1 * sn[e];
+                    hi[e] = x0 * sn[e] + x1 * cc[e];
                 }
             }
             if (live) {
@@ -1279,7 +1281,7 @@ extern "C" int zlm_gemm_tc_qkv_supported(int T, int N, int K, int ldx, int nq, i
 }
 
 // q [T, nq*hd] bf16 (row stride ldy) = norm+rotate(X Wq^T); k (normed, rotated) and v go to the
-// tokens' places in the paged pool.  cos_sin: [2][T][hd/2] from zlm_rope_table, or null.
+// tokens' places in the paged pool.  cos_sin: [2][hd/2][T] from zlm_rope_table, or null.
 extern "C" int zlm_gemm_tc_qkv(void* Y, const void* X, const void* W, int T, int N, int K, int ldx, int ldy,
                                const void* q_w, const void* k_w, int w_dtype, float eps, const float* cos_sin,
                                const int* token_pos, const int* token_slot, const int* block_table, int table_stride,
@@ -1307,7 +1309,7 @@ __global__ void rope_table_kernel(float* __restrict__ out, const float* __restri
                                   const int* __restrict__ token_pos, int T, int half) {
     const int idx = blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= T * half) return;
-    const int t = idx / half, i = idx - t * half;
+    const int i = idx / T, t = idx - i * T;         // [cos | sin][angle][token]: a warp of the product's epilogue reads along tokens
     if (!ZLM_CHK(token_pos + t, 4) || !ZLM_CHK(inv_freq + i, 4) || !ZLM_CHK(out + idx, 4) ||
         !ZLM_CHK(out + (size_t)T * half + idx, 4))
         return;

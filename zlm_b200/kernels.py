@@ -338,8 +338,9 @@ class CudaKernels:
         self._bf16_product(out, x, w, T, N, K, x.stride(0), out.stride(0), SWIGLU, impl)
 
     def rope_table(self, out: torch.Tensor, inv_freq: torch.Tensor, n_rot: int, token_pos: torch.Tensor) -> None:
-        """out [2, T, n_rot/2] fp32: cos and sin of token_pos[t] * inv_freq[i], the step's rotation
-        table (the same for every layer with the same frequencies)."""
+        """out [2, n_rot/2, T] fp32: cos and sin of token_pos[t] * inv_freq[i], the step's rotation
+        table (the same for every layer with the same frequencies); tokens innermost, so that the
+        32 token rows of a warp in the projection's epilogue read neighbouring floats."""
         T = token_pos.shape[0]
         assert out.dtype == torch.float32 and out.is_contiguous() and out.numel() == T * n_rot
         assert inv_freq.dtype == torch.float32 and inv_freq.numel() * 2 == n_rot and token_pos.dtype == torch.int32

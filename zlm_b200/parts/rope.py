@@ -35,13 +35,13 @@ class RotaryHalfSplit(PositionEncoding):
         self.inv_freq = inv.to(torch.float32).to(rt.device)
 
     def table(self, ctx: StepContext) -> torch.Tensor:
-        """cos and sin of every token of the step at this part's frequencies, [2, T, n_rot/2]
+        """cos and sin of every token of the step at this part's frequencies, [2, n_rot/2, T]
         fp32: computed by the first layer that asks in a step and shared by all layers with
         the same frequencies (the positions of a step are the same in every layer)."""
         key = ("rope_table", self.theta, self.head_dim, self.n_rot)
         t = ctx.extras.get(key)
         if t is None:
-            t = ctx.scratch(f"rope.table.{self.theta}.{self.head_dim}.{self.n_rot}", (2, ctx.T, self.n_rot // 2),
+            t = ctx.scratch(f"rope.table.{self.theta}.{self.head_dim}.{self.n_rot}", (2, self.n_rot // 2, ctx.T),
                             torch.float32)
             self.rt.k.rope_table(t, self.inv_freq, self.n_rot, ctx.token_pos)
             ctx.extras[key] = t
