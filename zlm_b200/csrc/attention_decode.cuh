@@ -1,6 +1,6 @@
-// The bodies of the decode attention kernels as functions of a group of warps, so that
-// the stand-alone kernels and the persistent decode kernel run the same code in the same
-// order of sums.  What they compute is described in attention_decode.cu.
+// The bodies of the decode attention kernels as functions of a group of warps (the kernels
+// in attention_decode.cu run them with the block as the group).  What they compute is
+// described in attention_decode.cu.
 #pragma once
 #include "common.cuh"
 #include "attn_common.cuh"

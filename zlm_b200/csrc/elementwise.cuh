@@ -1,5 +1,5 @@
-// Row functions of the embedding gather and of RMSNorm, shared by the stand-alone
-// kernels (elementwise.cu) and the persistent decode kernel.
+// Row functions of the embedding gather and of RMSNorm, as functions of a group of threads
+// (the kernels in elementwise.cu run them with the block as the group).
 #pragma once
 #include "common.cuh"
 

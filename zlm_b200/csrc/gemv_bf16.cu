@@ -71,8 +71,7 @@ gemv_bf16_kernel(void* __restrict__ Y, const __nv_bfloat16* __restrict__ X,
     // (one chain would run at the latency of the instruction).  K is cut into chunks of
     // 8 x SEG columns; warp w takes the w-th SEG columns of every chunk, as blocks of 32
     // in ascending k; chain 2 * (i & 1) + h takes the h-th 16 k of block i.  The chains are
-    // added at the end, (0 + 1) + (2 + 3).  SEG is 512 (the persistent decode kernel,
-    // decode_stream.cu, adds in that order) unless another width spreads K evenly over the
+    // added at the end, (0 + 1) + (2 + 3).  SEG is 512 unless another width spreads K evenly over the
     // warps where 512 would not (gemv_segment below).
     float ch[NT][4][4];
 #pragma unroll

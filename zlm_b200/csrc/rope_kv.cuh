@@ -1,6 +1,5 @@
 // The body of the q/k norm + rotation + cache write kernel as a function of a group of
-// warps (see rope_kv.cu for what it computes), shared by the stand-alone kernel and the
-// persistent decode kernel.
+// warps (see rope_kv.cu for what it computes; its kernel runs it with the block as the group).
 #pragma once
 #include "common.cuh"
 
