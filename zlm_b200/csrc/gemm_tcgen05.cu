@@ -554,15 +554,18 @@ __device__ __forceinline__ void qkv_epilogue_row(const QkvEpilogue& ep, unsigned
 // epilogue warps of both blocks.
 // ---------------------------------------------------------------------------
 #define TCQ_BM 256
-// Where the epilogue adds into the fp32 stream it hands the sums to the copy engine: a warp
-// puts 32 rows x 16 columns of its accumulator into shared memory (TCQ_RING such boxes of its
-// own, in the 64-byte swizzle, which keeps the row-per-thread 16-byte writes free of bank
-// conflicts) and one reduce-add of the box (cp.reduce.async.bulk.tensor, .add on f32) does the
-// read-modify-write in L2.  The row-per-thread loads and stores that it replaces touched 32
-// rows per instruction, 32 memory transactions each: 20 us for a tile of 256 x 240, as long as
-// the tile's products at K = 4,096 and all of it exposed after a block's last tile.
+// The epilogue hands its results to the copy engine: a warp puts 32 rows x 64 bytes of output
+// into shared memory (TCQ_RING such boxes of its own, in the 64-byte swizzle, which keeps the
+// row-per-thread 16-byte writes free of bank conflicts) and one bulk store of the box writes
+// them; where the product adds into the fp32 stream, one reduce-add of the box
+// (cp.reduce.async.bulk.tensor, .add on f32) does the read-modify-write in L2.  The
+// row-per-thread loads and stores that this replaces touched 32 rows per instruction, 32
+// memory transactions each: 20 us for the fp32 stream's tile of 256 x 240, as long as the
+// tile's products at K = 4,096 and all of it exposed after a block's last tile.  The copy
+// engine clips a box at the matrix's edges.  TCQ_BOX_ACC: accumulator columns that make a box.
 #define TCQ_RING 4
-#define TCQ_BOX_BYTES (32 * 16 * 4)
+#define TCQ_BOX_BYTES (32 * 64)
+#define TCQ_BOX_ACC(MODE) ((MODE) == 3 ? 64 : (MODE) == 0 ? 32 : 16)
 #define TCQ_OUT_BYTES (4 * TCQ_RING * TCQ_BOX_BYTES)
 template <int BN, int STAGES, int MODE>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1)
@@ -674,30 +677,61 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             if constexpr (MODE == 5) {
                 qkv_epilogue_row<BN>(ep, tmem_base + ((unsigned)(lg * 32) << 16) + buf * TCP_ACC, (__nv_bfloat16*)Y, arow,
                                      b0row, T, N, ldy);
-            } else if (MODE == 1 && y_tma) {
+            } else if (y_tma && BN % TCQ_BOX_ACC(MODE) == 0) {
+                // a box is 32 rows x 64 bytes of output: 16 fp32 sums, 32 bf16 values, or the 32 bf16
+                // results of 64 gate/up sums; a thread writes its row's four 16-byte pieces
+                constexpr int ACC = TCQ_BOX_ACC(MODE);
                 const unsigned taddr = tmem_base + ((unsigned)(lg * 32) << 16) + buf * TCP_ACC;
                 unsigned char* const ring = sOut + lg * (TCQ_RING * TCQ_BOX_BYTES);
+                const int n_out = MODE == 3 ? N / 2 : N;
 #pragma unroll 1
-                for (int c = 0; c < BN; c += 16, ++boxes) {
-                    if (b0row + c >= N || a0row + lg * 32 >= T) break;     // nothing of this box lies inside (warp-uniform)
+                for (int c = 0; c < BN; c += ACC, ++boxes) {
+                    const int x = MODE == 3 ? (b0row + c) / 2 : b0row + c;
+                    if (x >= n_out || a0row + lg * 32 >= T) break;     // nothing of this box lies inside (warp-uniform)
                     // the box about to be overwritten was handed over TCQ_RING boxes ago: wait until
                     // the copy engine has read it (the later ones may still be on their way)
                     if (lane == 0) asm volatile("cp.async.bulk.wait_group.read %0;\n" ::"n"(TCQ_RING - 1) : "memory");
                     __syncwarp();
-                    float v[16];
-                    tc_ld16(taddr + (unsigned)c, v);
                     unsigned char* const row = ring + (boxes % TCQ_RING) * TCQ_BOX_BYTES + lane * 64;
                     const int sw = (lane >> 1) & 3;
+                    __nv_bfloat162 t;
+#define ZLM_PK(a, b) (t = __floats2bfloat162_rn(a, b), *(unsigned*)&t)
 #pragma unroll
-                    for (int j = 0; j < 4; ++j)
-                        *(float4*)(row + ((j ^ sw) << 4)) = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                    for (int part = 0; part < ACC / 16; ++part) {
+                        float v[16];
+                        tc_ld16(taddr + (unsigned)(c + part * 16), v);
+                        if (MODE == 3) {
+                            uint4 pk;
+                            pk.x = ZLM_PK(silu_mul(v[0], v[8]), silu_mul(v[1], v[9]));
+                            pk.y = ZLM_PK(silu_mul(v[2], v[10]), silu_mul(v[3], v[11]));
+                            pk.z = ZLM_PK(silu_mul(v[4], v[12]), silu_mul(v[5], v[13]));
+                            pk.w = ZLM_PK(silu_mul(v[6], v[14]), silu_mul(v[7], v[15]));
+                            *(uint4*)(row + ((part ^ sw) << 4)) = pk;
+                        } else if (MODE == 0) {
+                            uint4 p0, p1;
+                            p0.x = ZLM_PK(v[0], v[1]); p0.y = ZLM_PK(v[2], v[3]); p0.z = ZLM_PK(v[4], v[5]); p0.w = ZLM_PK(v[6], v[7]);
+                            p1.x = ZLM_PK(v[8], v[9]); p1.y = ZLM_PK(v[10], v[11]); p1.z = ZLM_PK(v[12], v[13]); p1.w = ZLM_PK(v[14], v[15]);
+                            *(uint4*)(row + (((2 * part) ^ sw) << 4)) = p0;
+                            *(uint4*)(row + (((2 * part + 1) ^ sw) << 4)) = p1;
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 4; ++j)
+                                *(float4*)(row + ((j ^ sw) << 4)) = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                        }
+                    }
+#undef ZLM_PK
                     asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory");
                     __syncwarp();
                     if (lane == 0) {
-                        asm volatile(
-                            "cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2}], [%3];\n"
-                            ::"l"(&map_y), "r"(b0row + c), "r"(a0row + lg * 32),
-                              "r"(smem_u32(ring + (boxes % TCQ_RING) * TCQ_BOX_BYTES)) : "memory");
+                        const unsigned src = smem_u32(ring + (boxes % TCQ_RING) * TCQ_BOX_BYTES);
+                        if (MODE == 1)
+                            asm volatile(
+                                "cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%1, %2}], [%3];\n"
+                                ::"l"(&map_y), "r"(x), "r"(a0row + lg * 32), "r"(src) : "memory");
+                        else
+                            asm volatile(
+                                "cp.async.bulk.tensor.2d.global.shared::cta.tile.bulk_group [%0, {%1, %2}], [%3];\n"
+                                ::"l"(&map_y), "r"(x), "r"(a0row + lg * 32), "r"(src) : "memory");
                         asm volatile("cp.async.bulk.commit_group;\n" ::: "memory");
                     }
                 }
@@ -713,7 +747,7 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             __syncwarp();
             if (lane == 0) mbar_arrive_at(empty0[buf]);
         }
-        // the boxes handed to the copy engine have been added in before the block leaves
+        // the boxes handed to the copy engine have been written before the block leaves
         if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;\n" ::: "memory");
     }
     tc_fence_before();
@@ -1091,12 +1125,14 @@ static int launch_tc_pair(void* Y, const void* X, const void* W, int T, int N, i
     if (rc) return rc;
     rc = make_map(&mw, W, N, K, K, BN / 2);
     if (rc) return rc;
-    // adding into the fp32 stream goes through the copy engine where its rows can be described
-    // to it (16-byte aligned rows); else the threads add row by row
-    const int y_tma = mode == 1 && ldy % 4 == 0 && (uintptr_t)Y % 16 == 0;
+    // the results go through the copy engine where the output's rows can be described to it
+    // (16-byte aligned rows); else the threads store row by row
+    const int ybytes = (mode == 0 || mode == 3) ? 2 : 4;
+    const int y_tma = mode >= 0 && mode <= 3 && ((size_t)ldy * ybytes) % 16 == 0 && (uintptr_t)Y % 16 == 0 &&
+                      (mode != 3 || N % 2 == 0);
     CUtensorMap my = mx;
     if (y_tma) {
-        rc = zlm_make_map_out(&my, Y, T, N, ldy, 4, 32, 16);
+        rc = zlm_make_map_out(&my, Y, T, mode == 3 ? N / 2 : N, ldy, ybytes, 32, 64 / ybytes);
         if (rc) return rc;
     }
     const size_t smem = (size_t)STAGES * (TC_BM + BN / 2) * TC_BK * 2 + TCQ_OUT_BYTES + 1024 + 256;
