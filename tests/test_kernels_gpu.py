@@ -371,6 +371,14 @@ def test_linear_bf16_tcgen05_many_tokens(K, T, N, K_, form, width):
         acc = base.clone().cuda()
         K.linear(acc, x.cuda(), w.cuda(), accumulate=True, impl="tc")
         close(acc, base.double() + want, torch.float32, atol=1e-3, rtol=1e-3)
+        # the output as columns of a wider tensor: what lies beside them stays as it was (the
+        # epilogue's boxes are clipped at the product's own width, not at the row's)
+        for out_dtype in (torch.bfloat16, torch.float32):
+            wide = torch.full((T, N + 24), 7.0, dtype=out_dtype, device="cuda")
+            K.linear(wide[:, 8:8 + N], x.cuda(), w.cuda(), accumulate=out_dtype == torch.float32, impl="tc")
+            close(wide[:, 8:8 + N], want + (7.0 if out_dtype == torch.float32 else 0.0), out_dtype,
+                  atol=1e-3 if out_dtype == torch.float32 else 3e-2, rtol=1e-2)
+            assert bool((wide[:, :8] == 7.0).all()) and bool((wide[:, 8 + N:] == 7.0).all())
         if N % 16 == 0:
             gate, up = w[:N // 2], w[N // 2:]
             g, u = x.double() @ gate.double().t(), x.double() @ up.double().t()
