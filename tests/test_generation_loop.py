@@ -129,8 +129,12 @@ def test_sampling_params_and_uniforms():
     with pytest.raises(ValueError):
         SamplingParams(temperature=-1)
     with pytest.raises(ValueError):
-        SamplingParams(temperature=1, top_p=0)
+        SamplingParams(temperature=1, top_p=-0.1)
     assert SamplingParams().greedy and not SamplingParams(temperature=0.5).greedy
+    # the reference's edge cases (src/runtime/sampler.zig:85-110): top_k 1 and top_p 0 are greedy
+    # even with a temperature; top_p of 1 or more keeps the whole support
+    assert SamplingParams(temperature=1.5, top_k=1).greedy and SamplingParams(temperature=1, top_p=0).greedy
+    assert SamplingParams(temperature=1, top_p=3.0).top_p == 1.0 and not SamplingParams(temperature=1, top_p=3.0).greedy
     us = [uniform_for(3, r, p) for r in range(20) for p in range(50)]
     assert all(0.0 <= u < 1.0 for u in us) and len(set(us)) > 990
     assert abs(sum(us) / len(us) - 0.5) < 0.03

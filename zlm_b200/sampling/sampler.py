@@ -31,12 +31,17 @@ class SamplingParams:
             raise ValueError(f"temperature must be >= 0, got {self.temperature}")
         if self.top_k < 0:
             raise ValueError(f"top_k must be >= 0 (0 disables it), got {self.top_k}")
-        if not 0.0 < self.top_p <= 1.0 and self.temperature > 0:
-            raise ValueError(f"top_p must be in (0, 1] (1 disables it), got {self.top_p}")
+        if self.top_p < 0 or self.top_p != self.top_p:
+            raise ValueError(f"top_p must be >= 0 (1 or more disables it, 0 keeps the best token only), got {self.top_p}")
+        if self.top_p > 1.0:
+            object.__setattr__(self, "top_p", 1.0)       # "top_p >= 1 disables nucleus filtering"
 
     @property
     def greedy(self) -> bool:
-        return self.temperature <= 0
+        """Whether the choice is the argmax: temperature 0, and also a nucleus of mass 0 or the
+        best one of top_k = 1, which keep the highest logit (the lowest index among equals) whatever
+        the temperature (src/runtime/sampler.zig:85-110)."""
+        return self.temperature <= 0 or self.top_p <= 0 or self.top_k == 1
 
 
 def _splitmix64(x: int) -> int:
