@@ -408,10 +408,12 @@ extern "C" int zlm_attention_prefill_tc_supported(int nq, int nkv, int hd, int q
 static int g_fa_heads = 0;
 
 // Heads of a kv group per block.  Two heads can share a block (they share its keys and values,
-// and one head's softmax runs under the other's products), but the blocks are then half as
-// many and the longest twice as long.  The step takes about as long as the larger of its
-// longest block (the last tile of the longest prompt) and its whole work spread over the SMs;
-// the form for which that is smaller runs.  Odd groups take one.
+// and one head's softmax runs beside the other's: a step of 128 keys takes the two about 4,000
+// cycles against 2,500 for one alone), but the blocks are then half as many and the longest
+// 1.6 times as long.  The step takes about as long as the larger of its longest block (the last
+// tile of the longest prompt) and its whole work spread over the SMs; the form for which that is
+// smaller runs (2,048 tokens, 16 heads over 8: 38 us with one head a block, 46 with two; 32 over
+// 8: 73 and 54).  Odd groups take one.
 extern "C" int zlm_attention_prefill_tc_heads(int R, int max_new, int nq, int nkv) {
     if (nkv <= 0 || nq % nkv != 0 || (nq / nkv) % 2 != 0) return 1;
     if (g_fa_heads) return g_fa_heads;
@@ -422,7 +424,7 @@ extern "C" int zlm_attention_prefill_tc_heads(int R, int max_new, int nq, int nk
             sms = 148;
     }
     const int tiles = (max_new + FA_BM - 1) / FA_BM;
-    const double pairs_cost = 2.0 / 1.46;                                   // a block of two heads, per page, against one head
+    const double pairs_cost = 1.6;                                          // a block of two heads, per step, against one head
     const double work = (double)R * tiles * (tiles + 1) / 2 / sms;          // tiles' pages summed, per SM and head
     const double two = fmax(tiles * pairs_cost, work * (nq / 2) * pairs_cost), one = fmax((double)tiles, work * nq);
     return two <= one ? 2 : 1;
