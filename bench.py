@@ -162,7 +162,8 @@ class Runner:
             return self.eng
         self.drop()
         e = Engine.from_random(self.cfg, seed=0, dtype="bfloat16", device="cuda:0", max_tokens=need[1],
-                               max_batch=batch, max_seq_len=CONTEXT, max_step_tokens=8 * CONTEXT)
+                               max_batch=batch, max_seq_len=CONTEXT,
+                               max_step_tokens=max(8 * CONTEXT, batch * PROMPT_LEN))      # `generate` takes all prompts in one step
         if self.args.pdl or self.args.no_pdl:
             e.decoder.use_pdl = bool(self.args.pdl)
         self.eng, self.shape = e, need
