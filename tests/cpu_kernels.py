@@ -35,7 +35,7 @@ class PlainKernels:
         g, u = gu[:, :I].float(), gu[:, I:].float()
         out.copy_(((g / (1.0 + torch.exp(-g))) * u).to(out.dtype))
 
-    def linear(self, out, x, w, accumulate=False):
+    def linear(self, out, x, w, accumulate=False, defer=False):
         y = x.float() @ w.float().t()
         if accumulate:
             out += y

@@ -488,6 +488,61 @@ def test_linear_bf16_tcgen05_few_tokens(K, T):
     assert K.gemm_tc_status() == 0
 
 
+@pytest.mark.parametrize("T", [17, 40, 64, 100])
+def test_shares_of_a_few_token_product_are_added_up_by_the_kernel_that_reads_it_next(K, T):
+    """A few-token product that cuts K into shares may leave them to the norm (a product into
+    the fp32 stream) or to the norm / rotation / cache write (the q/k/v projection): the same
+    bits as with the product's own second kernel.  Anything else that touches the output gets
+    the product finished first."""
+    H, Kin = 1024, 2048                    # 8 tiles of 128 outputs on 148 SMs: K is cut
+    x, w = rnd((T, Kin), torch.bfloat16, 201).cuda(), rnd((H, Kin), torch.bfloat16, 202, 0.05).cuda()
+    nw = (1 + rnd((H,), torch.float32, 203, 0.1)).cuda()
+    base = rnd((T, H), torch.float32, 204).cuda()
+    # 1. into the stream, then the norm
+    want_x = base.clone()
+    K.linear(want_x, x, w, accumulate=True)
+    want_n = torch.empty((T, H), dtype=torch.bfloat16, device="cuda")
+    K.rmsnorm(want_n, want_x, nw, 1e-6)
+    got_x = base.clone()
+    K.linear(got_x, x, w, accumulate=True, defer=True)
+    assert K._shares is not None, "this product was expected to be cut into shares"
+    got_n = torch.empty_like(want_n)
+    K.rmsnorm(got_n, got_x, nw, 1e-6)
+    assert K._shares is None
+    assert torch.equal(got_n, want_n) and torch.equal(got_x, want_x)
+    # 2. the same, but the next reader is not the whole-stream norm: the product is finished first
+    rows = torch.tensor([T - 1, 0, 3], dtype=torch.int32, device="cuda")
+    got_x = base.clone()
+    K.linear(got_x, x, w, accumulate=True, defer=True)
+    some = torch.empty((3, H), dtype=torch.bfloat16, device="cuda")
+    K.rmsnorm(some, got_x, nw, 1e-6, rows)
+    assert K._shares is None and torch.equal(got_x, want_x) and torch.equal(some, want_n[rows.long()])
+    got_x = base.clone()
+    K.linear(got_x, x, w, accumulate=True, defer=True)
+    K.flush_shares()
+    assert torch.equal(got_x, want_x)
+    # 3. a q/k/v projection, then norm, rotation and cache write
+    nq, nkv, hd = 4, 2, 128
+    lens = [T - 9, 9]
+    pool, table, slots = make_paged(nkv, hd, [n + 70 for n in lens], torch.bfloat16, 205)
+    pos = torch.cat([torch.arange(70, 70 + n) for n in lens]).to(torch.int32).cuda()
+    slot = torch.cat([torch.full((n,), sl) for sl, n in zip(slots, lens)]).to(torch.int32).cuda()
+    wq = rnd(((nq + 2 * nkv) * hd, Kin), torch.bfloat16, 206, 0.05).cuda()
+    qw, kw = (1 + rnd((hd,), torch.float32, 207, 0.1)).cuda(), (1 + rnd((hd,), torch.float32, 208, 0.1)).cuda()
+    inv = torch.pow(torch.tensor(10000.0), -torch.arange(0, hd, 2).float() / hd).cuda()
+    outs = []
+    for defer in (False, True):
+        qkv = torch.empty((T, (nq + 2 * nkv) * hd), dtype=torch.bfloat16, device="cuda")
+        p = pool.clone().cuda()
+        K.linear(qkv, x, wq, defer=defer)
+        assert (K._shares is not None) == defer
+        K.qk_norm_rope_write(qkv, qw, kw, 1e-6, inv, hd, pos, slot, table.cuda(), p, nq, nkv, hd)
+        assert K._shares is None
+        outs.append((qkv[:, : nq * hd].clone(), p))
+    assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+    assert K.status(sync=True) == 0
+
+
 @pytest.mark.parametrize("T,nq,nkv,hd,Kin,norm,rope,width", [
     (500, 4, 2, 128, 256, True, True, 0), (700, 6, 3, 64, 192, True, True, 0), (390, 8, 0, 128, 128, True, True, 0),
     (450, 3, 1, 32, 96, False, True, 0), (600, 4, 4, 128, 320, True, False, 0), (1100, 5, 1, 128, 512, True, True, 128),

@@ -84,6 +84,44 @@ __global__ void rmsnorm_kernel(TO* __restrict__ out, const float* __restrict__ x
                        GroupSync{0, (int)blockDim.x}, blockDim.x);
 }
 
+// The same for a stream whose last product still lies in shares (fp32 [ks][R][H], the cut of K that
+// a few-token product leaves): the row's block adds them in first, x[r] += (s0 + s1 + ...) as the
+// product's own second kernel would, writes the row back, and norms it: one kernel instead of two.
+template <typename TO>
+__global__ void rmsnorm_shares_kernel(TO* __restrict__ out, float* __restrict__ x, VecW w,
+                                      const float* __restrict__ shares, int ks, size_t share_elems, int H, float eps) {
+    __shared__ float red[32];
+    pdl_trigger();
+    const int r = blockIdx.x;
+    pdl_wait();
+    float* xr = x + (size_t)r * H;
+    const float* sr = shares + (size_t)r * H;
+    if (!ZLM_CHK(xr, (size_t)H * 4) || !ZLM_CHK(out + (size_t)r * H, (size_t)H * sizeof(TO)) ||
+        !ZLM_CHK(w.p, (size_t)H * (w.dtype == ZLM_DTYPE_F32 ? 4 : 2)) || !ZLM_CHK(sr, (size_t)H * 4) ||
+        !ZLM_CHK(sr + (size_t)(ks - 1) * share_elems, (size_t)H * 4))
+        return;
+    if (H % 4 == 0) {
+        for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
+            float4 sum = make_float4(0.f, 0.f, 0.f, 0.f);
+            for (int s = 0; s < ks; ++s) {
+                const float4 p = *(const float4*)(sr + (size_t)s * share_elems + i);
+                sum.x += p.x; sum.y += p.y; sum.z += p.z; sum.w += p.w;
+            }
+            float4 a = *(const float4*)(xr + i);
+            a.x += sum.x; a.y += sum.y; a.z += sum.z; a.w += sum.w;
+            *(float4*)(xr + i) = a;
+        }
+    } else {
+        for (int i = threadIdx.x; i < H; i += blockDim.x) {
+            float sum = 0.f;
+            for (int s = 0; s < ks; ++s) sum += sr[(size_t)s * share_elems + i];
+            xr[i] += sum;
+        }
+    }
+    __syncthreads();          // the row as the block has just written it
+    rmsnorm_row<TO, 1>(out + (size_t)r * H, xr, w, H, eps, red, threadIdx.x, GroupSync{0, (int)blockDim.x}, blockDim.x);
+}
+
 // Many rows, bf16 output: a block of 256 threads walks rows r, r + gridDim.x, ... and has the
 // next row's loads in flight while it reduces and stores the current one.  (One block per row,
 // all blocks of a wave starting together, loads and then reduces in step across the whole GPU:
@@ -188,6 +226,24 @@ extern "C" int zlm_rmsnorm(void* out, int out_dtype, const float* x, const void*
     else
         ZLM_REQUIRE(false, "rmsnorm: unsupported output dtype %d", out_dtype);
     return zlm_check_launch("rmsnorm");
+}
+
+extern "C" int zlm_rmsnorm_shares(void* out, int out_dtype, float* x, const void* w, int w_dtype, int R, int H, float eps,
+                                  const float* shares, int ks, cudaStream_t st) {
+    if (R == 0) return ZLM_OK;
+    ZLM_REQUIRE(R > 0 && H > 0 && ks > 1 && shares, "rmsnorm_shares: bad sizes R=%d H=%d shares=%d", R, H, ks);
+    VecW vw{w, w_dtype};
+    // the same block as zlm_rmsnorm takes for a short step, so that the row's sum has the same order
+    int threads = 128;
+    while (threads < 1024 && threads * 4 < H) threads *= 2;
+    const size_t share_elems = (size_t)R * H;
+    if (out_dtype == ZLM_DTYPE_F32)
+        zlm_launch(rmsnorm_shares_kernel<float>, R, threads, 0, st, (float*)out, x, vw, shares, ks, share_elems, H, eps);
+    else if (out_dtype == ZLM_DTYPE_BF16)
+        zlm_launch(rmsnorm_shares_kernel<__nv_bfloat16>, R, threads, 0, st, (__nv_bfloat16*)out, x, vw, shares, ks, share_elems, H, eps);
+    else
+        ZLM_REQUIRE(false, "rmsnorm_shares: unsupported output dtype %d", out_dtype);
+    return zlm_check_launch("rmsnorm_shares");
 }
 
 // ---------------------------------------------------------------- swiglu

@@ -1037,7 +1037,7 @@ static int make_map(CUtensorMap* m, const void* ptr, int rows, int K, int ld, in
 
 template <int BN, int STAGES>
 static int launch_tc(void* Y, const void* X, const void* W, int T, int N, int K, int ldx, int ldy, int mode,
-                     int ksplit, float* scratch, cudaStream_t st) {
+                     int ksplit, float* scratch, cudaStream_t st, bool add_shares = true) {
     CUtensorMap mx, mw;
     int rc = make_map(&mx, X, T, K, ldx, BN);
     if (rc) return rc;
@@ -1069,7 +1069,7 @@ static int launch_tc(void* Y, const void* X, const void* W, int T, int N, int K,
     else ZLM_TC_LAUNCH(4)
 #undef ZLM_TC_LAUNCH
     rc = zlm_check_launch("gemm_tc");
-    if (rc || ksplit <= 1) return rc;
+    if (rc || ksplit <= 1 || !add_shares) return rc;
     return launch_reduce(Y, scratch, T, N, ldy, mode, ksplit, 0, st);
 }
 
@@ -1303,6 +1303,34 @@ extern "C" int zlm_gemm_tc(void* Y, const void* X, const void* W, int T, int N, 
     if (width == 240) return launch_tc_persistent<240, 4>(Y, X, W, T, N, K, ldx, ldy, mode, st);
     if (width == 224) return launch_tc_persistent<224, 4>(Y, X, W, T, N, K, ldx, ldy, mode, st);
     return launch_tc_persistent<256, 4>(Y, X, W, T, N, K, ldx, ldy, mode, st);
+}
+
+// A few-token product that runs as one round of stand-alone blocks cuts K into shares and leaves
+// them as fp32 [shares][T][N] in scratch; a second kernel adds them up.  Where the kernel that
+// reads the product next can do that on its way (the norm that follows a product into the fp32
+// stream, the norm / rotation / cache write that follows the q/k/v projection), the caller asks
+// for the shares alone: zlm_gemm_tc_shares_plan tells how many there would be (0: this product is
+// not of that form), zlm_gemm_tc_shares leaves them, zlm_gemm_tc_add_shares is the second kernel
+// for a caller that has to finish the product after all.
+extern "C" int zlm_gemm_tc_shares_plan(int T, int N, int K, int ldx) {
+    if (T <= 16 || T > 384 || !zlm_gemm_tc_supported(T, N, K, ldx)) return 0;
+    const FewPlan plan = few_plan(T, N, K);
+    const long long tiles = (long long)((N + TC_BM - 1) / TC_BM) * plan.t_tiles;
+    if (plan.ks <= 1 || plan.whole != 0 || tiles * plan.ks > sm_count()) return 0;
+    return plan.ks;
+}
+extern "C" int zlm_gemm_tc_shares(const void* X, const void* W, int T, int N, int K, int ldx, float* scratch,
+                                  cudaStream_t st) {
+    const int ks = zlm_gemm_tc_shares_plan(T, N, K, ldx);
+    ZLM_REQUIRE(ks > 1 && scratch, "gemm_tc_shares: the product T=%d N=%d K=%d is not cut into shares", T, N, K);
+    ZLM_REQUIRE(((uintptr_t)X % 16 == 0) && ((uintptr_t)W % 16 == 0), "gemm_tc: operands must be 16-byte aligned");
+    if (T <= 32) return launch_tc<32, 8>(nullptr, X, W, T, N, K, ldx, N, 0, ks, scratch, st, false);
+    if (T <= 64) return launch_tc<64, 8>(nullptr, X, W, T, N, K, ldx, N, 0, ks, scratch, st, false);
+    return launch_tc<128, 6>(nullptr, X, W, T, N, K, ldx, N, 0, ks, scratch, st, false);
+}
+extern "C" int zlm_gemm_tc_add_shares(void* Y, const float* scratch, int T, int N, int ldy, int mode, int ks, cudaStream_t st) {
+    ZLM_REQUIRE(ks > 1 && scratch && mode >= 0 && mode <= 2, "gemm_tc_add_shares: %d shares, mode %d", ks, mode);
+    return launch_reduce(Y, scratch, T, N, ldy, mode, ks, 0, st);
 }
 
 // 1 if the q/k/v projection of T tokens can carry norm, rotation and cache write in its epilogue:

@@ -144,9 +144,11 @@ class Engine:
         """The device work of one step: every schedule entry over the step's tokens,
         then logits at the ``wanted`` first rows of the uploaded ``want_rows``."""
         hidden = self.model.forward(ctx, self.cache.ios)
-        if not wanted:
-            return None
-        return self.model.logits(hidden, self.stager.view("want_rows", wanted), wanted)
+        logits = self.model.logits(hidden, self.stager.view("want_rows", wanted), wanted) if wanted else None
+        flush = getattr(self.rt.k, "flush_shares", None)
+        if flush is not None:
+            flush()             # a product that a part left for a kernel which then never came
+        return logits
 
     # ---- sampling and generation -------------------------------------------------
     def prefill_sample(self, slots: Sequence[int], prompts: Sequence[Sequence[int]], params,

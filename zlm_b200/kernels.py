@@ -116,6 +116,8 @@ class CudaKernels:
         self.decode_blocks: Optional[int] = None
         self.sm_count = int(torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count)
         self._fn = {}
+        self._shares = None            # (output, scratch, shares, accumulate) of a product left in shares of K (see linear)
+        self.defer_shares = True       # whether linear(defer=True) may leave a product so
         self._candidates = None        # (address of the last logits a few-token product wrote, rows, width, blocks, values, indices)
         self._scratch = {}
         self.scratch_generation = 0
@@ -157,6 +159,13 @@ class CudaKernels:
         spans are also noted as memory the next call may touch."""
         if t is None:
             return c_void_p(0)
+        if self._shares is not None:
+            # a product whose shares of K are not added up yet: whoever touches its output gets it finished first
+            lo, n = self._shares[0].data_ptr(), _span_bytes(self._shares[0])
+            if t.data_ptr() < lo + n and lo < t.data_ptr() + _span_bytes(t):
+                noted, self._ranges = self._ranges, []      # (this happens while a call's arguments are gathered)
+                self.flush_shares()
+                self._ranges = noted
         if self.bounds_check:
             self._ranges.append((t.data_ptr(), _span_bytes(t)))
         return c_void_p(t.data_ptr())
@@ -233,6 +242,11 @@ class CudaKernels:
         assert x.dtype == torch.float32 and x.shape[1] == H and w.shape == (H,)
         assert out.is_contiguous() and x.is_contiguous() and w.is_contiguous()
         assert rows is None or (rows.dtype == torch.int32 and rows.numel() >= R)
+        taken = self._takes_shares(x, ACCUM) if (rows is None and x.shape[0] == R) else None
+        if taken is not None:
+            self._call("zlm_rmsnorm_shares", self._p(out), c_int(_dt(out)), self._p(x), self._p(w), c_int(_dt(w)),
+                       c_int(R), c_int(H), c_float(eps), self._p(taken[0]), c_int(taken[1]), self._stream())
+            return
         self._call("zlm_rmsnorm", self._p(out), c_int(_dt(out)), self._p(x),
                    self._p(w), c_int(_dt(w)), self._p(rows), c_int(R), c_int(H),
                    c_float(eps), self._stream())
@@ -246,12 +260,18 @@ class CudaKernels:
                    c_int(T), c_int(I), self._stream())
 
     def linear(self, out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, accumulate: bool = False,
-               impl: Optional[str] = None) -> None:
+               impl: Optional[str] = None, defer: bool = False) -> None:
         """out = x @ w.T (out in x's dtype, or fp32), or out += x @ w.T into the fp32
         residual stream when ``accumulate``.  w is [N, K] row-major.  bf16 products pick
         their kernel by the number of tokens: "gemv" (register-fragment streaming, up to
         8), "tc" (TMA + tcgen05, from 9 on), "mma" (mma.sync, what the others do not take);
-        ``impl`` forces one (tests)."""
+        ``impl`` forces one (tests).
+
+        ``defer``: the caller expects ``rmsnorm`` (for a product into the stream) or
+        ``qk_norm_rope_write`` (for a q/k/v projection) to read ``out`` next.  A few-token product
+        that cuts K into shares may then leave them to that kernel, which adds them up on its way
+        (two launches fewer per layer at 17 to 64 tokens); any other use of ``out`` through this
+        class finishes the product first, so the hint is never wrong, only sometimes useless."""
         T, K = x.shape
         N = w.shape[0]
         if self._candidates is not None and self._candidates[0] == out.data_ptr():
@@ -272,7 +292,37 @@ class CudaKernels:
         mode = ACCUM if accumulate else (STORE_F32 if out.dtype == torch.float32 else STORE)
         if mode == STORE:
             assert out.dtype == torch.bfloat16
+        if (defer and self.defer_shares and impl is None and mode in (ACCUM, STORE) and T > 16 and out.is_contiguous()
+                and not self.streams_weights(T, N)):
+            ks = int(self.lib.zlm_gemm_tc_shares_plan(c_int(T), c_int(N), c_int(K), c_int(ldx)))
+            if ks > 1:
+                self.flush_shares()
+                scratch = self.scratch("gemm_tc.partials", ks * T * N, torch.float32, out.device)
+                self._call("zlm_gemm_tc_shares", self._p(x), self._p(w), c_int(T), c_int(N), c_int(K), c_int(ldx),
+                           self._p(scratch), self._stream())
+                self._shares = (out, scratch, ks, mode)
+                return
         self._bf16_product(out, x, w, T, N, K, ldx, ldy, mode, impl)
+
+    def flush_shares(self) -> None:
+        """Finishes a product that ``linear(defer=True)`` left in shares of K (its second kernel)."""
+        if self._shares is None:
+            return
+        out, scratch, ks, mode = self._shares
+        self._shares = None
+        T, N = out.shape
+        self._call("zlm_gemm_tc_add_shares", self._p(out), self._p(scratch), c_int(T), c_int(N), c_int(out.stride(0)),
+                   c_int(mode), c_int(ks), self._stream())
+
+    def _takes_shares(self, t: torch.Tensor, mode: int):
+        """The pending shares if they are those of ``t`` (whole, in this mode), else None after finishing them."""
+        if self._shares is None:
+            return None
+        out, scratch, ks, m = self._shares
+        if out.data_ptr() == t.data_ptr() and tuple(out.shape) == tuple(t.shape) and out.stride() == t.stride() and m == mode:
+            self._shares = None
+            return scratch, ks
+        return None
 
     # outputs from which a product counts as "as wide as a vocabulary" (see streams_weights)
     WIDE_PRODUCT = 65536
@@ -292,6 +342,7 @@ class CudaKernels:
             small = self.streams_weights(T, N)
             impl = "gemv" if (small or (T <= 16 and not tc_ok)) else ("tc" if tc_ok else "mma")
         if impl == "tc":
+            self.flush_shares()             # the shares' scratch is about to be written again
             ks = self.lib.zlm_gemm_tc_ksplit(T, N, K)
             scratch = self.scratch("gemm_tc.partials", ks * T * N, torch.float32, out.device) if ks > 1 else None
             self._call("zlm_gemm_tc", self._p(out), self._p(x), self._p(w),
@@ -405,13 +456,17 @@ class CudaKernels:
             assert pool is not None and pool.dtype == qkv.dtype and pool.is_contiguous()
             assert tuple(pool.shape[1:]) == (2, nkv, PAGE_TOKENS, hd)
             assert block_table is not None and block_table.dtype == torch.int32
-        self._call("zlm_qk_norm_rope_write", self._p(qkv), c_int(_dt(qkv)), c_int(qkv.stride(0)),
-                   self._p(q_w), self._p(k_w), c_int(_dt(q_w) if has_norm else F32),
-                   c_int(1 if has_norm else 0), c_float(eps), self._p(inv_freq), c_int(n_rot),
-                   self._p(token_pos), self._p(token_slot),
-                   self._p(block_table), c_int(block_table.stride(0) if block_table is not None else 0),
-                   self._p(pool), c_int(nq), c_int(nkv), c_int(hd), c_int(1 if write else 0), c_int(T),
-                   self._stream())
+        taken = self._takes_shares(qkv, STORE) if T < 512 else None
+        args = (self._p(qkv), c_int(_dt(qkv)), c_int(qkv.stride(0)),
+                self._p(q_w), self._p(k_w), c_int(_dt(q_w) if has_norm else F32),
+                c_int(1 if has_norm else 0), c_float(eps), self._p(inv_freq), c_int(n_rot),
+                self._p(token_pos), self._p(token_slot),
+                self._p(block_table), c_int(block_table.stride(0) if block_table is not None else 0),
+                self._p(pool), c_int(nq), c_int(nkv), c_int(hd), c_int(1 if write else 0), c_int(T))
+        if taken is not None:
+            self._call("zlm_qk_norm_rope_write_shares", *args, self._p(taken[0]), c_int(taken[1]), self._stream())
+        else:
+            self._call("zlm_qk_norm_rope_write", *args, self._stream())
 
     def attention(self, out: torch.Tensor, q: torch.Tensor, pool: torch.Tensor, block_table: torch.Tensor,
                   token_pos: torch.Tensor, token_slot: torch.Tensor, nq: int, nkv: int, hd: int,

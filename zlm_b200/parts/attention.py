@@ -114,11 +114,12 @@ class GQAAttention(Mixer):
             return
         if writes:
             qkv = rt.ws.get("attn.qkv", (T, self.Q + 2 * self.KV), rt.dtype)
-            k.linear(qkv, x, self.w_qkv)
+            # (the norm / rotation / cache write kernel reads the projection next, where there is one)
+            k.linear(qkv, x, self.w_qkv, defer=fused_pos or self.qk_norm)
             nkv = self.nkv
         else:
             qkv = rt.ws.get("attn.qkv", (T, self.Q), rt.dtype)
-            k.linear(qkv, x, self.w_q)
+            k.linear(qkv, x, self.w_q, defer=fused_pos or self.qk_norm)
             nkv = 0
         q = qkv[:, : self.Q]
         if fused_pos:
@@ -144,4 +145,4 @@ class GQAAttention(Mixer):
         k.attention(out, q, cache.pool, cache.block_table, ctx.token_pos, ctx.token_slot,
                     self.nq, self.nkv, self.hd, self.scale, self.window, ctx,
                     len_bucket=key[1] if key else None)
-        k.linear(residual, out, self.w_o, accumulate=True)
+        k.linear(residual, out, self.w_o, accumulate=True, defer=True)       # a norm reads the stream next

@@ -58,4 +58,4 @@ class SwiGLU(FeedForward):
             gu = rt.ws.get("ffn.gu", (T, 2 * self.inter), rt.dtype)
             k.linear(gu, x, self.w_gu)
             k.swiglu(act, gu)
-        k.linear(residual, act, self.w_down, accumulate=True)
+        k.linear(residual, act, self.w_down, accumulate=True, defer=True)      # a norm reads the stream next

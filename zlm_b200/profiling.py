@@ -148,12 +148,13 @@ class ProfilingKernels:
     def _linear_name(self, w, kind: str) -> str:
         return f"{kind} {self.weight_names.get(w.data_ptr(), f'[{w.shape[0]}x{w.shape[1]}]')}"
 
-    def linear(self, out, x, w, accumulate=False, impl=None):
+    def linear(self, out, x, w, accumulate=False, impl=None, defer=False):
         T, K = x.shape
         N = w.shape[0]
         n = _nbytes(w) + T * K * x.element_size() + T * N * out.element_size() * (2 if accumulate else 1)
+        # graph mode times every operation by itself, so a product is finished where it is issued
         return self._timed(self._linear_name(w, "linear"), n, 2.0 * T * N * K, self.k.linear, out, x, w,
-                           accumulate=accumulate, impl=impl)
+                           accumulate=accumulate, impl=impl, defer=defer and self.mode != "graph")
 
     def linear_swiglu(self, out, x, w, impl=None):
         T, K = x.shape
