@@ -183,6 +183,15 @@ class Part:
                 out[name] = t
         return out
 
+    def finish_products(self) -> None:
+        """Has a product finished that a part left in shares of K for the kernel it expected next
+        (``kernels.linear(..., defer=True)``).  Kernels called through the runtime's kernel object
+        see to this themselves; code that reads such a product's output in any other way (torch
+        operations on the stream, a kernel library of its own) calls this first."""
+        finish = getattr(self.rt.k, "flush_shares", None)
+        if finish is not None:
+            finish()
+
     # a part whose forward launches only kernels (no host-side branching on
     # device data, no allocation) may be captured in a CUDA graph
     graph_safe = True
@@ -197,6 +206,12 @@ class Part:
 
 
 class Norm(Part):
+    # Whether this norm reads the stream through ``kernels.rmsnorm`` alone.  A part before it may have
+    # left its last product into the stream in shares of K for that kernel to add up
+    # (``linear(..., defer=True)``); before a norm that reads the stream in any other way the
+    # arrangement has that product finished (``finish_products``).
+    reads_stream_by_kernel = False
+
     def forward(self, out: torch.Tensor, x: torch.Tensor, rows: Optional[torch.Tensor] = None) -> None:
         raise NotImplementedError
 

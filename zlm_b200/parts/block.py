@@ -37,7 +37,11 @@ class PreNormBlock(Part):
     def forward(self, hidden: torch.Tensor, ctx: StepContext, io: LayerIO) -> None:
         rt = self.rt
         x = rt.ws.get("block.normed", hidden.shape, rt.dtype)
+        if not self.mixer_norm.reads_stream_by_kernel:
+            self.finish_products()
         self.mixer_norm.forward(x, hidden)
         self.mixer.forward(x, hidden, ctx, io)
+        if not self.ffn_norm.reads_stream_by_kernel:
+            self.finish_products()
         self.ffn_norm.forward(x, hidden)
         self.ffn.forward(x, hidden, ctx)

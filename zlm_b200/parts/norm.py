@@ -15,6 +15,8 @@ from .base import Norm, ParamSpec
 
 @register_norm("rms_norm")
 class RMSNorm(Norm):
+    reads_stream_by_kernel = True
+
     def __init__(self, size: int, eps: float):
         self.size = int(size)
         self.eps = float(eps)
