@@ -499,3 +499,91 @@ def test_toy_mixer_with_a_cache_record_of_its_own_and_a_step_key():
     key = eng.model.step_key(make_context(eng.stager, arrays, T_, R_, eng.rt.ws))
     assert ("toy_latent", 0) in key and any(k[0] == "gqa_attention" for k in key)
     eng.release(s)
+
+
+def test_a_norm_that_reads_the_stream_by_itself_sees_finished_products():
+    """At layer widths where a few-token product is cut into shares of K, the parts leave their
+    last product into the stream to the norm kernel that follows.  A norm defined here, which
+    reads the stream with torch operations, is not that kernel: the arrangement has the product
+    finished before it, so a model with this norm gives what the same model gives with the
+    library's norm (the same weights by name), and the shares are in fact pending in between.
+    (A toy: it is no model of anyone's.)"""
+    from zlm_b200 import Engine, StepEntry
+    from zlm_b200.config import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
+    from zlm_b200.parts.base import Norm, ParamSpec
+    from zlm_b200.parts.model import DecoderModel
+    from zlm_b200.registry import ARCHITECTURES, NORMS, register_architecture, register_norm
+    from zlm_b200.weights import random_tensors
+
+    seen = {"pending": 0}
+    if "toy_torch_rms" not in NORMS:
+        @register_norm("toy_torch_rms")
+        class TorchRms(Norm):
+            graph_safe = False
+
+            def __init__(self, size, eps):
+                self.size, self.eps = size, eps
+
+            def param_specs(self):
+                return {"weight": ParamSpec((self.size,), kind="vector", init="one_plus_normal")}
+
+            def bind(self, params):
+                self.weight = params["weight"]
+
+            def forward(self, out, x, rows=None):
+                assert getattr(self.rt.k, "_shares", None) is None, "a product was still in shares when this norm read the stream"
+                src = x if rows is None else x[rows.long()[: out.shape[0]]]
+                y = src * torch.rsqrt(src.pow(2).mean(-1, keepdim=True) + self.eps) * self.weight.float()
+                out.copy_(y.to(out.dtype))
+
+    def spec(kind):
+        norm = lambda p: PartSpec(kind, {"eps": 1e-6}, prefix=p)
+        att = lambda p: PartSpec("gqa_attention", {
+            "num_heads": 8, "num_kv_heads": 2, "head_dim": 128, "qk_norm": True,
+            "position": {"kind": "rope_half_split", "theta": 10000.0, "head_dim": 128, "n_rot": 128}}, prefix=p)
+        layers = tuple(LayerSpec("pre_norm", att(f"l{i}.att."), PartSpec("swiglu", {"intermediate_size": 2048}, prefix=f"l{i}.ffn."),
+                                 norm(f"l{i}.n1."), norm(f"l{i}.n2.")) for i in range(2))
+        return ModelSpec("ToyWide", 1024, 300, 512, layers, (ScheduleEntry(0), ScheduleEntry(1)),
+                         PartSpec("token_embedding", {}, prefix="emb."), norm("out_norm."),
+                         PartSpec("lm_head", {"tied": False}, prefix="head."))
+
+    for name, kind in (("ToyWideTorchNormForCausalLM", "toy_torch_rms"), ("ToyWideForCausalLM", "rms_norm")):
+        if name not in ARCHITECTURES:
+            @register_architecture(name)
+            @dataclass(frozen=True)
+            class Cfg:
+                eos_token_ids: tuple = ()
+                _kind = kind
+                _name = name
+
+                @classmethod
+                def from_dict(cls, d):
+                    return cls()
+
+                def to_dict(self):
+                    return {"architectures": [self._name]}
+
+                def to_model_spec(self):
+                    return spec(self._kind)
+
+    t = random_tensors(DecoderModel(spec("rms_norm")).param_specs(), 11)
+    weights = {n: v.to(torch.bfloat16).cuda() if v.dim() > 1 else v.cuda() for n, v in t.items()}
+    ids = torch.randint(0, 300, (40,), generator=torch.Generator().manual_seed(12)).tolist()
+    logits = {}
+    for name in ("ToyWideForCausalLM", "ToyWideTorchNormForCausalLM"):
+        eng = Engine(ARCHITECTURES[name](), dict(weights), torch.bfloat16, "cuda:0", max_tokens=512, max_batch=2)
+        k = eng.rt.k
+        if name == "ToyWideForCausalLM":
+            # the hint is taken at this width: watch one product being left in shares
+            inner = k.rmsnorm
+            def watched(out, x, w, eps, rows=None, _inner=inner, _k=k):
+                seen["pending"] += _k._shares is not None
+                return _inner(out, x, w, eps, rows)
+            k.rmsnorm = watched
+        sl = eng.new_sequence()
+        logits[name] = eng.step([StepEntry(sl, ids, list(range(40)))]).float().cpu()
+        eng.check(sync=True)
+    assert seen["pending"] > 0, "no product was left in shares: this test would prove nothing"
+    a, b = logits["ToyWideForCausalLM"], logits["ToyWideTorchNormForCausalLM"]
+    assert float((a - b).norm() / a.norm()) < 2e-2
+    assert (a.argmax(-1) == b.argmax(-1)).float().mean() > 0.9

@@ -131,7 +131,7 @@ class DecoderModel:
         rt = self.rt
         x = rt.ws.get("model.head_in", (n_rows, self.spec.hidden_size), rt.dtype)
         if not self.final_norm.reads_stream_by_kernel:
-            self.finish_products()
+            self.final_norm.finish_products()
         self.final_norm.forward(x, hidden, rows)
         if out is None:
             out = rt.ws.get("model.logits", (n_rows, self.spec.vocab_size), torch.float32)
