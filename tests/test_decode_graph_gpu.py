@@ -16,6 +16,13 @@ from helpers import SHARP, assert_close, make_model, plain_logits, random_prompt
 
 pytestmark = pytest.mark.gpu
 
+
+@pytest.fixture(autouse=True)
+def _graphs_only(request):
+    if request.config.getoption("--zlm-bounds-check"):
+        pytest.skip("the bounds-check build runs without CUDA graphs")
+
+
 DTYPES = ["float32", "bfloat16"]
 NAMES = ["A", "B", "C"]
 

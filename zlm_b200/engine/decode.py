@@ -39,7 +39,9 @@ class DecodeRunner:
         # its weights and cache at once instead of when the cycle collector next runs
         self._engine = weakref.ref(engine)
         cuda = engine.device.type == "cuda"
-        self.use_graphs = (cuda and engine.model.graph_safe) if use_graphs is None else use_graphs
+        # (the bounds-check build reads its findings back after every call, which a capture does not allow)
+        checked = bool(getattr(engine.rt.k, "bounds_check", False))
+        self.use_graphs = (cuda and engine.model.graph_safe and not checked) if use_graphs is None else use_graphs
         # Programmatic dependent launch between the step's kernels (a kernel's blocks may be
         # scheduled while the kernel before it drains; each waits before it reads what that one
         # wrote): None = for steps of up to 16 rows.  Measured against plain stream order:
