@@ -587,3 +587,104 @@ def test_a_norm_that_reads_the_stream_by_itself_sees_finished_products():
     a, b = logits["ToyWideForCausalLM"], logits["ToyWideTorchNormForCausalLM"]
     assert float((a - b).norm() / a.norm()) < 2e-2
     assert (a.argmax(-1) == b.argmax(-1)).float().mean() > 0.9
+
+
+def test_toy_block_arrangement_in_one_layer_of_two():
+    """Another way of putting a mixer and a feed-forward on the stream, defined here: both read
+    the same normed input and add into the stream side by side (h += mixer(n(h)) + ffn(n(h))).
+    It sits in the first layer of a model whose second layer keeps the pre-norm arrangement;
+    the framework's files do not change.  (A toy: it is no model of anyone's.)"""
+    from zlm_b200 import Engine, StepEntry
+    from zlm_b200.config import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
+    from zlm_b200.parts.base import Part
+    from zlm_b200.parts.model import DecoderModel
+    from zlm_b200.registry import ARCHITECTURES, ARRANGEMENTS, register_architecture, register_arrangement
+    from zlm_b200.weights import random_tensors
+
+    if "toy_side_by_side" not in ARRANGEMENTS:
+        @register_arrangement("toy_side_by_side")
+        class SideBySide(Part):
+            def __init__(self, hidden_size, mixer, feed_forward, mixer_norm, feed_forward_norm):
+                self.mixer, self.ffn, self.norm, self.unused_norm = mixer, feed_forward, mixer_norm, feed_forward_norm
+
+            def children(self):
+                return {"mixer": self.mixer, "feed_forward": self.ffn, "mixer_norm": self.norm,
+                        "feed_forward_norm": self.unused_norm}
+
+            @property
+            def graph_safe(self):
+                return all(c.graph_safe for c in self.children().values())
+
+            def step_key(self, ctx):
+                return tuple(k for k in (c.step_key(ctx) for c in self.children().values()) if k is not None) or None
+
+            def forward(self, hidden, ctx, io):
+                x = self.rt.ws.get("toy.normed", hidden.shape, self.rt.dtype)
+                self.norm.forward(x, hidden)
+                self.mixer.forward(x, hidden, ctx, io)
+                self.ffn.forward(x, hidden, ctx)          # the same normed input, the stream already holds the mixer's part
+
+    if "ToySideBySideForCausalLM" not in ARCHITECTURES:
+        @register_architecture("ToySideBySideForCausalLM")
+        @dataclass(frozen=True)
+        class ToySideBySideConfig:
+            eos_token_ids: tuple = ()
+
+            @classmethod
+            def from_dict(cls, d):
+                return cls()
+
+            def to_dict(self):
+                return {"architectures": ["ToySideBySideForCausalLM"]}
+
+            def to_model_spec(self):
+                norm = lambda p: PartSpec("rms_norm", {"eps": 1e-5}, prefix=p)
+                att = lambda p: PartSpec("gqa_attention", {
+                    "num_heads": 3, "num_kv_heads": 1, "head_dim": 16, "qk_norm": True,
+                    "position": {"kind": "rope_half_split", "theta": 1000.0, "head_dim": 16, "n_rot": 16}}, prefix=p)
+                ffn = lambda p: PartSpec("swiglu", {"intermediate_size": 56}, prefix=p)
+                l0 = LayerSpec("toy_side_by_side", att("l0.att."), ffn("l0.ffn."), norm("l0.n1."), norm("l0.n2."))
+                l1 = LayerSpec("pre_norm", att("l1.att."), ffn("l1.ffn."), norm("l1.n1."), norm("l1.n2."))
+                return ModelSpec("ToySideBySideForCausalLM", 40, 77, 256, (l0, l1), (ScheduleEntry(0), ScheduleEntry(1)),
+                                 PartSpec("token_embedding", {}, prefix="emb."), norm("out_norm."),
+                                 PartSpec("lm_head", {"tied": False}, prefix="head."))
+
+    cfg = ARCHITECTURES["ToySideBySideForCausalLM"]()
+    t = random_tensors(DecoderModel(cfg.to_model_spec()).param_specs(), 21)
+    eng = Engine(cfg, {n: v.cuda() for n, v in t.items()}, torch.float32, "cuda:0", max_tokens=512, max_batch=4)
+
+    def attention(x, l, T):
+        pos = torch.arange(T)
+        q = P.head_rms_norm(P.linear(x, t[f"{l}.att.q_proj.weight"]).reshape(T, 3, 16), t[f"{l}.att.q_norm.weight"], 1e-6)
+        k = P.head_rms_norm(P.linear(x, t[f"{l}.att.k_proj.weight"]).reshape(T, 1, 16), t[f"{l}.att.k_norm.weight"], 1e-6)
+        v = P.linear(x, t[f"{l}.att.v_proj.weight"]).reshape(T, 1, 16)
+        q, k = P.rope_half_split(q, pos, 1000.0, 16), P.rope_half_split(k, pos, 1000.0, 16)
+        return P.linear(P.causal_attention(q, k, v).reshape(T, 48), t[f"{l}.att.o_proj.weight"])
+
+    def mlp(x, l):
+        return P.linear(P.swiglu(P.linear(x, t[f"{l}.ffn.gate_proj.weight"]), P.linear(x, t[f"{l}.ffn.up_proj.weight"])),
+                        t[f"{l}.ffn.down_proj.weight"])
+
+    def reference(ids):
+        T = len(ids)
+        h = P.embed(t["emb.weight"], ids)
+        x = P.rms_norm(h, t["l0.n1.weight"], 1e-5)
+        h = h + attention(x, "l0", T) + mlp(x, "l0")                       # side by side
+        h = h + attention(P.rms_norm(h, t["l1.n1.weight"], 1e-5), "l1", T)   # then the usual order
+        h = h + mlp(P.rms_norm(h, t["l1.n2.weight"], 1e-5), "l1")
+        return P.linear(P.rms_norm(h, t["out_norm.weight"], 1e-5), t["head.weight"])
+
+    g = torch.Generator().manual_seed(22)
+    seqs = [torch.randint(0, 77, (n,), generator=g).tolist() for n in (30, 11)]
+    slots = [eng.new_sequence() for _ in seqs]
+    got = eng.step([StepEntry(sl, s[:9], list(range(9))) for sl, s in zip(slots, seqs)]).cpu()
+    want = [reference(s) for s in seqs]
+    torch.testing.assert_close(got[:9], want[0][:9], atol=2e-5, rtol=1e-4)
+    torch.testing.assert_close(got[9:], want[1][:9], atol=2e-5, rtol=1e-4)
+    for i in range(9, 11):                                     # then token by token, from the cache
+        got = eng.step([StepEntry(sl, [s[i]], [0]) for sl, s in zip(slots, seqs)]).cpu()
+        torch.testing.assert_close(got[0], want[0][i], atol=2e-5, rtol=1e-4)
+        torch.testing.assert_close(got[1], want[1][i], atol=2e-5, rtol=1e-4)
+    # and through the generation loop (graphs where the parts allow them)
+    out = eng.generate([s[:5] for s in seqs], max_tokens=4)
+    assert [len(x) for x in out.tokens] == [4, 4]
