@@ -1,5 +1,5 @@
 """The host-side choices of the kernel library that need no GPU: how the weight-streaming
-product spreads K over its warps, and into how many shares of K the few-token tcgen05
+product spreads K over its warps and how many warps its blocks have, and into how many shares of K the few-token tcgen05
 product cuts the tiles that do not fill a round of the GPU.  The library loads without a
 GPU (it is compiled at the first call, a few seconds, if this checkout has not built it
 yet); without nvcc the tests are skipped."""
@@ -26,6 +26,22 @@ def test_gemv_segment_spreads_k_evenly(lib, K, seg):
     assert lib.zlm_gemv_segment(K) == seg
     if K % 1024 == 0:
         assert K % (8 * seg) == 0                   # whole chunks of 8 warps x seg columns: no warp idles
+
+
+@pytest.mark.parametrize("N,K,narrow,warps", [
+    (4096, 4096, 5, 8), (4096, 12288, 5, 8), (3072, 1024, 5, 8),   # one round of wide blocks: wide
+    (6144, 4096, 5, 4),          # 384 blocks: the 88 after the first round of 296 would run alone
+    (10240, 5120, 5, 4), (5120, 8192, 5, 4), (6144, 1024, 5, 4),
+    (12800, 4096, 5, 8),         # 800 blocks: 740 narrow ones at once would leave 60 with half the loads in flight
+    (24576, 4096, 5, 8),         # 1,536: five rounds of wide blocks and a short one, or two of narrow and a short one
+    (24576, 4096, 4, 4),         # with two token tiles four narrow blocks fit: 592 + 592 + 352
+    (10240, 5120, 4, 8),
+])
+def test_gemv_block_width_by_the_estimate_of_both_forms(lib, N, K, narrow, warps):
+    """Each case was timed on a B200 in both forms; the estimate names the faster one (or either,
+    where they were within a twentieth)."""
+    assert lib.zlm_gemv_plan_warps(N, K, 148, 2, narrow) == warps
+    assert lib.zlm_gemv_plan_warps(N, K, 0, 2, narrow) == 8        # nothing known about the device: wide
 
 
 @pytest.mark.parametrize("T,N,K,shares", [

@@ -108,6 +108,34 @@ def test_linear_bf16(K, T, N, K_):
     close(acc, base.double() + want, torch.float32, atol=1e-3, rtol=1e-3)
 
 
+@pytest.mark.parametrize("T", [1, 8, 11, 16])
+@pytest.mark.parametrize("N,K_", [(6144, 1024), (5000 + 9, 1000), (6144, 4096), (9600, 640), (5120, 3072)])
+def test_linear_bf16_gemv_blocks_of_four_warps(K, T, N, K_):
+    """More outputs than one round of the wide blocks holds: the product runs blocks of four warps
+    where the estimate says so (it does for each of these sizes at one token tile or at two).  All
+    output modes, a ragged number of outputs and a ragged K, and the fused gate/up epilogue; one
+    output far from the others' size, so that a block that read another block's rows shows."""
+    from zlm_b200.kernels import interleave_gate_up
+    assert 4 in (K.lib.zlm_gemv_plan_warps(N, K_, 148, 2, 5), K.lib.zlm_gemv_plan_warps(N, K_, 148, 2, 4))
+    x, w = rnd((T, K_), torch.bfloat16, 13), rnd((N, K_), torch.bfloat16, 14, 0.03)
+    w[N - 3] *= 30.0
+    want = x.double() @ w.double().t()
+    for out_dtype in (torch.bfloat16, torch.float32):
+        got = torch.full((T, N), 7.0, dtype=out_dtype, device="cuda")
+        K.linear(got, x.cuda(), w.cuda(), impl="gemv")
+        close(got, want, out_dtype, atol=1e-3 if out_dtype == torch.float32 else 3e-2, rtol=1e-2)
+    base = rnd((T, N), torch.float32, 15)
+    acc = base.clone().cuda()
+    K.linear(acc, x.cuda(), w.cuda(), accumulate=True, impl="gemv")
+    close(acc, base.double() + want, torch.float32, atol=1e-3, rtol=1e-3)
+    I = (N // 32) * 16
+    gate, up = w[:I], w[I:2 * I]
+    g, u = x.double() @ gate.double().t(), x.double() @ up.double().t()
+    got = torch.full((T, I), 7.0, dtype=torch.bfloat16, device="cuda")
+    K.linear_swiglu(got, x.cuda(), interleave_gate_up(gate.cuda(), up.cuda()), impl="gemv")
+    close(got, (g / (1 + torch.exp(-g))) * u, torch.bfloat16, atol=3e-2, rtol=3e-2)
+
+
 @pytest.mark.parametrize("T", [1, 7, 8, 13, 16])
 @pytest.mark.parametrize("K_,seg", [(1024, 128), (2048, 256), (3072, 384), (5120, 640), (7168, 128), (4096, 512),
                                     (12288, 512), (1000, 512), (4104, 512)])

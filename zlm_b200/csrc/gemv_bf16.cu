@@ -1,8 +1,8 @@
 // Weight-streaming bf16 product for decode steps of up to 16 tokens:
 // Y[t, n] = sum_k X[t, k] W[n, k], fp32 accumulation.
 //
-// The step is bound by reading W once.  A block owns 16 rows of W; its 8 warps
-// split K between them (512 columns each of every 4096, or another even split).  Every thread loads 16 bytes (8 consecutive k) of row g
+// The step is bound by reading W once.  A block owns 16 rows of W; its 8 warps (or 4:
+// zlm_gemv_plan_warps) split K between them (512 columns each of every 4096, or another even split).  Every thread loads 16 bytes (8 consecutive k) of row g
 // and of row g+8 straight from global memory into registers, and the 8 matching
 // k of token g of X; these registers are, as they are, the A and B fragments of
 // two m16n8k16 tensor-core products: a sum over k does not care in which order
@@ -49,12 +49,12 @@ __device__ __forceinline__ void gemv_mma(float* c, unsigned a0, unsigned a1, uns
 
 // MODE 0: Y bf16 = acc; MODE 1: Y fp32 += acc; MODE 2: Y fp32 = acc; MODE 3: the block's 16 rows are
 // 8 gate + 8 up channels, Y bf16 [T, N/2] = silu(gate) * up.  NT: token tiles of 8.
-template <int NT, int MODE>
-__global__ void __launch_bounds__(GEMV_THREADS, GEMV_MINBLOCKS)
+template <int NT, int MODE, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32, WARPS == 4 ? 4 : GEMV_MINBLOCKS)
 gemv_bf16_kernel(void* __restrict__ Y, const __nv_bfloat16* __restrict__ X,
                  const __nv_bfloat16* __restrict__ W, int T, int N, int K, int ldx, int ldy, int SEG,
                  float* __restrict__ best_v, int* __restrict__ best_i) {
-    __shared__ float red[GEMV_WARPS][NT][GEMV_ROWS][8];
+    __shared__ float red[WARPS][NT][GEMV_ROWS][8];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, q = lane & 3;
     const int n0 = blockIdx.x * GEMV_ROWS;
@@ -83,7 +83,7 @@ gemv_bf16_kernel(void* __restrict__ Y, const __nv_bfloat16* __restrict__ X,
 
     // GEMV_UNROLL blocks in flight.  The weights do not depend on the kernel before this one:
     // their first loads are issued before the wait for it, the activations after.
-    const int CHUNK = GEMV_WARPS * SEG;
+    const int CHUNK = WARPS * SEG;
     pdl_launch_dependents();
     uint4 a[GEMV_UNROLL], b[GEMV_UNROLL];
     bool have = warp * SEG + GEMV_UNROLL * 32 <= K;
@@ -155,13 +155,13 @@ gemv_bf16_kernel(void* __restrict__ Y, const __nv_bfloat16* __restrict__ X,
     }
     __syncthreads();
     if constexpr (MODE == 3) {
-        for (int idx = tid; idx < NT * 8 * 8; idx += GEMV_THREADS) {
+        for (int idx = tid; idx < NT * 8 * 8; idx += WARPS * 32) {
             const int j = idx / 64, rem = idx % 64;
             const int tok = j * 8 + rem / 8, row = rem % 8;
             if (tok >= T || n0 + row + 8 >= N) continue;
             float sg = 0.f, su = 0.f;
 #pragma unroll
-            for (int w = 0; w < GEMV_WARPS; ++w) {
+            for (int w = 0; w < WARPS; ++w) {
                 sg += red[w][j][row][tok & 7];
                 su += red[w][j][row + 8][tok & 7];
             }
@@ -169,7 +169,7 @@ gemv_bf16_kernel(void* __restrict__ Y, const __nv_bfloat16* __restrict__ X,
                 ((__nv_bfloat16*)Y)[(size_t)tok * ldy + n0 / 2 + row] = __float2bfloat16_rn((sg / (1.0f + expf(-sg))) * su);
         }
     } else {
-    for (int idx = tid; idx < NT * GEMV_ROWS * 8; idx += GEMV_THREADS) {
+    for (int idx = tid; idx < NT * GEMV_ROWS * 8; idx += WARPS * 32) {
         const int j = idx / (GEMV_ROWS * 8), rem = idx % (GEMV_ROWS * 8);
         const int tok = j * 8 + rem / GEMV_ROWS, row = rem % GEMV_ROWS;   // rows fastest: coalesced stores
         const int n = n0 + row;
@@ -177,7 +177,7 @@ gemv_bf16_kernel(void* __restrict__ Y, const __nv_bfloat16* __restrict__ X,
         float s = 0.f;
         if (live) {
 #pragma unroll
-            for (int w = 0; w < GEMV_WARPS; ++w) s += red[w][j][row][tok & 7];
+            for (int w = 0; w < WARPS; ++w) s += red[w][j][row][tok & 7];
             const size_t o = (size_t)tok * ldy + n;
             if (ZLM_CHK((char*)Y + o * (MODE == 0 ? 2 : 4), MODE == 0 ? 2 : 4)) {
                 if (MODE == 0) ((__nv_bfloat16*)Y)[o] = __float2bfloat16_rn(s);
@@ -212,25 +212,73 @@ gemv_bf16_kernel(void* __restrict__ Y, const __nv_bfloat16* __restrict__ X,
 // of K = 1024 two warps would do everything.  Where K is a multiple of 1024 but not of 4096 the
 // widest of 640, 384, 256 and 128 columns that divides K into whole chunks is taken instead
 // (multiples of the 128 columns a warp has in flight).
-extern "C" int zlm_gemv_segment(int K) {
-    if (K % 4096 == 0 || K % 1024 != 0) return 512;
+static int gemv_segment(int K, int warps) {
+    if (K % (512 * warps) == 0 || K % 1024 != 0) return 512;
     for (int seg : {640, 384, 256, 128})
-        if (K % (GEMV_WARPS * seg) == 0) return seg;
+        if (K % (warps * seg) == 0) return seg;
     return 512;
+}
+extern "C" int zlm_gemv_segment(int K) { return gemv_segment(K, GEMV_WARPS); }
+
+// Blocks of 8 warps or of 4.  A block of 8 warps has twice the loads in flight and is done in half
+// the time, which is what a product of one round of blocks wants; but two such blocks fill an SM,
+// and of 384 blocks the last 88 then run alone, far too few to keep the memory busy, where blocks
+// of 4 warps (5 to an SM, 4 with two token tiles) are all resident at once.  The choice is by an
+// estimate of both forms' time in microseconds: the blocks run in rounds of all resident places;
+// a round takes as long as its bytes at the memory's rate or as a block's own chain of loads
+// (a warp has 128 columns in flight, about a microsecond a trip), whichever is longer, and half
+// a microsecond around it.  Fitted on products of 300 to 3,000 blocks at K = 1024 and 4096 and
+// checked at K = 5120, 8192 and 12288: it names the faster form wherever the two differ by
+// more than a twentieth.
+static double gemv_estimate(int blocks, int K, int warps, int slots) {
+    const double trip_us = 1.0, bytes_per_us = 6.2e6, round_us = 0.5;
+    const double block_bytes = (double)GEMV_ROWS * K * 2;
+    const double chain = (double)((K + warps * 128 - 1) / (warps * 128)) * trip_us;
+    double t = 0;
+    for (int rem = blocks; rem > 0; rem -= slots) {
+        const double stream = (double)(rem < slots ? rem : slots) * block_bytes / bytes_per_us;
+        t += (stream > chain ? stream : chain) + round_us;
+    }
+    return t;
+}
+// 8 or 4: the warps of a block for a product of N outputs over K; wide and narrow are the blocks
+// of 8 and of 4 warps that an SM holds at once.
+extern "C" int zlm_gemv_plan_warps(int N, int K, int sms, int wide, int narrow) {
+    const int blocks = (N + GEMV_ROWS - 1) / GEMV_ROWS;
+    if (sms <= 0 || wide <= 0 || narrow <= 0 || blocks <= sms * wide) return 8;
+    return gemv_estimate(blocks, K, 4, sms * narrow) < gemv_estimate(blocks, K, 8, sms * wide) ? 4 : 8;
+}
+
+template <int NT, int WARPS>
+static int launch_gemv_w(void* Y, const __nv_bfloat16* X, const __nv_bfloat16* W, int T, int N, int K,
+                         int ldx, int ldy, int mode, float* best_v, int* best_i, cudaStream_t st) {
+    const int blocks = (N + GEMV_ROWS - 1) / GEMV_ROWS;
+    const int seg = gemv_segment(K, WARPS);
+    float* bv = mode == 2 ? best_v : nullptr;
+    int* bi = mode == 2 ? best_i : nullptr;
+    if (mode == 0) zlm_launch(gemv_bf16_kernel<NT, 0, WARPS>, blocks, WARPS * 32, 0, st, Y, X, W, T, N, K, ldx, ldy, seg, bv, bi);
+    else if (mode == 1) zlm_launch(gemv_bf16_kernel<NT, 1, WARPS>, blocks, WARPS * 32, 0, st, Y, X, W, T, N, K, ldx, ldy, seg, bv, bi);
+    else if (mode == 2) zlm_launch(gemv_bf16_kernel<NT, 2, WARPS>, blocks, WARPS * 32, 0, st, Y, X, W, T, N, K, ldx, ldy, seg, bv, bi);
+    else zlm_launch(gemv_bf16_kernel<NT, 3, WARPS>, blocks, WARPS * 32, 0, st, Y, X, W, T, N, K, ldx, ldy, seg, bv, bi);
+    return zlm_check_launch("gemv_bf16");
 }
 
 template <int NT>
 static int launch_gemv(void* Y, const __nv_bfloat16* X, const __nv_bfloat16* W, int T, int N, int K,
                        int ldx, int ldy, int mode, float* best_v, int* best_i, cudaStream_t st) {
-    const int blocks = (N + GEMV_ROWS - 1) / GEMV_ROWS;
-    const int seg = zlm_gemv_segment(K);
-    float* bv = mode == 2 ? best_v : nullptr;
-    int* bi = mode == 2 ? best_i : nullptr;
-    if (mode == 0) zlm_launch(gemv_bf16_kernel<NT, 0>, blocks, GEMV_THREADS, 0, st, Y, X, W, T, N, K, ldx, ldy, seg, bv, bi);
-    else if (mode == 1) zlm_launch(gemv_bf16_kernel<NT, 1>, blocks, GEMV_THREADS, 0, st, Y, X, W, T, N, K, ldx, ldy, seg, bv, bi);
-    else if (mode == 2) zlm_launch(gemv_bf16_kernel<NT, 2>, blocks, GEMV_THREADS, 0, st, Y, X, W, T, N, K, ldx, ldy, seg, bv, bi);
-    else zlm_launch(gemv_bf16_kernel<NT, 3>, blocks, GEMV_THREADS, 0, st, Y, X, W, T, N, K, ldx, ldy, seg, bv, bi);
-    return zlm_check_launch("gemv_bf16");
+    // the head's product (mode 2) is many rounds either way and keeps the wide blocks
+    static int sms = 0, wide = 0, narrow = 0;
+    if (!sms) {
+        int n = 0, w = 0, nw = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, zlm_device_index()) != cudaSuccess || n <= 0) n = 148;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&w, gemv_bf16_kernel<NT, 0, 8>, 8 * 32, 0) != cudaSuccess || w <= 0) w = 2;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&nw, gemv_bf16_kernel<NT, 0, 4>, 4 * 32, 0) != cudaSuccess || nw <= 0) nw = 4;
+        (void)cudaGetLastError();
+        wide = w; narrow = nw; sms = n;
+    }
+    if (mode != 2 && zlm_gemv_plan_warps(N, K, sms, wide, narrow) == 4)
+        return launch_gemv_w<NT, 4>(Y, X, W, T, N, K, ldx, ldy, mode, best_v, best_i, st);
+    return launch_gemv_w<NT, 8>(Y, X, W, T, N, K, ldx, ldy, mode, best_v, best_i, st);
 }
 
 extern "C" int zlm_gemv_max_tokens() { return 16; }
