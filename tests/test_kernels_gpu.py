@@ -571,6 +571,106 @@ def test_shares_of_a_few_token_product_are_added_up_by_the_kernel_that_reads_it_
     assert K.status(sync=True) == 0
 
 
+@pytest.mark.parametrize("T", [1, 5, 8, 13, 16])
+@pytest.mark.parametrize("H,Kin,N", [(1024, 2048, 3072), (1000, 520, 6144 + 16), (4096, 1024, 6144)])
+def test_a_norm_between_two_streaming_products_without_a_kernel_of_its_own(K, T, H, Kin, N):
+    """A streaming product into the stream that was told which norm follows leaves that norm's rows
+    (but for their scale) and the rows' sums of squares; ``rmsnorm`` then launches nothing, and the
+    streaming products that read its output scale their own sums.  Compared with the plain formula,
+    with the three kernels run one after the other, and with the norm's output read by something else
+    (it is then computed after all, the same bits as the norm's kernel).  One row of the stream is
+    made a hundred times larger than the others, so that a scale taken from another row shows."""
+    from zlm_b200.kernels import interleave_gate_up
+    x, w = rnd((T, Kin), torch.bfloat16, 301).cuda(), rnd((H, Kin), torch.bfloat16, 302, 0.05).cuda()
+    nw = (1 + rnd((H,), torch.float32, 303, 0.1)).cuda()
+    base = rnd((T, H), torch.float32, 304)
+    base[T // 2] *= 100.0
+    base = base.cuda()
+    w2 = rnd((N, H), torch.bfloat16, 305, 1.6 / H ** 0.5).cuda()      # outputs of the same size at every width
+    eps = 1e-5
+    # the three kernels one after the other
+    want_x = base.clone()
+    K.linear(want_x, x, w, accumulate=True)
+    want_n = torch.empty((T, H), dtype=torch.bfloat16, device="cuda")
+    K.rmsnorm(want_n, want_x, nw, eps)
+    before = K._launches
+    # the plain formula on the same stream (fp64)
+    xs = want_x.double()
+    normed = xs * torch.rsqrt((xs * xs).mean(-1, keepdim=True) + eps) * nw.double()
+    plain = normed @ w2.double().t()
+
+    def lazily():
+        got_x = base.clone()
+        K.expect_norm(nw)
+        K.linear(got_x, x, w, accumulate=True, defer=True)
+        assert K._norm_halves is not None and torch.equal(got_x, want_x)
+        got_n = torch.full((T, H), 7.0, dtype=torch.bfloat16, device="cuda")
+        K.norm_output_read_by_products(True)
+        n0 = K._launches
+        K.rmsnorm(got_n, got_x, nw, eps)
+        assert K._lazy is not None and K._launches == n0, "the norm was expected to be left to the products"
+        return got_x, got_n
+
+    # bf16 outputs, fp32 outputs (with the argmax's candidates), added into another stream, gate/up
+    got_x, got_n = lazily()
+    y = torch.empty((T, N), dtype=torch.bfloat16, device="cuda")
+    K.linear(y, got_n, w2)
+    close(y, plain, torch.bfloat16, atol=3e-2, rtol=2e-2)
+    lg = torch.empty((T, N), dtype=torch.float32, device="cuda")
+    K.linear(lg, got_n, w2)                                  # the same norm serves several products
+    close(lg, plain, torch.float32, atol=2e-2, rtol=1e-2)    # (the bound is that of bf16 rows times weight)
+    best = torch.empty(T, dtype=torch.int32, device="cuda")
+    K.argmax(best, lg, fresh=True)                           # from the candidates that the product left
+    assert torch.equal(best.cpu().long(), lg.argmax(-1).cpu())
+    other = rnd((T, N), torch.float32, 306).cuda()
+    acc = other.clone()
+    K.linear(acc, got_n, w2, accumulate=True)
+    close(acc, other.double() + plain, torch.float32, atol=2e-2, rtol=1e-2)
+    I = N // 2
+    act = torch.empty((T, I), dtype=torch.bfloat16, device="cuda")
+    K.linear_swiglu(act, got_n, interleave_gate_up(w2[:I].contiguous(), w2[I:].contiguous()))
+    g, u = plain[:, :I], plain[:, I:]
+    close(act, (g / (1 + torch.exp(-g))) * u, torch.bfloat16, atol=3e-2, rtol=3e-2)
+    assert K._lazy is not None
+    # and against the three kernels: the scale is applied to the sum instead of to every term
+    y3 = torch.empty((T, N), dtype=torch.float32, device="cuda")
+    K.linear(y3, want_n, w2)
+    close(lg, y3, torch.float32, atol=2e-2, rtol=1e-2)
+    # something else reads the norm's output: it is computed first, the kernel's own bits
+    copy = torch.empty((T, H // 2), dtype=torch.bfloat16, device="cuda")
+    K.swiglu(copy, got_n)
+    assert K._lazy is None and torch.equal(got_n, want_n)
+    # the stream is written before anyone read the norm: forgotten, nothing launched for it
+    got_x, got_n = lazily()
+    n0 = K._launches
+    K.linear(got_x, x, w, accumulate=True)
+    assert K._lazy is None and K._launches == n0 + 1
+    # without the arrangement's word on the readers, and for chosen rows, the norm runs as ever
+    got_x = base.clone()
+    K.expect_norm(nw)
+    K.linear(got_x, x, w, accumulate=True, defer=True)
+    got_n = torch.empty((T, H), dtype=torch.bfloat16, device="cuda")
+    K.rmsnorm(got_n, got_x, nw, eps)
+    assert K._lazy is None and K._norm_halves is None and torch.equal(got_n, want_n)
+    got_x = base.clone()
+    K.expect_norm(nw)
+    K.linear(got_x, x, w, accumulate=True, defer=True)
+    K.norm_output_read_by_products(True)
+    rows = torch.tensor([T - 1, 0], dtype=torch.int32, device="cuda")
+    some = torch.empty((2, H), dtype=torch.bfloat16, device="cuda")
+    K.rmsnorm(some, got_x, nw, eps, rows)
+    assert K._lazy is None and torch.equal(some, want_n[rows.long()])
+    # another norm's weight than the one announced: as ever
+    got_x = base.clone()
+    K.expect_norm(nw)
+    K.linear(got_x, x, w, accumulate=True, defer=True)
+    K.norm_output_read_by_products(True)
+    nw2 = nw.clone()
+    K.rmsnorm(got_n, got_x, nw2, eps)
+    assert K._lazy is None and torch.equal(got_n, want_n)
+    assert K.status(sync=True) == 0
+
+
 @pytest.mark.parametrize("T,nq,nkv,hd,Kin,norm,rope,width", [
     (500, 4, 2, 128, 256, True, True, 0), (700, 6, 3, 64, 192, True, True, 0), (390, 8, 0, 128, 128, True, True, 0),
     (450, 3, 1, 32, 96, False, True, 0), (600, 4, 4, 128, 320, True, False, 0), (1100, 5, 1, 128, 512, True, True, 128),

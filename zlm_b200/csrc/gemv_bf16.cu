@@ -49,12 +49,29 @@ __device__ __forceinline__ void gemv_mma(float* c, unsigned a0, unsigned a1, uns
 
 // MODE 0: Y bf16 = acc; MODE 1: Y fp32 += acc; MODE 2: Y fp32 = acc; MODE 3: the block's 16 rows are
 // 8 gate + 8 up channels, Y bf16 [T, N/2] = silu(gate) * up.  NT: token tiles of 8.
+//
+// The RMSNorm between a product into the stream and the product that reads the normed stream, without
+// a kernel of its own (GemvNorm).  MODE 4 is MODE 1 that also leaves what the norm needs: next[t, n] =
+// bf16(Y[t, n] * weight[n]), the normed row but for its scale, and for every token the sum of Y^2 over
+// this block's 16 outputs (squares[t][block]).  A product that is given such sums for its input adds
+// them up in a fixed order, scale[t] = 1 / sqrt(sum / K + eps), and multiplies its sums by it before
+// anything else is done with them: sum_k W[n, k] (x[k] w[k] scale) = scale * sum_k W[n, k] (x[k] w[k]).
+// Squares, sum and scale are 32-bit (src/kernels/transformer/norm.zig:128-166).
+struct GemvNorm {
+    const float* in_squares;        // [T][in_blocks], or null: X is what it is
+    int in_blocks;
+    float in_eps;
+    VecW weight;                    // MODE 4: the following norm's weight [N]
+    __nv_bfloat16* next;            // MODE 4: [T][N]
+    float* squares;                 // MODE 4: [T][blocks of this product]
+};
 template <int NT, int MODE, int WARPS>
-__global__ void __launch_bounds__(WARPS * 32, WARPS == 4 ? 4 : GEMV_MINBLOCKS)
+__global__ void __launch_bounds__(WARPS * 32, WARPS == 4 ? 4 : 2)
 gemv_bf16_kernel(void* __restrict__ Y, const __nv_bfloat16* __restrict__ X,
                  const __nv_bfloat16* __restrict__ W, int T, int N, int K, int ldx, int ldy, int SEG,
-                 float* __restrict__ best_v, int* __restrict__ best_i) {
+                 float* __restrict__ best_v, int* __restrict__ best_i, const GemvNorm nm) {
     __shared__ float red[WARPS][NT][GEMV_ROWS][8];
+    __shared__ float scale[NT * 8];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int g = lane >> 2, q = lane & 3;
     const int n0 = blockIdx.x * GEMV_ROWS;
@@ -95,6 +112,33 @@ gemv_bf16_kernel(void* __restrict__ Y, const __nv_bfloat16* __restrict__ X,
         }
     }
     pdl_wait();
+    // What the epilogue would otherwise wait for after the last product: the stream's old values
+    // (MODE 1 and 4), the following norm's weight, and the scale of an input whose norm was left to
+    // this product.  Asked for now, they arrive under the weights' first loads.
+    constexpr int EPI = (NT * GEMV_ROWS * 8 + WARPS * 32 - 1) / (WARPS * 32);
+    float y_old[EPI], nw_row = 0.f;
+    if constexpr (MODE == 1 || MODE == 4) {
+#pragma unroll
+        for (int it = 0; it < EPI; ++it) {
+            const int idx = tid + it * WARPS * 32;
+            const int tok = (idx / (GEMV_ROWS * 8)) * 8 + (idx % (GEMV_ROWS * 8)) / GEMV_ROWS, n = n0 + idx % GEMV_ROWS;
+            const float* yp = (const float*)Y + (size_t)tok * ldy + n;
+            y_old[it] = (idx < NT * GEMV_ROWS * 8 && tok < T && n < N && ZLM_CHK(yp, 4)) ? *yp : 0.f;
+        }
+        if (MODE == 4 && n0 + tid % GEMV_ROWS < N) nw_row = nm.weight[n0 + tid % GEMV_ROWS];   // a thread's row is the same in every turn
+    }
+    if (nm.in_squares) {
+        // the scale of a row whose norm is left to this product: a warp a token, the blocks' sums in
+        // lanes and then across them, the same order in every block and every run
+        for (int tok = warp; tok < T; tok += WARPS) {
+            const float* sq = nm.in_squares + (size_t)tok * nm.in_blocks;
+            float ss = 0.f;
+            for (int i = lane; i < nm.in_blocks; i += 32)
+                if (ZLM_CHK(sq + i, 4)) ss += sq[i];
+            ss = warp_sum(ss);
+            if (lane == 0) scale[tok] = 1.0f / sqrtf(ss / (float)K + nm.in_eps);
+        }
+    }
     for (int kc = warp * SEG; kc < K; kc += CHUNK) {
         const int kend = min(K, kc + SEG);
         int kb = kc;
@@ -165,11 +209,15 @@ gemv_bf16_kernel(void* __restrict__ Y, const __nv_bfloat16* __restrict__ X,
                 sg += red[w][j][row][tok & 7];
                 su += red[w][j][row + 8][tok & 7];
             }
+            if (nm.in_squares) { sg *= scale[tok]; su *= scale[tok]; }
             if (ZLM_CHK((__nv_bfloat16*)Y + (size_t)tok * ldy + n0 / 2 + row, 2))
                 ((__nv_bfloat16*)Y)[(size_t)tok * ldy + n0 / 2 + row] = __float2bfloat16_rn((sg / (1.0f + expf(-sg))) * su);
         }
     } else {
-    for (int idx = tid; idx < NT * GEMV_ROWS * 8; idx += WARPS * 32) {
+#pragma unroll
+    for (int it = 0; it < EPI; ++it) {
+        const int idx = tid + it * WARPS * 32;
+        if (idx >= NT * GEMV_ROWS * 8) break;            // whole warps
         const int j = idx / (GEMV_ROWS * 8), rem = idx % (GEMV_ROWS * 8);
         const int tok = j * 8 + rem / GEMV_ROWS, row = rem % GEMV_ROWS;   // rows fastest: coalesced stores
         const int n = n0 + row;
@@ -178,12 +226,24 @@ gemv_bf16_kernel(void* __restrict__ Y, const __nv_bfloat16* __restrict__ X,
         if (live) {
 #pragma unroll
             for (int w = 0; w < WARPS; ++w) s += red[w][j][row][tok & 7];
+            if (nm.in_squares) s *= scale[tok];
             const size_t o = (size_t)tok * ldy + n;
             if (ZLM_CHK((char*)Y + o * (MODE == 0 ? 2 : 4), MODE == 0 ? 2 : 4)) {
                 if (MODE == 0) ((__nv_bfloat16*)Y)[o] = __float2bfloat16_rn(s);
-                else if (MODE == 1) ((float*)Y)[o] += s;
+                else if (MODE == 1 || MODE == 4) { s += y_old[it]; ((float*)Y)[o] = s; }     // s: the stream's new value
                 else ((float*)Y)[o] = s;
-            }
+            } else s = 0.f;
+        }
+        if (MODE == 4) {
+            // what the norm after this product needs: the new values times its weight, and the
+            // token's sum of squares over this block's outputs (16 neighbouring lanes, whole warps)
+            if (live && ZLM_CHK(nm.next + (size_t)tok * N + n, 2))
+                nm.next[(size_t)tok * N + n] = __float2bfloat16_rn(s * nw_row);
+            float ss = live ? s * s : 0.f;
+#pragma unroll
+            for (int o2 = 8; o2 > 0; o2 >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o2);
+            if (row == 0 && tok < T && ZLM_CHK(nm.squares + (size_t)tok * gridDim.x + blockIdx.x, 4))
+                nm.squares[(size_t)tok * gridDim.x + blockIdx.x] = ss;
         }
         if (MODE == 2 && best_v) {
             // The logits' argmax starts here: the best of this block's 16 outputs for every token
@@ -251,21 +311,22 @@ extern "C" int zlm_gemv_plan_warps(int N, int K, int sms, int wide, int narrow) 
 
 template <int NT, int WARPS>
 static int launch_gemv_w(void* Y, const __nv_bfloat16* X, const __nv_bfloat16* W, int T, int N, int K,
-                         int ldx, int ldy, int mode, float* best_v, int* best_i, cudaStream_t st) {
+                         int ldx, int ldy, int mode, float* best_v, int* best_i, const GemvNorm& nm, cudaStream_t st) {
     const int blocks = (N + GEMV_ROWS - 1) / GEMV_ROWS;
     const int seg = gemv_segment(K, WARPS);
     float* bv = mode == 2 ? best_v : nullptr;
     int* bi = mode == 2 ? best_i : nullptr;
-    if (mode == 0) zlm_launch(gemv_bf16_kernel<NT, 0, WARPS>, blocks, WARPS * 32, 0, st, Y, X, W, T, N, K, ldx, ldy, seg, bv, bi);
-    else if (mode == 1) zlm_launch(gemv_bf16_kernel<NT, 1, WARPS>, blocks, WARPS * 32, 0, st, Y, X, W, T, N, K, ldx, ldy, seg, bv, bi);
-    else if (mode == 2) zlm_launch(gemv_bf16_kernel<NT, 2, WARPS>, blocks, WARPS * 32, 0, st, Y, X, W, T, N, K, ldx, ldy, seg, bv, bi);
-    else zlm_launch(gemv_bf16_kernel<NT, 3, WARPS>, blocks, WARPS * 32, 0, st, Y, X, W, T, N, K, ldx, ldy, seg, bv, bi);
+    if (mode == 0) zlm_launch(gemv_bf16_kernel<NT, 0, WARPS>, blocks, WARPS * 32, 0, st, Y, X, W, T, N, K, ldx, ldy, seg, bv, bi, nm);
+    else if (mode == 1) zlm_launch(gemv_bf16_kernel<NT, 1, WARPS>, blocks, WARPS * 32, 0, st, Y, X, W, T, N, K, ldx, ldy, seg, bv, bi, nm);
+    else if (mode == 2) zlm_launch(gemv_bf16_kernel<NT, 2, WARPS>, blocks, WARPS * 32, 0, st, Y, X, W, T, N, K, ldx, ldy, seg, bv, bi, nm);
+    else if (mode == 3) zlm_launch(gemv_bf16_kernel<NT, 3, WARPS>, blocks, WARPS * 32, 0, st, Y, X, W, T, N, K, ldx, ldy, seg, bv, bi, nm);
+    else zlm_launch(gemv_bf16_kernel<NT, 4, WARPS>, blocks, WARPS * 32, 0, st, Y, X, W, T, N, K, ldx, ldy, seg, bv, bi, nm);
     return zlm_check_launch("gemv_bf16");
 }
 
 template <int NT>
 static int launch_gemv(void* Y, const __nv_bfloat16* X, const __nv_bfloat16* W, int T, int N, int K,
-                       int ldx, int ldy, int mode, float* best_v, int* best_i, cudaStream_t st) {
+                       int ldx, int ldy, int mode, float* best_v, int* best_i, const GemvNorm& nm, cudaStream_t st) {
     // the head's product (mode 2) is many rounds either way and keeps the wide blocks
     static int sms = 0, wide = 0, narrow = 0;
     if (!sms) {
@@ -277,8 +338,8 @@ static int launch_gemv(void* Y, const __nv_bfloat16* X, const __nv_bfloat16* W, 
         wide = w; narrow = nw; sms = n;
     }
     if (mode != 2 && zlm_gemv_plan_warps(N, K, sms, wide, narrow) == 4)
-        return launch_gemv_w<NT, 4>(Y, X, W, T, N, K, ldx, ldy, mode, best_v, best_i, st);
-    return launch_gemv_w<NT, 8>(Y, X, W, T, N, K, ldx, ldy, mode, best_v, best_i, st);
+        return launch_gemv_w<NT, 4>(Y, X, W, T, N, K, ldx, ldy, mode, best_v, best_i, nm, st);
+    return launch_gemv_w<NT, 8>(Y, X, W, T, N, K, ldx, ldy, mode, best_v, best_i, nm, st);
 }
 
 extern "C" int zlm_gemv_max_tokens() { return 16; }
@@ -286,24 +347,29 @@ extern "C" int zlm_gemv_max_tokens() { return 16; }
 extern "C" int zlm_gemv_blocks(int N) { return (N + GEMV_ROWS - 1) / GEMV_ROWS; }
 
 static int gemv_entry(void* Y, const void* X, const void* W, int T, int N, int K, int ldx, int ldy, int mode,
-                      float* best_v, int* best_i, cudaStream_t st) {
+                      float* best_v, int* best_i, const GemvNorm& nm, cudaStream_t st) {
     if (T == 0 || N == 0) return ZLM_OK;
     ZLM_REQUIRE(T > 0 && T <= 16, "gemv_bf16: takes 1 to 16 tokens, got %d", T);
     ZLM_REQUIRE(N > 0 && K > 0, "gemv_bf16: bad sizes N=%d K=%d", N, K);
     ZLM_REQUIRE(K % 8 == 0 && ldx % 8 == 0,
                 "gemv_bf16: the inner size K=%d (row stride %d) must be a multiple of 8 for bf16 kernels", K, ldx);
     ZLM_REQUIRE(((uintptr_t)X % 16 == 0) && ((uintptr_t)W % 16 == 0), "gemv_bf16: operands must be 16-byte aligned");
-    ZLM_REQUIRE(mode >= 0 && mode <= 3, "gemv_bf16: mode %d", mode);
+    ZLM_REQUIRE(mode >= 0 && mode <= 4, "gemv_bf16: mode %d", mode);
     ZLM_REQUIRE(mode != 3 || N % 16 == 0, "gemv_bf16: the fused gate/up product needs N=%d to be a multiple of 16", N);
+    ZLM_REQUIRE(mode != 4 || (nm.weight.p && nm.next && nm.squares), "gemv_bf16: the following norm's weight and outputs are missing");
+    ZLM_REQUIRE(!nm.in_squares || nm.in_blocks > 0, "gemv_bf16: sums of squares of %d blocks", nm.in_blocks);
     const __nv_bfloat16* x = (const __nv_bfloat16*)X;
     const __nv_bfloat16* w = (const __nv_bfloat16*)W;
-    if (T <= 8) return launch_gemv<1>(Y, x, w, T, N, K, ldx, ldy, mode, best_v, best_i, st);
-    return launch_gemv<2>(Y, x, w, T, N, K, ldx, ldy, mode, best_v, best_i, st);
+    if (T <= 8) return launch_gemv<1>(Y, x, w, T, N, K, ldx, ldy, mode, best_v, best_i, nm, st);
+    return launch_gemv<2>(Y, x, w, T, N, K, ldx, ldy, mode, best_v, best_i, nm, st);
 }
+
+static GemvNorm gemv_no_norm() { return GemvNorm{nullptr, 0, 0.f, VecW{nullptr, ZLM_DTYPE_F32}, nullptr, nullptr}; }
 
 extern "C" int zlm_gemv_bf16(void* Y, const void* X, const void* W, int T, int N, int K, int ldx,
                              int ldy, int mode, cudaStream_t st) {
-    return gemv_entry(Y, X, W, T, N, K, ldx, ldy, mode, nullptr, nullptr, st);
+    ZLM_REQUIRE(mode != 4, "gemv_bf16: mode 4 is zlm_gemv_bf16_norms'");
+    return gemv_entry(Y, X, W, T, N, K, ldx, ldy, mode, nullptr, nullptr, gemv_no_norm(), st);
 }
 
 // Y fp32 [T, N] = X W^T, and for every token the best (value, index) of each block's 16 outputs:
@@ -311,7 +377,21 @@ extern "C" int zlm_gemv_bf16(void* Y, const void* X, const void* W, int T, int N
 extern "C" int zlm_gemv_bf16_best(void* Y, const void* X, const void* W, int T, int N, int K, int ldx, int ldy,
                                   float* best_v, int* best_i, cudaStream_t st) {
     ZLM_REQUIRE(best_v && best_i, "gemv_bf16_best: the candidates' arrays are missing");
-    return gemv_entry(Y, X, W, T, N, K, ldx, ldy, 2, best_v, best_i, st);
+    return gemv_entry(Y, X, W, T, N, K, ldx, ldy, 2, best_v, best_i, gemv_no_norm(), st);
+}
+
+// The product with an RMSNorm's halves in it (GemvNorm above).  in_squares [T][in_blocks]: X is a
+// normed row but for its scale, which is taken from these sums with in_eps (null: X as it is).
+// norm_weight (mode 1 only; null: no following norm): Y += acc also leaves next [T][N] bf16 and
+// squares [T][zlm_gemv_blocks(N)] for the product after the norm.  best_v / best_i as above
+// (mode 2; may be null).
+extern "C" int zlm_gemv_bf16_norms(void* Y, const void* X, const void* W, int T, int N, int K, int ldx, int ldy,
+                                   int mode, float* best_v, int* best_i, const float* in_squares, int in_blocks,
+                                   float in_eps, const void* norm_weight, int norm_weight_dtype, void* next,
+                                   float* squares, cudaStream_t st) {
+    ZLM_REQUIRE(mode != 4 && (!norm_weight || mode == 1), "gemv_bf16_norms: a following norm goes with mode 1, got %d", mode);
+    GemvNorm nm{in_squares, in_blocks, in_eps, VecW{norm_weight, norm_weight_dtype}, (__nv_bfloat16*)next, squares};
+    return gemv_entry(Y, X, W, T, N, K, ldx, ldy, norm_weight ? 4 : mode, best_v, best_i, nm, st);
 }
 
 ZLM_TRANSLATION_UNIT(gemv_bf16)

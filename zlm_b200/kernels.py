@@ -119,6 +119,12 @@ class CudaKernels:
         self._shares = None            # (output, scratch, shares, accumulate) of a product left in shares of K (see linear)
         self.defer_shares = True       # whether linear(defer=True) may leave a product so
         self._candidates = None        # (address of the last logits a few-token product wrote, rows, width, blocks, values, indices)
+        # An RMSNorm between two streaming products without a kernel of its own (see ``expect_norm``):
+        self.lazy_norms = True         # whether that may happen at all
+        self._norm_hint = None         # the weight of the norm that is to follow the next product into the stream
+        self._norm_halves = None       # (stream, rows times weight, sums of squares, blocks, weight): a product left them
+        self._lazy_ok = False          # the next norm's output is read by products only (the arrangement's word)
+        self._lazy = None              # (out, stream, weight, eps, rows times weight, sums of squares, blocks): a norm not run
         self._scratch = {}
         self.scratch_generation = 0
         self._launches = 0
@@ -166,9 +172,56 @@ class CudaKernels:
                 noted, self._ranges = self._ranges, []      # (this happens while a call's arguments are gathered)
                 self.flush_shares()
                 self._ranges = noted
+        if self._lazy is not None or self._norm_halves is not None:
+            self._touch_norms(t)
         if self.bounds_check:
             self._ranges.append((t.data_ptr(), _span_bytes(t)))
         return c_void_p(t.data_ptr())
+
+    @staticmethod
+    def _overlap(a: torch.Tensor, b: torch.Tensor) -> bool:
+        return a.data_ptr() < b.data_ptr() + _span_bytes(b) and b.data_ptr() < a.data_ptr() + _span_bytes(a)
+
+    def _touch_norms(self, t: torch.Tensor) -> None:
+        """A kernel is about to be given ``t``.  Halves of a norm that a product left are void once anything
+        else touches the stream they belong to.  A norm that was not run is run now if ``t`` is its output;
+        if ``t`` is its stream, the part that was to read the output has gone on to write (the arrangement
+        said that it reads before it writes and nobody reads afterwards), and the norm is forgotten."""
+        if self._norm_halves is not None and self._overlap(t, self._norm_halves[0]):
+            self._norm_halves = None
+        if self._lazy is not None:
+            if self._overlap(t, self._lazy[0]):
+                noted, self._ranges = self._ranges, []      # (this happens while a call's arguments are gathered)
+                self.finish_norm()
+                self._ranges = noted
+            elif self._overlap(t, self._lazy[1]):
+                self._lazy = None
+
+    def expect_norm(self, weight: Optional[torch.Tensor]) -> None:
+        """An arrangement's word that ``rmsnorm`` with this weight is the next reader of the stream after
+        the next product into it (``linear(..., accumulate=True, defer=True)``); None takes it back.  A
+        streaming product (up to 16 tokens) then also leaves the normed rows but for their scale, and
+        the rows' sums of squares block by block; ``rmsnorm`` launches nothing, and the streaming
+        products that read its output take the scale from those sums and apply it to their own sums.
+        73 launches fewer in a decode step.  Whatever else is given the norm's output through this
+        class has the norm run first (``finish_norm``), so the word is never wrong, only sometimes
+        useless; code that reads it by other means says so beforehand (``norm_output_read_by_products``)."""
+        self._norm_hint = weight if self.lazy_norms else None
+
+    def norm_output_read_by_products(self, yes: bool) -> None:
+        """An arrangement's word on the next ``rmsnorm``: its output is read only through this class,
+        before the reading part writes into the stream, and by nobody after that.  Holds for one call."""
+        self._lazy_ok = bool(yes) and self.lazy_norms
+
+    def finish_norm(self) -> None:
+        """Runs a norm that ``rmsnorm`` left to the products after it."""
+        if self._lazy is None:
+            return
+        out, x, w, eps = self._lazy[:4]
+        self._lazy = None
+        R, H = out.shape
+        self._call("zlm_rmsnorm", self._p(out), c_int(_dt(out)), self._p(x), self._p(w), c_int(_dt(w)),
+                   self._p(None), c_int(R), c_int(H), c_float(eps), self._stream())
 
     def _register_ranges(self) -> None:
         lib = self.lib
@@ -242,6 +295,15 @@ class CudaKernels:
         assert x.dtype == torch.float32 and x.shape[1] == H and w.shape == (H,)
         assert out.is_contiguous() and x.is_contiguous() and w.is_contiguous()
         assert rows is None or (rows.dtype == torch.int32 and rows.numel() >= R)
+        halves, self._norm_halves = self._norm_halves, None
+        ok, self._lazy_ok = self._lazy_ok, False
+        if (halves is not None and ok and rows is None and out.dtype == torch.bfloat16
+                and halves[0].data_ptr() == x.data_ptr() and tuple(halves[0].shape) == (R, H)
+                and halves[4].data_ptr() == w.data_ptr()):
+            # the product before left this norm's halves and only streaming products read ``out``: nothing to launch
+            self._lazy = (out, x, w, float(eps)) + tuple(halves[1:4])
+            return
+        self._lazy = None
         taken = self._takes_shares(x, ACCUM) if (rows is None and x.shape[0] == R) else None
         if taken is not None:
             self._call("zlm_rmsnorm_shares", self._p(out), c_int(_dt(out)), self._p(x), self._p(w), c_int(_dt(w)),
@@ -292,6 +354,12 @@ class CudaKernels:
         mode = ACCUM if accumulate else (STORE_F32 if out.dtype == torch.float32 else STORE)
         if mode == STORE:
             assert out.dtype == torch.bfloat16
+        if accumulate and defer:
+            hint, self._norm_hint = self._norm_hint, None
+            if (hint is not None and impl is None and self.streams_weights(T, N) and out.is_contiguous()
+                    and hint.is_contiguous() and tuple(hint.shape) == (N,)):
+                self._gemv(out, x, w, T, N, K, ldx, ldy, ACCUM, norm_weight=hint)
+                return
         if (defer and self.defer_shares and impl is None and mode in (ACCUM, STORE) and T > 16 and out.is_contiguous()
                 and not self.streams_weights(T, N)):
             ks = int(self.lib.zlm_gemm_tc_shares_plan(c_int(T), c_int(N), c_int(K), c_int(ldx)))
@@ -305,7 +373,10 @@ class CudaKernels:
         self._bf16_product(out, x, w, T, N, K, ldx, ldy, mode, impl)
 
     def flush_shares(self) -> None:
-        """Finishes a product that ``linear(defer=True)`` left in shares of K (its second kernel)."""
+        """Finishes a product that ``linear(defer=True)`` left in shares of K (its second kernel), and a
+        norm that was left to the products after it."""
+        self.finish_norm()
+        self._norm_halves = None
         if self._shares is None:
             return
         out, scratch, ks, mode = self._shares
@@ -349,20 +420,41 @@ class CudaKernels:
                        c_int(T), c_int(N), c_int(K), c_int(ldx), c_int(ldy), c_int(mode), self._p(scratch),
                        self._stream())
             return
-        if impl == "gemv" and mode == STORE_F32 and out.is_contiguous():
+        if impl == "gemv":
+            self._gemv(out, x, w, T, N, K, ldx, ldy, mode)
+            return
+        self._call("zlm_gemm_bf16_mma", self._p(out), self._p(x), self._p(w),
+                   c_int(T), c_int(N), c_int(K), c_int(ldx), c_int(ldy), c_int(mode), self._stream())
+
+    def _gemv(self, out, x, w, T, N, K, ldx, ldy, mode, norm_weight: Optional[torch.Tensor] = None) -> None:
+        """The streaming product, with what it may carry beside its sums: candidates for the argmax of
+        logits, the scale of a norm that was not run (``x`` is that norm's output), the halves of the
+        norm that follows (``norm_weight``)."""
+        lazy = self._lazy
+        if not (lazy is not None and lazy[0].data_ptr() == x.data_ptr() and tuple(lazy[0].shape) == (T, K) and ldx == K):
+            lazy = None
+        nb = int(self.lib.zlm_gemv_blocks(c_int(N)))
+        cv = ci = nxt = sq = None
+        if mode == STORE_F32 and out.is_contiguous():
             # fp32 outputs of a few-token product are logits: the product also leaves, for every
             # token, the best of each block's 16 outputs, and ``argmax`` of the same tensor picks
             # among those candidates instead of reading the logits again
-            nb = int(self.lib.zlm_gemv_blocks(c_int(N)))
             cv = self.scratch("gemv.best_values", T * nb, torch.float32, out.device)
             ci = self.scratch("gemv.best_indices", T * nb, torch.int32, out.device)
-            self._call("zlm_gemv_bf16_best", self._p(out), self._p(x), self._p(w), c_int(T), c_int(N), c_int(K),
-                       c_int(ldx), c_int(ldy), self._p(cv), self._p(ci), self._stream())
+        if norm_weight is not None:
+            nxt = self.scratch("gemv.norm_rows", T * N, torch.bfloat16, out.device)
+            sq = self.scratch("gemv.norm_squares", T * nb, torch.float32, out.device)
+        # a norm not run: its rows times weight stand in for x, the scale comes from the sums of squares
+        px = self._p(lazy[4]) if lazy is not None else self._p(x)
+        self._call("zlm_gemv_bf16_norms", self._p(out), px, self._p(w), c_int(T), c_int(N), c_int(K),
+                   c_int(ldx), c_int(ldy), c_int(mode), self._p(cv), self._p(ci),
+                   self._p(lazy[5]) if lazy is not None else c_void_p(0), c_int(lazy[6] if lazy is not None else 0),
+                   c_float(lazy[3] if lazy is not None else 0.0), self._p(norm_weight),
+                   c_int(_dt(norm_weight) if norm_weight is not None else 0), self._p(nxt), self._p(sq), self._stream())
+        if cv is not None:
             self._candidates = (out.data_ptr(), T, N, nb, cv, ci)
-            return
-        name = {"gemv": "zlm_gemv_bf16", "mma": "zlm_gemm_bf16_mma"}[impl]
-        self._call(name, self._p(out), self._p(x), self._p(w),
-                   c_int(T), c_int(N), c_int(K), c_int(ldx), c_int(ldy), c_int(mode), self._stream())
+        if norm_weight is not None:
+            self._norm_halves = (out, nxt, sq, nb, norm_weight)
 
     def set_gemm_form(self, form: Optional[str] = None, width: int = 0) -> None:
         """Forces the many-token tcgen05 product's form ("single": one block per tile,

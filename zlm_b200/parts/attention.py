@@ -21,6 +21,8 @@ from .base import CacheRequest, LayerIO, Mixer, ParamSpec, StepContext
 
 @register_mixer("gqa_attention")
 class GQAAttention(Mixer):
+    reads_input_by_products = True       # x goes into the q/k/v projection and nowhere else
+
     def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  qk_norm: bool = False, qk_norm_eps: float = 1e-6, window: int = 0,
                  position: Optional[Mapping[str, Any]] = None, kv_proj: bool = True):

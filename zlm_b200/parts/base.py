@@ -206,7 +206,8 @@ class Part:
 
 
 class Norm(Part):
-    # Whether this norm reads the stream through ``kernels.rmsnorm`` alone.  A part before it may have
+    # Whether this norm reads the stream through ``kernels.rmsnorm`` alone (with the tensor it keeps as
+    # ``weight``, if the product before it is to prepare it: ``CudaKernels.expect_norm``).  A part before it may have
     # left its last product into the stream in shares of K for that kernel to add up
     # (``linear(..., defer=True)``); before a norm that reads the stream in any other way the
     # arrangement has that product finished (``finish_products``).
@@ -222,6 +223,12 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
+    # Whether the part reads its input x only through the kernel object's products (``linear`` and
+    # its fused forms), all of them before it first writes into the stream, and not afterwards.  The
+    # arrangement passes this on for the norm before the part (``norm_output_read_by_products``), whose
+    # rows may then never be written out: the products take them from the product before the norm.
+    reads_input_by_products = False
+
     def cache_request(self) -> Optional[CacheRequest]:
         return None
 
@@ -233,5 +240,7 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
+    reads_input_by_products = False      # as Mixer.reads_input_by_products
+
     def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx: StepContext) -> None:
         raise NotImplementedError

@@ -16,6 +16,8 @@ from .base import FeedForward, ParamSpec, StepContext
 
 @register_feed_forward("swiglu")
 class SwiGLU(FeedForward):
+    reads_input_by_products = True       # x goes into the gate/up product and nowhere else
+
     def __init__(self, hidden_size: int, intermediate_size: int):
         self.hidden = int(hidden_size)
         self.inter = int(intermediate_size)

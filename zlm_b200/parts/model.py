@@ -121,8 +121,15 @@ class DecoderModel:
         rt = self.rt
         hidden = rt.ws.get("model.hidden", (ctx.T, self.spec.hidden_size), torch.float32)
         self.embedding.forward(hidden, ctx.token_ids)
-        for e, io in zip(self.spec.schedule, ios):
+        sched = self.spec.schedule
+        for i, (e, io) in enumerate(zip(sched, ios)):
+            # who reads the stream after this block: the next block's first norm (the final norm reads
+            # chosen rows only and is told of nothing)
+            nxt = self.blocks[sched[i + 1].layer] if i + 1 < len(sched) else None
+            first = getattr(nxt, "first_norm_weight", None)
+            ctx.extras["norm_after_block"] = first() if first is not None else None
             self.blocks[e.layer].forward(hidden, ctx, io)
+        ctx.extras["norm_after_block"] = None
         return hidden
 
     def logits(self, hidden: torch.Tensor, rows: torch.Tensor, n_rows: int,
