@@ -25,11 +25,11 @@ attention_decode_kernel(__nv_bfloat16* __restrict__ out, int out_stride, const _
                         const int* __restrict__ block_table, int table_stride,
                         const int* __restrict__ token_pos, const int* __restrict__ token_slot, int nq, int nkv,
                         float scale_log2, int window, int splits, int per, float* __restrict__ part_o,
-                        float* __restrict__ part_ml) {
+                        float* __restrict__ part_ml, int fresh) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     attention_decode_item<HD, true>(smem_raw, threadIdx.x, GroupSync{0, DEC_THREADS}, blockIdx.x, blockIdx.y,
                                     blockIdx.z, out, out_stride, q, q_stride, pool, block_table, table_stride,
-                                    token_pos, token_slot, nq, nkv, scale_log2, window, splits, per, part_o, part_ml);
+                                    token_pos, token_slot, nq, nkv, scale_log2, window, splits, per, part_o, part_ml, fresh);
 }
 
 __global__ void __launch_bounds__(COMB_THREADS)
@@ -48,7 +48,7 @@ template <int HD>
 static int launch_decode(__nv_bfloat16* out, int out_stride, const __nv_bfloat16* q, int q_stride,
                          const __nv_bfloat16* pool, const int* block_table, int table_stride,
                          const int* token_pos, const int* token_slot, int T, int nq, int nkv, float scale,
-                         int window, int splits, int per, float* part_o, float* part_ml, cudaStream_t st) {
+                         int window, int splits, int per, float* part_o, float* part_ml, int fresh, cudaStream_t st) {
     const size_t stage_bytes = (size_t)4 * ZLM_PAGE * HD * sizeof(__nv_bfloat16);
     const size_t merge_bytes = (size_t)DEC_WARPS * 16 * (HD + 2) * sizeof(float);
     const size_t smem = stage_bytes > merge_bytes ? stage_bytes : merge_bytes;
@@ -65,7 +65,7 @@ static int launch_decode(__nv_bfloat16* out, int out_stride, const __nv_bfloat16
     dim3 grid(T, nkv, splits);
     const float scale_log2 = scale * 1.4426950408889634f;
     zlm_launch(kern, grid, dim3(DEC_THREADS), smem, st, out, out_stride, q, q_stride, pool, block_table, table_stride,
-               token_pos, token_slot, nq, nkv, scale_log2, window, splits, per, part_o, part_ml);
+               token_pos, token_slot, nq, nkv, scale_log2, window, splits, per, part_o, part_ml, fresh);
     int rc = zlm_check_launch("attention_decode");
     if (rc) return rc;
     if (splits > 1) {
@@ -82,12 +82,15 @@ extern "C" int zlm_attention_decode_supported(int nq, int nkv, int hd) {
 }
 
 // every split takes `per` pages; splits * per pages must cover the longest sequence.
-// scratch: part_o needs T*nq*splits*hd floats, part_ml T*nq*splits*2 floats (unused if splits == 1)
-extern "C" int zlm_attention_decode(void* out, int out_stride, const void* q, int q_stride, const void* pool,
-                                    const int* block_table, int table_stride, const int* token_pos,
-                                    const int* token_slot, int T, int nq, int nkv, int hd, float scale,
-                                    int window, int splits, int per, float* part_o, float* part_ml,
-                                    cudaStream_t st) {
+// scratch: part_o needs T*nq*splits*hd floats, part_ml T*nq*splits*2 floats (unused if splits == 1).
+// fresh: how many of each sequence's newest positions the kernels of this step may have written
+// (1 for a decode step); pages that hold older positions only are read before the wait for the
+// kernel before this one.  0: not known, nothing is read early.
+extern "C" int zlm_attention_decode_fresh(void* out, int out_stride, const void* q, int q_stride, const void* pool,
+                                          const int* block_table, int table_stride, const int* token_pos,
+                                          const int* token_slot, int T, int nq, int nkv, int hd, float scale,
+                                          int window, int splits, int per, float* part_o, float* part_ml,
+                                          int fresh, cudaStream_t st) {
     if (T == 0) return ZLM_OK;
     ZLM_REQUIRE(zlm_attention_decode_supported(nq, nkv, hd),
                 "attention_decode: %d heads over %d kv heads of size %d is not a shape this kernel takes", nq, nkv, hd);
@@ -95,17 +98,27 @@ extern "C" int zlm_attention_decode(void* out, int out_stride, const void* q, in
                 "attention_decode: splits=%d (at most %d) of %d pages", splits, COMB_MAX_SPLITS, per);
     ZLM_REQUIRE(splits == 1 || (part_o && part_ml), "attention_decode: scratch missing for %d splits", splits);
     ZLM_REQUIRE(q_stride % 2 == 0 && ((uintptr_t)q % 4 == 0), "attention_decode: q must be 4-byte aligned");
+    ZLM_REQUIRE(fresh >= 0, "attention_decode: fresh=%d", fresh);
 #define ZLM_DEC_CASE(H)                                                                                       \
     case H:                                                                                                   \
         return launch_decode<H>((__nv_bfloat16*)out, out_stride, (const __nv_bfloat16*)q, q_stride,           \
                                 (const __nv_bfloat16*)pool, block_table, table_stride, token_pos, token_slot, \
-                                T, nq, nkv, scale, window, splits, per, part_o, part_ml, st);
+                                T, nq, nkv, scale, window, splits, per, part_o, part_ml, fresh, st);
     switch (hd) {
         ZLM_DEC_CASE(16) ZLM_DEC_CASE(32) ZLM_DEC_CASE(48) ZLM_DEC_CASE(64) ZLM_DEC_CASE(80) ZLM_DEC_CASE(96)
         ZLM_DEC_CASE(112) ZLM_DEC_CASE(128)
     }
 #undef ZLM_DEC_CASE
     ZLM_REQUIRE(false, "attention_decode: head_dim=%d", hd);
+}
+
+extern "C" int zlm_attention_decode(void* out, int out_stride, const void* q, int q_stride, const void* pool,
+                                    const int* block_table, int table_stride, const int* token_pos,
+                                    const int* token_slot, int T, int nq, int nkv, int hd, float scale,
+                                    int window, int splits, int per, float* part_o, float* part_ml,
+                                    cudaStream_t st) {
+    return zlm_attention_decode_fresh(out, out_stride, q, q_stride, pool, block_table, table_stride, token_pos,
+                                      token_slot, T, nq, nkv, hd, scale, window, splits, per, part_o, part_ml, 0, st);
 }
 
 // ---------------------------------------------------------------------------

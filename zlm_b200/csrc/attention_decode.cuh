@@ -16,7 +16,7 @@ __device__ __forceinline__ void attention_decode_item(
     unsigned char* smem_raw, const int tid, const GroupSync gs, const int t, const int kvh, const int split,
     __nv_bfloat16* out, int out_stride, const __nv_bfloat16* q, int q_stride, const __nv_bfloat16* pool,
     const int* block_table, int table_stride, const int* token_pos, const int* token_slot, int nq, int nkv,
-    float scale_log2, int window, int splits, int per, float* part_o, float* part_ml) {
+    float scale_log2, int window, int splits, int per, float* part_o, float* part_ml, int fresh) {
     constexpr int KS = HD / 16;            // k-steps of Q K^T; pairs of output n-tiles of P V
     constexpr int CH = HD / 8;             // 16-byte chunks per row
     constexpr int TILE = ZLM_PAGE * HD;    // elements of one K or V page of one kv head
@@ -42,8 +42,13 @@ __device__ __forceinline__ void attention_decode_item(
     const int p_end = min(page_hi, p_begin + per);
     if (p_begin >= p_end && splits > 1) return;      // the combine kernel skips this split too
 
-    if (PDL) pdl_wait();          // q and this step's keys and values come from the kernel before
-    // the pages do not depend on q: start them now, they land while q is fetched
+    // q and this step's keys and values come from the kernel before; pages that hold only positions
+    // from earlier steps do not, and their loads start before the wait for that kernel.  `fresh`
+    // is how many of a sequence's newest positions this step may have written (0: not known,
+    // nothing is read early).
+    const int old_pages = fresh > 0 ? max(0, pos + 1 - fresh) / ZLM_PAGE : 0;
+    const bool early0 = PDL && p_begin < p_end && p_begin < old_pages;
+    const bool early1 = early0 && p_begin + 1 < p_end && p_begin + 1 < old_pages;
     auto load_page = [&](int p, int stage) {
         if (!ZLM_CHK(pages + p, 4)) return;
         const __nv_bfloat16* kb = pool + (size_t)pages[p] * page_stride + (size_t)kvh * TILE;
@@ -57,10 +62,24 @@ __device__ __forceinline__ void attention_decode_item(
         }
     };
 
-    if (p_begin < p_end) load_page(p_begin, 0);
-    dec_commit();
-    if (p_begin + 1 < p_end) load_page(p_begin + 1, 1);
-    dec_commit();
+    if (early0) {
+        load_page(p_begin, 0);
+        dec_commit();
+        if (early1) {
+            load_page(p_begin + 1, 1);
+            dec_commit();
+        }
+    }
+    if (PDL) pdl_wait();
+    // the other pages do not depend on q either: they land while q is fetched
+    if (!early0) {
+        if (p_begin < p_end) load_page(p_begin, 0);
+        dec_commit();
+    }
+    if (!early1) {
+        if (p_begin + 1 < p_end) load_page(p_begin + 1, 1);
+        dec_commit();
+    }
     // Q fragments: row i of the 16-row tile is head kvh*G + i (zero beyond the group)
     unsigned qf[KS][4] = {};
     {

@@ -581,12 +581,15 @@ class CudaKernels:
             if splits > 1:
                 part_o = plan.scratch("attn.part_o", (T * nq * splits * hd,), torch.float32)
                 part_ml = plan.scratch("attn.part_ml", (T * nq * splits * 2,), torch.float32)
-            self._call("zlm_attention_decode", self._p(out), c_int(out.stride(0)),
+            # (a decode step writes one position per sequence: every page below that one is from earlier
+            # steps, and its load need not wait for the kernel that wrote this step's keys and values)
+            self._call("zlm_attention_decode_fresh", self._p(out), c_int(out.stride(0)),
                        self._p(q), c_int(q.stride(0)), self._p(pool),
                        self._p(block_table), c_int(block_table.stride(0)),
                        self._p(token_pos), self._p(token_slot), c_int(T), c_int(nq),
                        c_int(nkv), c_int(hd), c_float(scale), c_int(window), c_int(splits), c_int(per),
-                       self._p(part_o), self._p(part_ml), self._stream())
+                       self._p(part_o), self._p(part_ml), c_int(max(1, int(getattr(plan, "max_new", 1) or 1))),
+                       self._stream())
             return
         if (plan is not None and not plan.is_decode and q.dtype == torch.bfloat16
                 and getattr(plan, "cu_seqlens", None) is not None
