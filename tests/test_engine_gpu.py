@@ -137,3 +137,33 @@ def test_fp32_cuttings_are_bitwise_equal(tmp_path):
             ents.insert(0, StepEntry(b, [ps[1][t - 80]], []))
         got.append(eng.step(ents).clone())
     assert torch.equal(torch.cat(got), whole)
+
+
+@pytest.mark.parametrize("name", NAMES)
+def test_decode_steps_leave_the_norms_to_the_products(tmp_path, name):
+    """In a bfloat16 step of a few tokens every norm but the first and the last has a streaming
+    product before it and streaming products after it, and launches nothing: two launches fewer a
+    layer than with the norms' own kernels, the same logits within rounding (both are compared
+    with the plain implementation by the other tests; here with each other, at steps of 1, 5 and
+    16 tokens), and nothing of it in a step of 17 tokens, which the other products take."""
+    from zlm_b200 import StepEntry
+    eng, cfg, ref = build(tmp_path, name, "bfloat16")
+    k = eng.rt.k
+    L = cfg.num_hidden_layers
+    (p,) = random_prompts(cfg.vocab_size, [60], seed=33)
+    want = plain_logits(ref, cfg, p)
+    for chunk in (1, 5, 16, 17):
+        got, launches = {}, {}
+        for lazy in (True, False):
+            k.lazy_norms = lazy
+            s = eng.new_sequence()
+            eng.step([StepEntry(s, p[:20], [])])
+            before = k._launches
+            got[lazy] = eng.step([StepEntry(s, p[20:20 + chunk], list(range(chunk)))]).clone()
+            launches[lazy] = k._launches - before
+            eng.release(s)
+        k.lazy_norms = True
+        assert launches[False] - launches[True] == (2 * L - 1 if chunk <= 16 else 0), (chunk, launches)
+        assert_close(got[True], want[20:20 + chunk], "bfloat16", f"{name} norms left to the products, {chunk} tokens")
+        assert_close(got[True], got[False], "bfloat16", f"{name} with and without the norms' kernels, {chunk} tokens")
+    assert k._lazy is None and k._norm_halves is None and k._norm_hint is None
