@@ -90,3 +90,18 @@ def test_many_token_tile_width(lib, T, N, K, width):
 ])
 def test_prefill_attention_heads_per_block(lib, R, max_new, nq, nkv, heads):
     assert lib.zlm_attention_prefill_tc_heads(R, max_new, nq, nkv) == heads
+
+
+@pytest.mark.parametrize("rows,pages,want", [
+    (8, 40, (7, 6)), (8, 48, (7, 7)), (8, 64, (7, 10)),        # 64 pairs: a part for every block the device holds
+    (16, 64, (3, 22)), (24, 40, (2, 20)), (32, 64, (1, 64)), (48, 40, (1, 40)),   # but no second wave
+    (1, 40, (10, 4)), (1, 64, (16, 4)), (1, 16, (8, 2)), (4, 64, (7, 10)),        # few pairs: fewer, longer parts
+    (64, 40, (2, 24)), (64, 8, (1, 8)),                        # more pairs than the device holds: two waves
+])
+def test_decode_attention_cut(rows, pages, want):
+    """The cut of the decode attention at 8 kv heads on a device that holds 444 blocks, as timed."""
+    from zlm_b200.kernels import decode_splits
+    splits, per = decode_splits(rows, 8, pages, 444)
+    assert (splits, per) == want
+    assert splits * per >= pages and (splits - 1) * per < pages      # the parts cover the pages, none is empty by design
+    assert rows * 8 > 444 or splits * rows * 8 <= 444 * 1.1          # one wave of blocks wherever the pairs allow it

@@ -49,18 +49,42 @@ DECODE_BLOCKS_PER_SM = 3      # blocks of the decode attention that an SM holds 
 
 
 def decode_splits(rows: int, nkv: int, len_bucket: int, blocks: int = 148 * DECODE_BLOCKS_PER_SM):
-    """How the decode attention cuts a sequence's pages: (splits, pages per split).  A
-    block's start (the query, its first pages) and end (merging its warps, writing its
-    partial result) cost about as much as several pages, so the parts are as long as they
-    can be while every block that runs at a time (``blocks``: the device's SMs x 3)
-    still has one: one wave of blocks, two for large batches (measured at 2,100 tokens:
-    batch 16 4.2 TB/s with one wave against 3.7 with two; batch 64 5.7 TB/s with two
-    against 5.5 with four and 4.6 with sixteen), and at least two pages long.
+    """How the decode attention cuts a sequence's pages: (splits, pages per split).
     ``len_bucket`` is the longest sequence of the step in pages, rounded up, so that the
-    choice (and a captured graph) holds for many steps."""
-    work = len_bucket * rows * nkv
-    waves = 2 if work >= 16 * blocks else 1
-    per = max(2, -(-work // (blocks * waves)))
+    choice (and a captured graph) holds for many steps; ``blocks`` is what the device holds
+    at a time (its SMs x 3).
+
+    A block's start (the query, its first pages) and end (merging its warps, writing its
+    partial result) cost about as much as several pages, and one block streams a page in
+    about 0.8 us however idle the memory is (two pages in flight).  Timed inside whole decode
+    steps (Qwen3-8B and 0.6B sizes, contexts 2,048 and 4,095; timed alone, kernel after
+    kernel, fewer and longer parts look better than they are in a step, where every block's
+    first two pages are loaded while the kernels before still run):
+    - more (token, kv head) pairs than the device holds blocks (batch 64 at 8 kv heads): parts
+      for two waves of blocks (at 2,100 tokens 5.7 TB/s with two waves against 5.5 with four and
+      4.6 with sixteen; one part a pair 113 us against 95), one wave for short sequences;
+    - otherwise one part for every block the device holds, parts of at least two pages, and no
+      second wave of blocks (a few blocks over, 448 on 444 places at batch 8, cost nothing in a
+      step): so from 245 pairs on there is one part and no combine (batch 32: a step 5 to 7 %
+      shorter than with two waves; batch 16 at 4,095 tokens 2 to 3 % shorter with three parts
+      than with seven);
+    - up to 32 pairs (batch 1 to 4 at 8 kv heads) the parts' own chains of pages bound the kernel
+      and the combine reads every part: as many parts as give half of what the device holds, of
+      at least 4 pages (2 for sequences of up to 16 pages, 8 at 32 pairs): batch 1 at 4,095
+      tokens 16 parts of 4 pages instead of 32 of 2, a step 3 % (8B sizes) to 7 % (0.6B) shorter."""
+    pairs = max(1, rows * nkv)
+    if pairs > blocks:
+        work = len_bucket * pairs
+        waves = 2 if work >= 16 * blocks else 1
+        per = max(2, -(-work // (blocks * waves)))
+    elif pairs <= 32:
+        wanted = -(-(blocks // 2) // pairs)
+        least = 8 if pairs == 32 else (2 if len_bucket <= 16 else 4)
+        per = max(least, -(-len_bucket // wanted))
+    else:
+        per = max(2, -(-len_bucket * pairs // blocks))
+        while per < len_bucket and -(-len_bucket // per) * pairs * 10 > blocks * 11:      # (64 pairs x 7 on 444 places stay)
+            per += 1
     per = min(per, max(1, len_bucket))
     splits = -(-len_bucket // per)
     while splits > 1024:
