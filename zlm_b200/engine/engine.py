@@ -143,6 +143,9 @@ class Engine:
     def run_model(self, ctx, wanted: int) -> Optional[torch.Tensor]:
         """The device work of one step: every schedule entry over the step's tokens,
         then logits at the ``wanted`` first rows of the uploaded ``want_rows``."""
+        forget = getattr(self.rt.k, "forget_pending", None)
+        if forget is not None:
+            forget()            # (only a step that raised half-way leaves anything)
         hidden = self.model.forward(ctx, self.cache.ios)
         logits = self.model.logits(hidden, self.stager.view("want_rows", wanted), wanted) if wanted else None
         flush = getattr(self.rt.k, "flush_shares", None)

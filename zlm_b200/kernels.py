@@ -237,6 +237,13 @@ class CudaKernels:
         before the reading part writes into the stream, and by nobody after that.  Holds for one call."""
         self._lazy_ok = bool(yes) and self.lazy_norms
 
+    def forget_pending(self) -> None:
+        """Drops what one call left for a later one (shares of K, a norm's halves, a norm not run, the
+        arrangement's words) without finishing any of it: for the start of a step, where anything still
+        pending belongs to a step that was given up."""
+        self._shares = self._norm_hint = self._norm_halves = self._lazy = None
+        self._lazy_ok = False
+
     def finish_norm(self) -> None:
         """Runs a norm that ``rmsnorm`` left to the products after it."""
         if self._lazy is None:
