@@ -22,9 +22,6 @@
 #ifndef GEMV_UNROLL
 #define GEMV_UNROLL 4
 #endif
-#ifndef GEMV_MINBLOCKS
-#define GEMV_MINBLOCKS 1
-#endif
 
 __device__ __forceinline__ uint4 ld_stream16(const void* p) {
     uint4 v;
