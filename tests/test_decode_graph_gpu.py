@@ -166,3 +166,45 @@ def test_graph_row_count_changes_and_comes_back(tmp_path, dtype):
         run([0, 4, 2, 3])
     assert len(dec.graphs) == before and n4 >= 1, "the 4-row graph was not replayed"
     assert dec.replays > 0
+
+
+@pytest.mark.parametrize("rows", [8, 20, 30, 64])
+def test_dependent_launches_change_no_bit(rows):
+    """Decode steps with programmatic dependent launches and in plain stream order: the same
+    kernels, so the same bits, at Qwen3-0.6B's layer sizes (two layers), where the steps of 20
+    and 64 rows run the tcgen05 products with their shares and the split attention, and against
+    the plain implementation for one of the rows.  At 30 rows the attention mixer asks for plain
+    launches (one part per pair on about half the blocks the device holds); forced on, they still
+    change nothing."""
+    from zlm_b200 import Engine, StepEntry
+    from zlm_b200.parts.model import DecoderModel
+    from zlm_b200.registry import config_from_dict
+    from zlm_b200.weights import random_tensors
+    from zlm_b200.weights.loader import target_dtype
+    from test_layer_sizes_gpu import SIZES, TOL_8B
+    cfg = config_from_dict(dict(SIZES["0.6B"], vocab_size=2056))
+    tensors = random_tensors(DecoderModel(cfg.to_model_spec()).param_specs(), 8, "cpu", torch.float32)
+    specs = DecoderModel(cfg.to_model_spec()).param_specs()
+    dev = {n: t.to("cuda").to(target_dtype(specs[n], t.dtype, torch.bfloat16)) for n, t in tensors.items()}
+    eng = Engine(cfg, dev, torch.bfloat16, "cuda:0", max_tokens=rows * 512, max_batch=rows)
+    dec = eng.decoder
+    assert dec._pdl(rows) == (rows != 30)
+    lens = [40 + (37 * i) % 300 for i in range(rows)]
+    prompts = random_prompts(cfg.vocab_size, [n + 6 for n in lens], seed=88)
+    runs = {}
+    for pdl in (True, False):
+        dec.use_pdl = pdl
+        dec.graphs.clear()
+        slots = [eng.new_sequence() for _ in range(rows)]
+        eng.step([StepEntry(s, p[:n], []) for s, p, n in zip(slots, prompts, lens)])
+        got = []
+        for t in range(6):
+            dec.step(slots, [p[n + t] for p, n in zip(prompts, lens)], greedy())
+            got.append(dec.last_logits[:rows].clone())
+        for s in slots:
+            eng.release(s)
+        runs[pdl] = torch.stack(got)
+    assert torch.equal(runs[True], runs[False])
+    want = plain_logits(reference_tensors(tensors, "bfloat16"), cfg, prompts[3][:lens[3] + 6])
+    assert_close(runs[True][:, 3], want[lens[3]:], "bfloat16", f"row 3 of {rows}", TOL_8B["bfloat16"])
+    assert eng.rt.k.status(sync=True) == 0

@@ -83,7 +83,7 @@ gemv_bf16_kernel(void* __restrict__ Y, const __nv_bfloat16* __restrict__ X,
     }
     // Four chains of sums per thread, so that four tensor-core products can be in flight
     // (one chain would run at the latency of the instruction).  K is cut into chunks of
-    // 8 x SEG columns; warp w takes the w-th SEG columns of every chunk, as blocks of 32
+    // WARPS x SEG columns; warp w takes the w-th SEG columns of every chunk, as blocks of 32
     // in ascending k; chain 2 * (i & 1) + h takes the h-th 16 k of block i.  The chains are
     // added at the end, (0 + 1) + (2 + 3).  SEG is 512 unless another width spreads K evenly over the
     // warps where 512 would not (gemv_segment below).

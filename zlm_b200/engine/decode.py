@@ -44,10 +44,13 @@ class DecodeRunner:
         self.use_graphs = (cuda and engine.model.graph_safe and not checked) if use_graphs is None else use_graphs
         # Programmatic dependent launch between the step's kernels (a kernel's blocks may be
         # scheduled while the kernel before it drains; each waits before it reads what that one
-        # wrote): None = for steps of up to 16 rows.  Measured against plain stream order:
+        # wrote): None = on, unless a part of the model asks for plain stream order at this
+        # number of rows (``Part.prefers_plain_launches``).  Measured against plain stream order:
         # Qwen3-8B sizes, batch 8: 2,074 -> 2,097 tokens/s, batch 1: 296 -> 299; 0.6B sizes,
-        # batch 8: 5,940 -> 6,100, batch 1: 964 -> 1,028; at batch 64 (one block per SM with
-        # nearly all its shared memory) 8,446 -> 8,475 and 16,450 -> 16,120: left off there.
+        # batch 8: 5,940 -> 6,100, batch 1: 964 -> 1,028.  Above 16 rows it used to gain nothing
+        # (batch 64: 8,446 -> 8,475 and 16,450 -> 16,120); since the decode attention loads its
+        # first pages before its wait it does: a step at batch 17 / 24 / 40 / 64 is 2 to 3 / 3 / 3 /
+        # 2 to 3 % shorter at 8B sizes and 2 to 5 / 6 / 5 / 2 to 4 % at 0.6B sizes.
         self.use_pdl: Optional[bool] = None
         self.graphs: "OrderedDict[Tuple, torch.cuda.CUDAGraph]" = OrderedDict()
         self.graph_generation = -1
@@ -148,7 +151,9 @@ class DecodeRunner:
     def _pdl(self, R: int) -> bool:
         if not hasattr(self.e.rt.k, "set_pdl"):
             return False
-        return self.use_pdl if self.use_pdl is not None else R <= 16
+        if self.use_pdl is not None:
+            return self.use_pdl
+        return not self.e.model.prefers_plain_launches(R)
 
     def _device_work(self, ctx, R: int, params: SamplingParams) -> None:
         if self._pdl(R):

@@ -65,7 +65,8 @@ def decode_splits(rows: int, nkv: int, len_bucket: int, blocks: int = 148 * DECO
       4.6 with sixteen; one part a pair 113 us against 95), one wave for short sequences;
     - otherwise one part for every block the device holds, parts of at least two pages, and no
       second wave of blocks (a few blocks over, 448 on 444 places at batch 8, cost nothing in a
-      step): so from 245 pairs on there is one part and no combine (batch 32: a step 5 to 7 %
+      step while the parts are of up to 12 pages; 224 pairs cut in two parts of 25 pages cost
+      a step 5 %): so from 223 pairs on there is one part and no combine (batch 32: a step 5 to 7 %
       shorter than with two waves; batch 16 at 4,095 tokens 2 to 3 % shorter with three parts
       than with seven);
     - up to 32 pairs (batch 1 to 4 at 8 kv heads) the parts' own chains of pages bound the kernel
@@ -83,7 +84,9 @@ def decode_splits(rows: int, nkv: int, len_bucket: int, blocks: int = 148 * DECO
         per = max(least, -(-len_bucket // wanted))
     else:
         per = max(2, -(-len_bucket * pairs // blocks))
-        while per < len_bucket and -(-len_bucket // per) * pairs * 10 > blocks * 11:      # (64 pairs x 7 on 444 places stay)
+        # (a few blocks over, 64 pairs x 7 on 444 places, are let be where the parts are short; four
+        # blocks of 25 pages that start when the first places come free cost a step 5 %)
+        while per < len_bucket and -(-len_bucket // per) * pairs * 10 > blocks * (11 if per <= 12 else 10):
             per += 1
     per = min(per, max(1, len_bucket))
     splits = -(-len_bucket // per)

@@ -196,6 +196,12 @@ class Part:
     # device data, no allocation) may be captured in a CUDA graph
     graph_safe = True
 
+    def prefers_plain_launches(self, rows: int) -> bool:
+        """Whether a decode step of ``rows`` sequences should launch its kernels in plain stream
+        order instead of as dependent launches (a kernel's blocks scheduled while the kernel
+        before it drains).  One part that says yes decides for the step."""
+        return False
+
     def step_key(self, ctx: "StepContext"):
         """What about a step, beyond its numbers of tokens and sequences, changes the
         launches this part makes (grid sizes, kernel choices): any hashable value, or

@@ -30,6 +30,9 @@ class PreNormBlock(Part):
     def graph_safe(self) -> bool:      # type: ignore[override]
         return all(c.graph_safe for c in self.children().values())
 
+    def prefers_plain_launches(self, rows: int) -> bool:
+        return any(c.prefers_plain_launches(rows) for c in self.children().values())
+
     def step_key(self, ctx: StepContext):
         keys = tuple(k for k in (c.step_key(ctx) for c in self.children().values()) if k is not None)
         return keys or None

@@ -100,6 +100,10 @@ class DecoderModel:
     def graph_safe(self) -> bool:
         return all(b.graph_safe for b in self.blocks)
 
+    def prefers_plain_launches(self, rows: int) -> bool:
+        asks = (getattr(b, "prefers_plain_launches", None) for b in self.blocks)
+        return any(ask(rows) for ask in asks if ask is not None)
+
     def step_key(self, ctx: StepContext) -> Tuple:
         """The parts' say on which steps make the same launches (``Part.step_key``): the
         distinct keys of all parts, in the order of their first appearance."""
