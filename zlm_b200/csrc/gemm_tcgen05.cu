@@ -175,12 +175,25 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
     tc_fence_after();
     const unsigned tmem_base = *tmem_slot;
     pdl_launch_dependents();
-    pdl_wait();          // set-up above overlaps the kernel before; operands and Y are touched from here on
+    // Set-up above overlaps the kernel before.  So do the first loads of W, which no kernel of the
+    // step writes: the ring's stages are all free at the start, and the producer fills them with W
+    // before it waits for the kernel before, with the activations after.  Everybody else waits here;
+    // operands from other kernels and Y are touched after the wait only.
+    const int early = min(KB, STAGES);
+    if (warp == 0 && lane == 0) {
+        for (int kb = 0; kb < early; ++kb) {
+            mbar_expect_tx(&full[kb], A_BYTES + B_BYTES);
+            tma_load_2d(sA + kb * A_BYTES, &map_a, (kb_lo + kb) * TC_BK, a0row, &full[kb]);
+        }
+    }
+    pdl_wait();
 
     if (warp == 0) {
         if (lane == 0) {
-            int issued = 0;
-            for (int kb = 0; kb < KB; ++kb) {
+            int issued = early;
+            for (int kb = 0; kb < early; ++kb)
+                tma_load_2d(sB + kb * B_BYTES, &map_b, (kb_lo + kb) * TC_BK, b0row, &full[kb]);
+            for (int kb = early; kb < KB; ++kb) {
                 const int s = kb % STAGES;
                 const unsigned round = kb / STAGES;
                 if (!mbar_wait(&empty[s], (round & 1) ^ 1, abort_flag, 1)) break;
@@ -814,7 +827,6 @@ gemm_tc_few_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     tc_fence_after();
     const unsigned tmem_base = *tmem_slot;
     pdl_launch_dependents();
-    pdl_wait();
 
     // item -> (tile of outputs, tile of tokens, share of K); the share's k blocks
 #define ZLM_ITEM(item)                                                        \
@@ -825,6 +837,21 @@ gemm_tc_few_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     const int kb_lo = z * kb_per;                                             \
     const int KB = split ? max(0, min(KB_all, kb_lo + kb_per) - kb_lo) : KB_all;
 
+    // The first item's first loads of W (which no kernel of the step writes) go out before the wait
+    // for the kernel before: the ring's stages are all free at the start.  The activations of those
+    // stages follow after the wait, and nothing else of another kernel's is touched before it.
+    int early = 0;
+    if (warp == 0 && lane == 0 && (int)blockIdx.x < items) {
+        ZLM_ITEM((int)blockIdx.x)
+        (void)b0row;
+        early = min(KB, STAGES);
+        for (int kb = 0; kb < early; ++kb) {
+            mbar_expect_tx(&full[kb], A_BYTES + B_BYTES);
+            tma_load_2d(sA + kb * A_BYTES, &map_w, (kb_lo + kb) * TC_BK, a0row, &full[kb]);
+        }
+    }
+    pdl_wait();
+
     if (warp == 0) {
         if (lane == 0) {
             unsigned it = 0;
@@ -833,6 +860,10 @@ gemm_tc_few_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                 ZLM_ITEM(item)
                 for (int kb = 0; kb < KB; ++kb, ++it) {
                     const int s = it % STAGES;
+                    if ((int)it < early) {      // the stage's W is on its way already
+                        tma_load_2d(sB + s * B_BYTES, &map_x, (kb_lo + kb) * TC_BK, b0row, &full[s]);
+                        continue;
+                    }
                     if (!mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1, abort_flag, 1)) { ok = false; break; }
                     mbar_expect_tx(&full[s], A_BYTES + B_BYTES);
                     tma_load_2d(sA + s * A_BYTES, &map_w, (kb_lo + kb) * TC_BK, a0row, &full[s]);

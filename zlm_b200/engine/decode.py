@@ -49,8 +49,9 @@ class DecodeRunner:
         # Qwen3-8B sizes, batch 8: 2,074 -> 2,097 tokens/s, batch 1: 296 -> 299; 0.6B sizes,
         # batch 8: 5,940 -> 6,100, batch 1: 964 -> 1,028.  Above 16 rows it used to gain nothing
         # (batch 64: 8,446 -> 8,475 and 16,450 -> 16,120); since the decode attention loads its
-        # first pages before its wait it does: a step at batch 17 / 24 / 40 / 64 is 2 to 3 / 3 / 3 /
-        # 2 to 3 % shorter at 8B sizes and 2 to 5 / 6 / 5 / 2 to 4 % at 0.6B sizes.
+        # first pages, and the few-token products their first weights, before their wait it does:
+        # a step at batch 17 / 24 / 40 / 64 is 2 to 6 / 1 to 3 / 5 / 3 % shorter at 8B sizes and
+        # 7 / 6 / 5 to 7 / 2 to 5 % at 0.6B sizes.
         self.use_pdl: Optional[bool] = None
         self.graphs: "OrderedDict[Tuple, torch.cuda.CUDAGraph]" = OrderedDict()
         self.graph_generation = -1

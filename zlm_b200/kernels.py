@@ -358,7 +358,9 @@ class CudaKernels:
     def linear(self, out: torch.Tensor, x: torch.Tensor, w: torch.Tensor, accumulate: bool = False,
                impl: Optional[str] = None, defer: bool = False) -> None:
         """out = x @ w.T (out in x's dtype, or fp32), or out += x @ w.T into the fp32
-        residual stream when ``accumulate``.  w is [N, K] row-major.  bf16 products pick
+        residual stream when ``accumulate``.  w is [N, K] row-major and is not written by any kernel
+        of the same step (in a decode step the products' first loads of w do not wait for the kernels
+        before them).  bf16 products pick
         their kernel by the number of tokens: "gemv" (register-fragment streaming, up to
         8), "tc" (TMA + tcgen05, from 9 on), "mma" (mma.sync, what the others do not take);
         ``impl`` forces one (tests).
