@@ -201,7 +201,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
         // this thread is the producer: the Q tiles and the first step's keys and values are on
         // their way before the block has met (they arrive at barriers this thread has just set
-        // up; their stages are free, so nothing waits)
+        // up; their stages are free, so nothing waits).  Q and this step's keys and values come
+        // from the kernel before: as a dependent launch the block is set up while that kernel
+        // drains, and waits for it here.
+        pdl_launch_dependents();
+        pdl_wait();
         mbar_expect_tx(q_full, HPC * Q_BYTES);
         for (int h = 0; h < HPC; ++h) {
             // Q: two 64-column halves per head, 128 token rows
@@ -219,6 +223,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+    pdl_wait();              // (thread 0 has waited before the block met; for the others this returns at once)
     const unsigned tmem_base = *tmem_slot;
 
     if (warp == 0) {

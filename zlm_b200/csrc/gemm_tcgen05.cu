@@ -622,6 +622,20 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     tc_fence_after();
     const unsigned tmem_base = *tmem_slot;
     pdl_launch_dependents();
+    // The first tile's first loads of W (which no kernel of the step writes) go out before the wait
+    // for the kernel before: the ring's stages are all free at the start.  The tokens of those
+    // stages follow after the wait, and nothing else of another kernel's is touched before it.
+    int early = 0;
+    if (warp == 0 && lane == 0 && pair < tiles) {
+        int tm, tn;
+        tile_of(pair, m_tiles, n_tiles, gm, tm, tn);
+        const int b0row = tn * BN + rank * (BN / 2);
+        early = min(KB, STAGES);
+        for (int kb = 0; kb < early; ++kb) {
+            if (rank == 0) mbar_expect_tx(&full[kb], 2 * (A_BYTES + B_BYTES));
+            tma_load_2d_pair(sB + kb * B_BYTES, &map_b, kb * TC_BK, b0row, cluster_addr(&full[kb], 0));
+        }
+    }
     pdl_wait();
 
     if (warp == 0) {
@@ -635,9 +649,13 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 const int b0row = tn * BN + rank * (BN / 2);
                 for (int kb = 0; kb < KB; ++kb, ++it) {
                     const int s = it % STAGES;
+                    const unsigned bar0 = cluster_addr(&full[s], 0);
+                    if ((int)it < early) {      // the stage's W is on its way already
+                        tma_load_2d_pair(sA + s * A_BYTES, &map_a, kb * TC_BK, a0row, bar0);
+                        continue;
+                    }
                     if (!mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1, abort_flag, 1)) { ok = false; break; }
                     if (rank == 0) mbar_expect_tx(&full[s], 2 * (A_BYTES + B_BYTES));
-                    const unsigned bar0 = cluster_addr(&full[s], 0);
                     tma_load_2d_pair(sA + s * A_BYTES, &map_a, kb * TC_BK, a0row, bar0);
                     tma_load_2d_pair(sB + s * B_BYTES, &map_b, kb * TC_BK, b0row, bar0);
                 }
@@ -1403,6 +1421,8 @@ extern "C" int zlm_gemm_tc_qkv(void* Y, const void* X, const void* W, int T, int
 __global__ void rope_table_kernel(float* __restrict__ out, const float* __restrict__ inv_freq,
                                   const int* __restrict__ token_pos, int T, int half) {
     const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    pdl_trigger();
+    pdl_wait();              // the table may still be read by the products of the step before
     if (idx >= T * half) return;
     const int i = idx / T, t = idx - i * T;         // [cos | sin][angle][token]: a warp of the product's epilogue reads along tokens
     if (!ZLM_CHK(token_pos + t, 4) || !ZLM_CHK(inv_freq + i, 4) || !ZLM_CHK(out + idx, 4) ||

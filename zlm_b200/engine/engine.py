@@ -62,6 +62,10 @@ class Engine:
         self.layout = MetaLayout(self.max_step_tokens, self.max_batch)
         self.stager = MetaStager(self.layout, self.device)
         self.steps_run = 0
+        # dependent launches for the kernels of ``step`` (prefill and chunks; the decode runner has
+        # a switch of its own).  Measured, a step of 2,048 / 512 tokens: Qwen3-8B sizes 23.8 -> 23.4 /
+        # 9.35 -> 8.75 ms, 0.6B sizes 5.37 -> 4.93 / 3.98 -> 3.85 ms.
+        self.use_pdl = True
         self.last_logits: Optional[torch.Tensor] = None      # of the last prefill_sample / decode_sample
         from ..sampling import Sampler
         self.sampler = Sampler(self.rt)
@@ -135,7 +139,17 @@ class Engine:
         self.cache.reserve(growth)            # raises before anything is launched
         self.stager.upload(arrays, T, R)
         ctx = make_context(self.stager, arrays, T, R, self.rt.ws)
-        logits = self.run_model(ctx, W)
+        # dependent launches: a kernel is set up, and has its first weights on the way, while the
+        # kernel before it drains (every kernel that is launched so waits before it touches what
+        # another one wrote)
+        pdl = getattr(self.rt.k, "set_pdl", None) if self.use_pdl else None
+        if pdl is not None:
+            pdl(True)
+        try:
+            logits = self.run_model(ctx, W)
+        finally:
+            if pdl is not None:
+                pdl(False)
         self.cache.commit(growth)
         self.steps_run += 1
         return logits
