@@ -688,3 +688,105 @@ def test_toy_block_arrangement_in_one_layer_of_two():
     # and through the generation loop (graphs where the parts allow them)
     out = eng.generate([s[:5] for s in seqs], max_tokens=4)
     assert [len(x) for x in out.tokens] == [4, 4]
+
+
+def test_toy_mixer_that_reads_its_input_by_products_has_its_norms_left_to_them():
+    """A mixer defined here (no cache, no state: y = ((x A^T) * (x B^T)) C^T) says that it reads its
+    input through the kernel object's products alone (``reads_input_by_products``) and adds into the
+    stream with ``linear(accumulate=True, defer=True)``.  In steps of a few tokens the norms before
+    it and after it then launch nothing: its two products take the norm's scale from the sums of
+    squares that the product before left, and its last product leaves them for the feed-forward's
+    norm.  Compared with a plain forward written here, and with the same engine when the norms run
+    as kernels.  (A toy: it is no model of anyone's.)"""
+    from zlm_b200 import Engine, StepEntry
+    from zlm_b200.config import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
+    from zlm_b200.parts.base import Mixer, ParamSpec
+    from zlm_b200.parts.model import DecoderModel
+    from zlm_b200.registry import ARCHITECTURES, MIXERS, register_architecture, register_mixer
+    from zlm_b200.weights import random_tensors
+    H, I, V, L = 64, 96, 120, 3
+
+    if "toy_two_products" not in MIXERS:
+        @register_mixer("toy_two_products")
+        class TwoProducts(Mixer):
+            reads_input_by_products = True
+
+            def __init__(self, hidden_size, inner):
+                self.h, self.inner = hidden_size, inner
+
+            def param_specs(self):
+                return {n: ParamSpec(s) for n, s in (("a.weight", (self.inner, self.h)), ("b.weight", (self.inner, self.h)),
+                                                     ("c.weight", (self.h, self.inner)))}
+
+            def bind(self, params):
+                self.a, self.b, self.c = params["a.weight"], params["b.weight"], params["c.weight"]
+
+            def forward(self, x, residual, ctx, io):
+                k, T = self.rt.k, x.shape[0]
+                pa = ctx.scratch("toy2.a", (T, self.inner), x.dtype)
+                pb = ctx.scratch("toy2.b", (T, self.inner), x.dtype)
+                k.linear(pa, x, self.a)
+                k.linear(pb, x, self.b)
+                pa.mul_(pb)                                     # its own buffers: torch may have them
+                k.linear(residual, pa, self.c, accumulate=True, defer=True)
+
+    if "ToyTwoProductsForCausalLM" not in ARCHITECTURES:
+        @register_architecture("ToyTwoProductsForCausalLM")
+        @dataclass(frozen=True)
+        class Cfg:
+            eos_token_ids: tuple = ()
+
+            @classmethod
+            def from_dict(cls, d):
+                return cls()
+
+            def to_dict(self):
+                return {"architectures": ["ToyTwoProductsForCausalLM"]}
+
+            def to_model_spec(self):
+                norm = lambda p: PartSpec("rms_norm", {"eps": 1e-5}, prefix=p)
+                layers = tuple(LayerSpec("pre_norm", PartSpec("toy_two_products", {"inner": I}, prefix=f"l{i}.mix."),
+                                         PartSpec("swiglu", {"intermediate_size": I}, prefix=f"l{i}.ffn."),
+                                         norm(f"l{i}.n1."), norm(f"l{i}.n2.")) for i in range(L))
+                return ModelSpec("ToyTwoProductsForCausalLM", H, V, 512, layers, tuple(ScheduleEntry(i) for i in range(L)),
+                                 PartSpec("token_embedding", {}, prefix="emb."), norm("out_norm."),
+                                 PartSpec("lm_head", {"tied": True}, prefix="head."))
+
+    cfg = ARCHITECTURES["ToyTwoProductsForCausalLM"]()
+    t = random_tensors(DecoderModel(cfg.to_model_spec()).param_specs(), 17)
+    for n in t:
+        if ".mix." in n:
+            t[n] = t[n] * 20                # so that the mixer's share of the stream is not lost in rounding
+    ref = {n: (v.to(torch.bfloat16).float() if v.dim() == 2 else v) for n, v in t.items()}
+    dev = {n: (v.to(torch.bfloat16) if v.dim() == 2 else v).cuda() for n, v in t.items()}
+
+    def plain(ids):
+        h = P.embed(ref["emb.weight"], ids)
+        for i in range(L):
+            x = P.rms_norm(h, ref[f"l{i}.n1.weight"], 1e-5)
+            h = h + P.linear(P.linear(x, ref[f"l{i}.mix.a.weight"]) * P.linear(x, ref[f"l{i}.mix.b.weight"]),
+                             ref[f"l{i}.mix.c.weight"])
+            x = P.rms_norm(h, ref[f"l{i}.n2.weight"], 1e-5)
+            h = h + P.linear(P.swiglu(P.linear(x, ref[f"l{i}.ffn.gate_proj.weight"]), P.linear(x, ref[f"l{i}.ffn.up_proj.weight"])),
+                             ref[f"l{i}.ffn.down_proj.weight"])
+        return P.linear(P.rms_norm(h, ref["out_norm.weight"], 1e-5), ref["emb.weight"])
+
+    eng = Engine(cfg, dev, torch.bfloat16, "cuda:0", max_tokens=256, max_batch=2)
+    k = eng.rt.k
+    ids = torch.randint(0, V, (30,), generator=torch.Generator().manual_seed(18)).tolist()
+    want = plain(ids)
+    got, launches = {}, {}
+    for lazy in (True, False):
+        k.lazy_norms = lazy
+        sl = eng.new_sequence()
+        eng.step([StepEntry(sl, ids[:21], [])])                 # 21 tokens: the other products, every norm a kernel
+        before = k._launches
+        got[lazy] = eng.step([StepEntry(sl, ids[21:], list(range(9)))]).float().cpu()      # 9 tokens: streaming products
+        launches[lazy] = k._launches - before
+        eng.release(sl)
+    k.lazy_norms = True
+    assert launches[False] - launches[True] == 2 * L - 1, launches        # every norm but the first and the last
+    for lazy in (True, False):
+        rel = (got[lazy] - want[21:]).norm(dim=-1) / want[21:].norm(dim=-1)
+        assert float(rel.max()) < 2e-2, (lazy, rel)
+    eng.check(sync=True)
