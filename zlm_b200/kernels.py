@@ -230,7 +230,7 @@ class CudaKernels:
         streaming product (up to 16 tokens) then also leaves the normed rows but for their scale, and
         the rows' sums of squares block by block; ``rmsnorm`` launches nothing, and the streaming
         products that read its output take the scale from those sums and apply it to their own sums.
-        73 launches fewer in a decode step.  Whatever else is given the norm's output through this
+        Two launches fewer a layer in a decode step.  Whatever else is given the norm's output through this
         class has the norm run first (``finish_norm``), so the word is never wrong, only sometimes
         useless; code that reads it by other means says so beforehand (``norm_output_read_by_products``)."""
         self._norm_hint = weight if self.lazy_norms else None
