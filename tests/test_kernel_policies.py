@@ -105,3 +105,17 @@ def test_decode_attention_cut(rows, pages, want):
     assert (splits, per) == want
     assert splits * per >= pages and (splits - 1) * per < pages      # the parts cover the pages, none is empty by design
     assert rows * 8 > 444 or splits * rows * 8 <= 444 * 1.1          # one wave of blocks wherever the pairs allow it
+
+
+def test_decode_attention_cut_always_covers_the_pages():
+    """Whatever the batch, the heads and the length: the parts cover every page, none of them is
+    empty by design, and there are no more of them than the combine takes."""
+    from zlm_b200.kernels import decode_splits
+    for blocks in (444, 132 * 3, 8):
+        for rows in (1, 2, 3, 4, 7, 8, 16, 17, 27, 28, 31, 32, 55, 56, 64, 200, 1024):
+            for nkv in (1, 2, 5, 8, 16, 64):
+                for pages in list(range(1, 70)) + [128, 500, 2048, 16384]:
+                    splits, per = decode_splits(rows, nkv, pages, blocks)
+                    assert per >= 1 and 1 <= splits <= 1024, (rows, nkv, pages, blocks, splits, per)
+                    assert splits * per >= pages, (rows, nkv, pages, blocks, splits, per)
+                    assert (splits - 1) * per < pages, (rows, nkv, pages, blocks, splits, per)
